@@ -1,0 +1,538 @@
+// SPConvIdx: rulebook ("index") generation for submanifold, strided and transposed sparse convolution.
+//
+// Replaces spconv::func::createSparseSubMIndex / createSparseConvIndex of the reference
+// (trt/spconv/index.cu:253-476) behind the I/O contract of SPConvIdxPlugin (trt/spconv/index_trt.cu:52-249).
+//
+// Pipeline (all counts stay on the device, no host synchronisation):
+//   SubM : table reset -> insert inputs -> probe neighbours (pair table + per-CTA counts) -> segment scan
+//          -> compaction -> padding fill
+//   Conv : table reset -> insert outputs (first-touch pair id wins) -> count winners -> scan -> number
+//          outputs + coordinates -> translate slots to output ids (+ per-CTA counts) -> segment scan
+//          -> compaction -> padding fill
+// Work decomposition: one thread per (input voxel, kernel row), a kernel row being the run of offsets along the
+// fastest axis; a warp holds 32 consecutive inputs of one row so the pair table is written with 128-byte
+// coalesced stores and the probes of one thread fall into one 32-byte hash bucket (see common.cuh).
+#include "common.cuh"
+
+namespace d3d {
+namespace {
+
+constexpr int kIdxThreads = 256;  // inputs per CTA in every pass; the granularity of the per-CTA counts
+constexpr int kSegment = 128;     // every kernel-offset segment starts at a multiple of 128 (trt/spconv/index.cu:21)
+constexpr int kMaxKernelVol = 512;
+
+struct Geometry {
+  int ndim;
+  int kvol;
+  int rows;    // kvol / ksize[ndim-1]
+  int klast;   // ksize[ndim-1]
+  int transpose;
+  int ksize[D3D_MAX_NDIM], stride[D3D_MAX_NDIM], pad[D3D_MAX_NDIM], dil[D3D_MAX_NDIM];
+  int shape[D3D_MAX_NDIM + 1];  // extent of the key space: [B, D0', D1', ..]
+};
+
+__device__ __forceinline__ void load_coor(const int32_t* __restrict__ coors, int ndim, int64_t i, int* c) {
+  if (ndim == 3) {
+    int4 v = __ldg(reinterpret_cast<const int4*>(coors) + i);
+    c[0] = v.x, c[1] = v.y, c[2] = v.z, c[3] = v.w;
+  } else {
+    for (int d = 0; d <= ndim; ++d) c[d] = __ldg(coors + i * (ndim + 1) + d);
+  }
+}
+
+// Output coordinate along dimension d for kernel tap kd (trt/spconv/geometry.h:41-49 forward, :66-72 transposed).
+__device__ __forceinline__ bool out_coord(const Geometry& g, int d, int in, int kd, int* out) {
+  int o;
+  if (g.transpose) {
+    o = in * g.stride[d] - g.pad[d] + kd * g.dil[d];
+  } else {
+    int dc = in + g.pad[d] - kd * g.dil[d];
+    if (dc % g.stride[d] != 0) return false;
+    o = dc / g.stride[d];
+  }
+  *out = o;
+  return o >= 0 && o < g.shape[d + 1];
+}
+
+// Resolve the leading (all but fastest) taps of kernel row `row`; returns false when the row is out of range
+// for this input. *prefix receives the packed key of the leading coordinates.
+__device__ __forceinline__ bool row_prefix(const Geometry& g, const int* c, int row, uint32_t* prefix) {
+  if (c[0] < 0 || c[0] >= g.shape[0]) return false;
+  int taps[D3D_MAX_NDIM];
+  int rem = row;
+  for (int d = g.ndim - 2; d >= 0; --d) {
+    taps[d] = rem % g.ksize[d];
+    rem /= g.ksize[d];
+  }
+  uint32_t key = (uint32_t)c[0];
+  for (int d = 0; d < g.ndim - 1; ++d) {
+    int o;
+    if (!out_coord(g, d, c[d + 1], taps[d], &o)) return false;
+    key = key * (uint32_t)g.shape[d + 1] + (uint32_t)o;
+  }
+  *prefix = key;
+  return true;
+}
+
+__device__ __forceinline__ void decode_key(const Geometry& g, uint32_t key, int32_t* out) {
+  for (int d = g.ndim; d >= 1; --d) {
+    out[d] = (int32_t)(key % (uint32_t)g.shape[d]);
+    key /= (uint32_t)g.shape[d];
+  }
+  out[0] = (int32_t)key;
+}
+
+__device__ __forceinline__ int live_count(const int32_t* num_act_in, int64_t n_max) {
+  int n = *num_act_in;
+  n = n < 0 ? 0 : n;
+  return n > n_max ? (int)n_max : n;
+}
+
+// ---------------------------------------------------------------------------------------------
+__global__ void reset_table_kernel(unsigned long long* table, const int32_t* num_act_in, int64_t n_max, int fan,
+                                   uint32_t cap_max) {
+  uint32_t cap = hash_capacity((long long)live_count(num_act_in, n_max) * fan, cap_max);
+  ulonglong2* t2 = reinterpret_cast<ulonglong2*>(table);
+  for (uint32_t s = blockIdx.x * blockDim.x + threadIdx.x; s < cap / 2; s += gridDim.x * blockDim.x)
+    t2[s] = make_ulonglong2(kEmptySlot, kEmptySlot);
+}
+
+__global__ void subm_insert_kernel(unsigned long long* table, const int32_t* __restrict__ coors,
+                                   const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max) {
+  int n = live_count(num_act_in, n_max);
+  uint32_t mask = hash_capacity(n, cap_max) - 1;
+  int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  int c[D3D_MAX_NDIM + 1];
+  load_coor(coors, g.ndim, i, c);
+  uint32_t key = 0;
+  for (int d = 0; d <= g.ndim; ++d) {
+    if (c[d] < 0 || c[d] >= g.shape[d]) return;
+    key = key * (uint32_t)g.shape[d] + (uint32_t)c[d];
+  }
+  hash_insert_min(table, mask, key, (uint32_t)i);
+}
+
+// SubM probe: pair_out[k][i] = id of the active voxel at (coor_i + pad - k*dil), or -1 (trt/spconv/index.cu:48-84).
+// CTA (x = input block, y = kernel row); also emits the number of hits per (k, input block).
+__global__ void subm_probe_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ coors,
+                                  const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
+                                  int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk) {
+  __shared__ int warp_cnt[kIdxThreads / 32];
+  int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  uint32_t mask = hash_capacity(n, cap_max) - 1;
+  int row = blockIdx.y;
+  int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  int c[D3D_MAX_NDIM + 1];
+  uint32_t prefix = 0;
+  bool row_ok = false;
+  if (i < n) {
+    load_coor(coors, g.ndim, i, c);
+    row_ok = row_prefix(g, c, row, &prefix);
+  }
+  int dl = g.ndim - 1;
+  for (int kl = 0; kl < g.klast; ++kl) {
+    int k = row * g.klast + kl;
+    int v = -1, o;
+    if (row_ok && out_coord(g, dl, c[dl + 1], kl, &o))
+      v = hash_lookup(table, mask, prefix * (uint32_t)g.shape[dl + 1] + (uint32_t)o);
+    if (i < n) pair_out[(int64_t)k * n_max + i] = v;
+    unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+    if (lane_id() == 0) warp_cnt[threadIdx.x >> 5] = __popc(hits);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      int s = 0;
+      for (int w = 0; w < kIdxThreads / 32; ++w) s += warp_cnt[w];
+      block_counts[(int64_t)k * nblk + blockIdx.x] = s;
+    }
+    __syncthreads();
+  }
+}
+
+// Conv insert: every valid (input, offset) inserts its output key with value = i*kvol + k; the smallest pair id
+// survives in the slot.  pair_out[k][i] receives the slot (>= 0) or -1.
+__global__ void conv_insert_kernel(unsigned long long* table, const int32_t* __restrict__ coors,
+                                   const int32_t* num_act_in, int64_t n_max, Geometry g, int fan, uint32_t cap_max,
+                                   int32_t* __restrict__ pair_out) {
+  int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  uint32_t mask = hash_capacity((long long)n * fan, cap_max) - 1;
+  int row = blockIdx.y;
+  int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  if (i >= n) return;
+  int c[D3D_MAX_NDIM + 1];
+  uint32_t prefix = 0;
+  load_coor(coors, g.ndim, i, c);
+  bool row_ok = row_prefix(g, c, row, &prefix);
+  int dl = g.ndim - 1;
+  for (int kl = 0; kl < g.klast; ++kl) {
+    int k = row * g.klast + kl;
+    int v = -1, o;
+    if (row_ok && out_coord(g, dl, c[dl + 1], kl, &o)) {
+      uint32_t slot = hash_insert_min(table, mask, prefix * (uint32_t)g.shape[dl + 1] + (uint32_t)o,
+                                      (uint32_t)(i * g.kvol + k));
+      v = slot == 0xFFFFFFFFu ? -1 : (int)slot;
+    }
+    pair_out[(int64_t)k * n_max + i] = v;
+  }
+}
+
+// A pair "wins" its output voxel when its id is the one left in the slot.
+__device__ __forceinline__ bool is_winner(const unsigned long long* table, int slot, uint32_t pair_id) {
+  return slot >= 0 && (uint32_t)table[slot] == pair_id;
+}
+
+__global__ void conv_count_winners_kernel(const unsigned long long* __restrict__ table,
+                                          const int32_t* __restrict__ pair_out, const int32_t* num_act_in,
+                                          int64_t n_max, int kvol, int32_t* __restrict__ winners) {
+  __shared__ int scratch[40];
+  int n = live_count(num_act_in, n_max);
+  int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  int cnt = 0;
+  if (i < n)
+    for (int k = 0; k < kvol; ++k) cnt += is_winner(table, pair_out[(int64_t)k * n_max + i], (uint32_t)(i * kvol + k));
+  int total;
+  block_exclusive_scan(cnt, scratch, &total);
+  if (threadIdx.x == 0) winners[blockIdx.x] = total;
+}
+
+// Number the output voxels in pair-id order and write their coordinates (index.cu:104-121).
+__global__ void conv_assign_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ pair_out,
+                                   const int32_t* num_act_in, int64_t n_max, Geometry g,
+                                   const int32_t* __restrict__ winners_base, int32_t max_out,
+                                   int32_t* __restrict__ slot_out, int32_t* __restrict__ out_coors) {
+  __shared__ int scratch[40];
+  int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  int cnt = 0;
+  if (i < n)
+    for (int k = 0; k < g.kvol; ++k)
+      cnt += is_winner(table, pair_out[(int64_t)k * n_max + i], (uint32_t)(i * g.kvol + k));
+  int total;
+  int id = winners_base[blockIdx.x] + block_exclusive_scan(cnt, scratch, &total);
+  if (i >= n || cnt == 0) return;
+  for (int k = 0; k < g.kvol; ++k) {
+    int slot = pair_out[(int64_t)k * n_max + i];
+    if (!is_winner(table, slot, (uint32_t)(i * g.kvol + k))) continue;
+    if (id < max_out) {
+      slot_out[slot] = id;
+      int32_t oc[D3D_MAX_NDIM + 1];
+      decode_key(g, (uint32_t)(table[slot] >> 32), oc);
+      for (int d = 0; d <= g.ndim; ++d) out_coors[(int64_t)id * (g.ndim + 1) + d] = oc[d];
+    } else {
+      slot_out[slot] = -1;  // beyond maxNumActOut: the pair is dropped (index.cu:158-172)
+    }
+    ++id;
+  }
+}
+
+// pair_out: slot -> output id; per-(k, input block) hit counts.  CTA (x = input block, y = k).
+__global__ void conv_translate_kernel(int32_t* __restrict__ pair_out, const int32_t* __restrict__ slot_out,
+                                      const int32_t* num_act_in, int64_t n_max, int32_t* __restrict__ block_counts,
+                                      int nblk) {
+  __shared__ int warp_cnt[kIdxThreads / 32];
+  int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  int k = blockIdx.y;
+  int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  int v = -1;
+  if (i < n) {
+    int slot = pair_out[(int64_t)k * n_max + i];
+    if (slot >= 0) v = slot_out[slot];
+    pair_out[(int64_t)k * n_max + i] = v;
+  }
+  unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+  if (lane_id() == 0) warp_cnt[threadIdx.x >> 5] = __popc(hits);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int s = 0;
+    for (int w = 0; w < kIdxThreads / 32; ++w) s += warp_cnt[w];
+    block_counts[(int64_t)k * nblk + blockIdx.x] = s;
+  }
+}
+
+// Single CTA of 1024 threads.  Warp w scans the counts of offsets w, w+32, ..; then the segment starts
+// (each rounded up to 128, trt/spconv/index.cu:148-156) and numIndex (index.cu:139-144) are produced.
+// seg[0..kvol] = start of each segment (seg[kvol] = numIndex), seg[kvol+1 .. 2*kvol] = pair count of each offset.
+__global__ void segment_scan_kernel(int32_t* __restrict__ block_counts, int nblk, int kvol,
+                                    const int32_t* num_act_in, int64_t n_max, int32_t* __restrict__ seg,
+                                    int32_t* num_index) {
+  __shared__ int counts[kMaxKernelVol];
+  int n = live_count(num_act_in, n_max);
+  int live_blk = (n + kIdxThreads - 1) / kIdxThreads;
+  int warp = threadIdx.x >> 5, lane = lane_id();
+  for (int k = warp; k < kvol; k += blockDim.x >> 5) {
+    int carry = 0;
+    for (int base = 0; base < live_blk; base += 32) {
+      int j = base + lane;
+      int v = j < live_blk ? block_counts[(int64_t)k * nblk + j] : 0;
+      int inc = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        int t = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += t;
+      }
+      if (j < live_blk) block_counts[(int64_t)k * nblk + j] = carry + inc - v;
+      carry += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) counts[k] = carry;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int pos = 0;
+    for (int k = 0; k < kvol; ++k) {
+      seg[k] = pos;
+      seg[kvol + 1 + k] = counts[k];
+      pos += (counts[k] + kSegment - 1) / kSegment * kSegment;
+    }
+    seg[kvol] = pos;
+    *num_index = pos;
+  }
+}
+
+// Write the compacted (gatherIn, scatterOut, kernelOffset) triples (trt/spconv/index.cu:123-146).
+__global__ void compact_kernel(const int32_t* __restrict__ pair_out, const int32_t* __restrict__ block_prefix,
+                               const int32_t* __restrict__ seg, const int32_t* num_act_in, int64_t n_max, int nblk,
+                               int32_t* __restrict__ index, int64_t row_len) {
+  __shared__ int warp_off[kIdxThreads / 32 + 1];
+  int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  int k = blockIdx.y;
+  int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  int v = i < n ? pair_out[(int64_t)k * n_max + i] : -1;
+  unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+  int warp = threadIdx.x >> 5;
+  if (lane_id() == 0) warp_off[warp + 1] = __popc(hits);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    warp_off[0] = 0;
+    for (int w = 1; w <= kIdxThreads / 32; ++w) warp_off[w] += warp_off[w - 1];
+  }
+  __syncthreads();
+  if (v < 0) return;
+  int64_t pos = (int64_t)seg[k] + block_prefix[(int64_t)k * nblk + blockIdx.x] + warp_off[warp] +
+                __popc(hits & lanemask_lt());
+  if (pos >= row_len) return;
+  index[pos] = i;
+  index[row_len + pos] = v;
+  index[2 * row_len + pos] = k;
+}
+
+// Everything that is not a pair is -1: the unused tail of each 128-aligned segment and the rows beyond
+// numIndex (the reference memsets the three rows beforehand, trt/spconv/index.cu:352-354).
+__global__ void fill_padding_kernel(const int32_t* __restrict__ seg, int kvol, int32_t* __restrict__ index,
+                                    int64_t row_len) {
+  int num_index = seg[kvol];
+  int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  // in-segment padding: at most 127 entries per offset
+  for (int64_t t = tid; t < (int64_t)kvol * kSegment; t += nthreads) {
+    int k = (int)(t / kSegment), j = (int)(t % kSegment);
+    int64_t pos = (int64_t)seg[k] + seg[kvol + 1 + k] + j;
+    if (pos < seg[k + 1] && pos < row_len) {
+      index[pos] = -1;
+      index[row_len + pos] = -1;
+      index[2 * row_len + pos] = -1;
+    }
+  }
+  int64_t tail = row_len - num_index;
+  for (int64_t t = tid; t < 3 * tail; t += nthreads) {
+    int64_t r = t / tail, p = t % tail;
+    index[r * row_len + num_index + p] = -1;
+  }
+}
+
+struct Plan {
+  Geometry g;
+  int64_t n_max;
+  int64_t row_len;
+  int nblk;
+  int fan;
+  uint32_t cap_max;
+  // workspace
+  unsigned long long* table;
+  int32_t* pair_out;
+  int32_t* block_counts;
+  int32_t* seg;
+  int32_t* slot_out;
+  int32_t* winners;
+  size_t bytes;
+};
+
+int make_plan(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in, void* workspace, Plan* plan) {
+  D3D_REQUIRE(p && in && n_in >= 3, D3D_ERR_INVALID_ARGUMENT);
+  int ndim = p->ndim;
+  D3D_REQUIRE(ndim >= 1 && ndim <= D3D_MAX_NDIM, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(in[0].nb_dims == 2 && in[0].dims[1] == ndim + 1, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(in[2].nb_dims == ndim + 2, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(in[0].dtype == D3D_INT32 && in[1].dtype == D3D_INT32, D3D_ERR_UNSUPPORTED_DTYPE);
+  Geometry& g = plan->g;
+  g.ndim = ndim;
+  g.kvol = 1;
+  g.transpose = p->transpose && !p->subm;
+  for (int d = 0; d < D3D_MAX_NDIM; ++d) g.ksize[d] = g.stride[d] = g.dil[d] = 1, g.pad[d] = 0;
+  int64_t fan = 1;
+  for (int d = 0; d < ndim; ++d) {
+    D3D_REQUIRE(p->kernel_size[d] >= 1 && p->stride[d] >= 1 && p->dilation[d] >= 1, D3D_ERR_INVALID_ARGUMENT);
+    g.ksize[d] = p->kernel_size[d], g.stride[d] = p->stride[d], g.pad[d] = p->padding[d], g.dil[d] = p->dilation[d];
+    g.kvol *= g.ksize[d];
+    fan *= g.transpose ? g.ksize[d] : (g.ksize[d] + g.stride[d] - 1) / g.stride[d];
+  }
+  D3D_REQUIRE(g.kvol <= kMaxKernelVol, D3D_ERR_TOO_LARGE);
+  g.klast = g.ksize[ndim - 1];
+  g.rows = g.kvol / g.klast;
+  // key space = output spatial shape (input shape for SubM, index_trt.cu:212-226)
+  int64_t vol = in[2].dims[0];
+  g.shape[0] = (int)in[2].dims[0];
+  for (int d = 0; d < ndim; ++d) {
+    int64_t e = in[2].dims[d + 2];
+    if (!p->subm) {
+      if (g.transpose)
+        e = (e - 1) * g.stride[d] - 2 * g.pad[d] + (g.ksize[d] - 1) * g.dil[d] + p->out_padding[d] + 1;
+      else
+        e = (e + 2 * g.pad[d] - g.dil[d] * (g.ksize[d] - 1) - 1) / g.stride[d] + 1;
+    }
+    D3D_REQUIRE(e >= 1, D3D_ERR_INVALID_ARGUMENT);
+    g.shape[d + 1] = (int)e;
+    vol *= e;
+    D3D_REQUIRE(vol < (1ll << 31), D3D_ERR_TOO_LARGE);  // keys are 31-bit linear offsets, as in the reference
+  }
+  plan->n_max = in[0].dims[0];
+  D3D_REQUIRE(plan->n_max >= 0 && plan->n_max * (int64_t)g.kvol < (1ll << 31), D3D_ERR_TOO_LARGE);
+  plan->row_len = (int64_t)g.kvol * (plan->n_max + 128);
+  plan->nblk = (int)ceil_div(plan->n_max > 0 ? plan->n_max : 1, kIdxThreads);
+  plan->fan = p->subm ? 1 : (int)(fan < g.kvol ? fan : g.kvol);
+  size_t cap = next_pow2((size_t)(plan->n_max > 8 ? plan->n_max : 8) * plan->fan * 2);
+  D3D_REQUIRE(cap <= (1ull << 30), D3D_ERR_TOO_LARGE);
+  plan->cap_max = (uint32_t)(cap < 16 ? 16 : cap);
+  Carver w(workspace);
+  plan->table = w.take<unsigned long long>(plan->cap_max);
+  plan->pair_out = w.take<int32_t>((size_t)g.kvol * (plan->n_max > 0 ? plan->n_max : 1));
+  plan->block_counts = w.take<int32_t>((size_t)g.kvol * plan->nblk);
+  plan->seg = w.take<int32_t>(2 * (size_t)g.kvol + 2);
+  plan->slot_out = p->subm ? nullptr : w.take<int32_t>(plan->cap_max);
+  plan->winners = p->subm ? nullptr : w.take<int32_t>((size_t)plan->nblk + 1);
+  plan->bytes = w.off;
+  return D3D_OK;
+}
+
+}  // namespace
+}  // namespace d3d
+
+using namespace d3d;
+
+extern "C" int d3d_spconv_index_parse(int ndim, const void* data_s, size_t len, d3d_spconv_index_params* p) {
+  D3D_REQUIRE(data_s && p && ndim >= 1 && ndim <= D3D_MAX_NDIM, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(len >= (size_t)(5 * ndim + 1) * 4 + 2, D3D_ERR_BAD_BLOB);
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(data_s);
+  memset(p, 0, sizeof(*p));
+  p->ndim = ndim;
+  int32_t* fields[5] = {p->kernel_size, p->stride, p->padding, p->dilation, p->out_padding};
+  for (int f = 0; f < 5; ++f) memcpy(fields[f], b + (size_t)f * ndim * 4, (size_t)ndim * 4);
+  memcpy(&p->max_num_act_out, b + (size_t)5 * ndim * 4, 4);
+  p->subm = b[(size_t)5 * ndim * 4 + 4] != 0;
+  p->transpose = b[(size_t)5 * ndim * 4 + 5] != 0;
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_index_num_outputs(const d3d_spconv_index_params* p) {
+  D3D_REQUIRE(p, D3D_ERR_INVALID_ARGUMENT);
+  return p->subm ? 2 : 5;
+}
+
+extern "C" int d3d_spconv_index_output_desc(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
+                                            int out_index, d3d_tensor_desc* out) {
+  D3D_REQUIRE(p && in && out && n_in >= 3, D3D_ERR_INVALID_ARGUMENT);
+  int ndim = p->ndim;
+  memset(out, 0, sizeof(*out));
+  out->dtype = D3D_INT32;
+  int64_t kvol = 1;
+  for (int d = 0; d < ndim; ++d) kvol *= p->kernel_size[d];
+  switch (out_index) {
+    case 0:
+      out->nb_dims = 2, out->dims[0] = 3, out->dims[1] = kvol * (in[0].dims[0] + 128);
+      return D3D_OK;
+    case 1:
+    case 3: out->nb_dims = 1, out->dims[0] = 1; return D3D_OK;
+    case 2: out->nb_dims = 2, out->dims[0] = p->max_num_act_out, out->dims[1] = ndim + 1; return D3D_OK;
+    case 4:
+      *out = in[2];
+      for (int d = 0; d < ndim; ++d) {
+        int64_t e = in[2].dims[d + 2];
+        if (p->transpose)
+          e = (e - 1) * p->stride[d] - 2 * p->padding[d] + (p->kernel_size[d] - 1) * p->dilation[d] +
+              p->out_padding[d] + 1;
+        else
+          e = (e + 2 * p->padding[d] - p->dilation[d] * (p->kernel_size[d] - 1) - 1) / p->stride[d] + 1;
+        out->dims[d + 2] = e;
+      }
+      return D3D_OK;
+    default: return D3D_ERR_INVALID_ARGUMENT;
+  }
+}
+
+extern "C" int d3d_spconv_index_workspace(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
+                                          size_t* bytes) {
+  D3D_REQUIRE(bytes, D3D_ERR_INVALID_ARGUMENT);
+  Plan plan;
+  int rc = make_plan(p, in, n_in, nullptr, &plan);
+  if (rc != D3D_OK) return rc;
+  *bytes = plan.bytes;
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
+                                        const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                                        void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  D3D_REQUIRE(inputs && outputs && out, D3D_ERR_INVALID_ARGUMENT);
+  Plan plan;
+  int rc = make_plan(p, in, n_in, workspace, &plan);
+  if (rc != D3D_OK) return rc;
+  D3D_REQUIRE(n_out >= (p->subm ? 2 : 5), D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(workspace && workspace_bytes >= plan.bytes, D3D_ERR_WORKSPACE_TOO_SMALL);
+  D3D_REQUIRE(out[0].nb_dims == 2 && out[0].dims[0] == 3 && out[0].dims[1] == plan.row_len, D3D_ERR_INVALID_ARGUMENT);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int32_t* coors = reinterpret_cast<const int32_t*>(inputs[0]);
+  const int32_t* num_act_in = reinterpret_cast<const int32_t*>(inputs[1]);
+  int32_t* index = reinterpret_cast<int32_t*>(outputs[0]);
+  int32_t* num_index = reinterpret_cast<int32_t*>(outputs[1]);
+  const Geometry& g = plan.g;
+  const int64_t n_max = plan.n_max;
+  if (n_max == 0) {
+    cudaMemsetAsync(num_index, 0, sizeof(int32_t), st);
+    if (!p->subm) cudaMemsetAsync(outputs[3], 0, sizeof(int32_t), st);
+    D3D_CHECK_LAUNCH();
+    return D3D_OK;
+  }
+  D3D_REQUIRE(coors && num_act_in && index && num_index, D3D_ERR_INVALID_ARGUMENT);
+  const int nblk = plan.nblk;
+  reset_table_kernel<<<stream_grid(plan.cap_max / 2, 256), 256, 0, st>>>(plan.table, num_act_in, n_max, plan.fan,
+                                                                         plan.cap_max);
+  if (p->subm) {
+    subm_insert_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max);
+    subm_probe_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
+                                                                  plan.cap_max, plan.pair_out, plan.block_counts, nblk);
+  } else {
+    int32_t* out_coors = reinterpret_cast<int32_t*>(outputs[2]);
+    int32_t* num_act_out = reinterpret_cast<int32_t*>(outputs[3]);
+    D3D_REQUIRE(out_coors && num_act_out, D3D_ERR_INVALID_ARGUMENT);
+    D3D_REQUIRE(out[2].dims[0] >= p->max_num_act_out, D3D_ERR_INVALID_ARGUMENT);
+    conv_insert_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.fan,
+                                                                   plan.cap_max, plan.pair_out);
+    conv_count_winners_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g.kvol,
+                                                            plan.winners);
+    scan_totals_kernel<<<1, 1024, 0, st>>>(plan.winners, nblk, p->max_num_act_out, num_act_out);
+    conv_assign_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g, plan.winners,
+                                                     p->max_num_act_out, plan.slot_out, out_coors);
+    conv_translate_kernel<<<dim3(nblk, g.kvol), kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max,
+                                                                      plan.block_counts, nblk);
+  }
+  segment_scan_kernel<<<1, 1024, 0, st>>>(plan.block_counts, nblk, g.kvol, num_act_in, n_max, plan.seg, num_index);
+  compact_kernel<<<dim3(nblk, g.kvol), kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in,
+                                                             n_max, nblk, index, plan.row_len);
+  fill_padding_kernel<<<stream_grid(3 * plan.row_len, 256), 256, 0, st>>>(plan.seg, g.kvol, index, plan.row_len);
+  D3D_CHECK_LAUNCH();
+  return D3D_OK;
+}

@@ -1,0 +1,381 @@
+// SPConvMM: sparse convolution feature computation over a rulebook.
+//
+// Replaces spconv::SPConvMMPlugin / spconv::func::indexedSpConv of the reference
+// (trt/spconv/mm_trt.cu:39-206, trt/spconv/mm.h:35-71).  The reference walks the rulebook pair by pair
+// (input-stationary) and scatters with fp16 atomics after a separate bias-initialisation pass.  Here the
+// rulebook is first inverted into an output-stationary neighbour table  nbr[k][o] = input row feeding output o
+// through offset k (or -1); every output row is then produced exactly once: fp32 accumulation over all offsets,
+// bias (+ optional residual and ReLU) in the epilogue, one coalesced store.  Results are deterministic.
+//
+// This file holds the host side (blob parsing, weight upload, C ABI) and the SIMT kernel that serves fp32 and
+// channel counts the tensor-core kernel cannot take; spconv_mm_tc.cu holds the tcgen05/TMEM kernel.
+#include <string.h>
+
+#include <new>
+
+#include "common.cuh"
+#include "spconv_mm_internal.h"
+
+namespace d3d {
+namespace {
+
+// ---------------------------------------------------------------------------------------------
+// Neighbour table
+// ---------------------------------------------------------------------------------------------
+__global__ void table_fill_kernel(int4* table, int64_t n16) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x)
+    table[i] = make_int4(-1, -1, -1, -1);
+}
+
+// index rows: gatherIn | scatterOut | kernelOffset (trt/spconv/index_trt.cu:211-213); `inverse` swaps the
+// first two (trt/spconv/mm_trt.cu:174-177).
+__global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t row_len,
+                                     const int32_t* __restrict__ num_index, int inverse, int kvol, int64_t m_max,
+                                     int32_t* __restrict__ table) {
+  int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  int64_t n = *num_index;
+  n = n > row_len ? row_len : n;
+  if (p >= n) return;
+  int k = __ldg(index + 2 * row_len + p);
+  if (k < 0 || k >= kvol) return;  // padding entry
+  int g = __ldg(index + (inverse ? row_len : 0) + p);
+  int s = __ldg(index + (inverse ? 0 : row_len) + p);
+  if (g < 0 || s < 0 || s >= m_max) return;
+  table[(int64_t)k * m_max + s] = g;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SIMT kernel: tile of 32 outputs per CTA, 256 threads, thread = (row, 8-strided column group).
+// ---------------------------------------------------------------------------------------------
+constexpr int kTileM = 32;
+constexpr int kChunkK = 32;
+constexpr int kSimtThreads = 256;
+
+template <class T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <class T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+template <class T, int CPT>
+__global__ void __launch_bounds__(kSimtThreads)
+spconv_mm_simt_kernel(const T* __restrict__ in_feats, int64_t n_in_max, const T* __restrict__ weight,
+                      const float* __restrict__ bias, const int32_t* __restrict__ table, int64_t m_max,
+                      int64_t pitch, int kvol, int cin, int cout, T* __restrict__ out_feats, int relu, const T* __restrict__ residual) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  float* a_s = reinterpret_cast<float*>(smem_raw);                   // [kTileM][kChunkK + 1]
+  float* w_s = a_s + kTileM * (kChunkK + 1);                         // [kChunkK][cout]
+  int32_t* idx_s = reinterpret_cast<int32_t*>(w_s + kChunkK * cout); // [kvol][kTileM]
+  int32_t* kvalid_s = idx_s + kvol * kTileM;                         // [kvol]
+
+  const int64_t tile0 = (int64_t)blockIdx.x * kTileM;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int r = tid >> 3, cg = tid & 7;
+
+  for (int k = warp; k < kvol; k += kSimtThreads / 32) {
+    int64_t o = tile0 + lane;
+    int v = o < m_max ? __ldg(table + (int64_t)k * pitch + o) : -1;
+    if (v >= n_in_max) v = -1;
+    idx_s[k * kTileM + lane] = v;
+    unsigned any = __ballot_sync(0xffffffffu, v >= 0);
+    if (lane == 0) kvalid_s[k] = any != 0;
+  }
+  __syncthreads();
+
+  float acc[CPT];
+#pragma unroll
+  for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+
+  for (int k = 0; k < kvol; ++k) {
+    if (!kvalid_s[k]) continue;
+    const T* wk = weight + (int64_t)k * cin * cout;
+    for (int c0 = 0; c0 < cin; c0 += kChunkK) {
+      int kc = cin - c0 < kChunkK ? cin - c0 : kChunkK;
+      __syncthreads();
+      for (int e = tid; e < kTileM * kChunkK; e += kSimtThreads) {
+        int rr = e / kChunkK, cc = e % kChunkK;
+        int src = idx_s[k * kTileM + rr];
+        float v = 0.f;
+        if (src >= 0 && cc < kc) v = to_f32(in_feats[(int64_t)src * cin + c0 + cc]);
+        a_s[rr * (kChunkK + 1) + cc] = v;
+      }
+      for (int e = tid; e < kc * cout; e += kSimtThreads) w_s[e] = to_f32(wk[(int64_t)c0 * cout + e]);
+      __syncthreads();
+      for (int cc = 0; cc < kc; ++cc) {
+        float a = a_s[r * (kChunkK + 1) + cc];
+#pragma unroll
+        for (int j = 0; j < CPT; ++j) {
+          int col = cg + 8 * j;
+          if (col < cout) acc[j] = fmaf(a, w_s[cc * cout + col], acc[j]);
+        }
+      }
+    }
+  }
+
+  int64_t o = tile0 + r;
+  if (o < m_max) {
+#pragma unroll
+    for (int j = 0; j < CPT; ++j) {
+      int col = cg + 8 * j;
+      if (col < cout) {
+        float v = acc[j] + bias[col];
+        if (residual) v += to_f32(residual[o * cout + col]);
+        if (relu) v = fmaxf(v, 0.f);
+        out_feats[o * cout + col] = from_f32<T>(v);
+      }
+    }
+  }
+}
+
+template <class T> int launch_simt_typed(const MmLaunch& a) {
+  const d3d_spconv_mm_s* h = a.h;
+  int cout = h->p.out_channels, cin = h->p.in_channels, kvol = h->p.kernel_vol;
+  int64_t m_max = h->p.max_num_act_out;
+  if (m_max == 0) return D3D_OK;
+  size_t smem = sizeof(float) * (kTileM * (kChunkK + 1) + (size_t)kChunkK * cout) +
+                sizeof(int32_t) * ((size_t)kvol * kTileM + kvol);
+  D3D_REQUIRE(smem <= 200 * 1024, D3D_ERR_TOO_LARGE);
+  dim3 grid((unsigned)ceil_div(m_max, kTileM));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(a.stream);
+  int cpt = (cout + 7) / 8;
+#define D3D_SIMT_CASE(N)                                                                                           \
+  {                                                                                                                \
+    auto kern = spconv_mm_simt_kernel<T, N>;                                                                       \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
+    kern<<<grid, kSimtThreads, smem, st>>>(reinterpret_cast<const T*>(a.in_feats), a.max_num_act_in,               \
+                                           reinterpret_cast<const T*>(h->w_dev), h->b_dev, a.table, m_max,          \
+                                           (m_max + 127) / 128 * 128, kvol, cin, cout, reinterpret_cast<T*>(a.out_feats), a.relu,                    \
+                                           reinterpret_cast<const T*>(a.residual));                                \
+  }
+  if (cpt <= 2) D3D_SIMT_CASE(2)
+  else if (cpt <= 4) D3D_SIMT_CASE(4)
+  else if (cpt <= 8) D3D_SIMT_CASE(8)
+  else if (cpt <= 16) D3D_SIMT_CASE(16)
+  else if (cpt <= 32) D3D_SIMT_CASE(32)
+  else return D3D_ERR_TOO_LARGE;
+#undef D3D_SIMT_CASE
+  D3D_CHECK_LAUNCH();
+  return D3D_OK;
+}
+
+}  // namespace
+
+int launch_spconv_mm_simt(const MmLaunch& a) {
+  switch (a.dtype) {
+    case D3D_FLOAT: return launch_simt_typed<float>(a);
+    case D3D_HALF: return launch_simt_typed<__half>(a);
+    case D3D_BF16: return launch_simt_typed<__nv_bfloat16>(a);
+    default: return D3D_ERR_UNSUPPORTED_DTYPE;
+  }
+}
+
+}  // namespace d3d
+
+using namespace d3d;
+
+// ---------------------------------------------------------------------------------------------
+// C ABI
+// ---------------------------------------------------------------------------------------------
+extern "C" int d3d_spconv_mm_create(const void* data_s, size_t len, d3d_spconv_mm_t* handle) {
+  D3D_REQUIRE(data_s && handle, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(len >= 19, D3D_ERR_BAD_BLOB);
+  const uint8_t* b = reinterpret_cast<const uint8_t*>(data_s);
+  d3d_spconv_mm_params p;
+  memcpy(&p.kernel_vol, b + 0, 4);
+  memcpy(&p.in_channels, b + 4, 4);
+  memcpy(&p.out_channels, b + 8, 4);
+  memcpy(&p.max_num_act_out, b + 12, 4);
+  p.subm = b[16] != 0;
+  p.inverse = b[17] != 0;
+  p.with_bias = b[18] != 0;
+  D3D_REQUIRE(p.kernel_vol >= 1 && p.in_channels >= 1 && p.out_channels >= 1 && p.max_num_act_out >= 0,
+              D3D_ERR_BAD_BLOB);
+  size_t nw = (size_t)p.kernel_vol * p.in_channels * p.out_channels;
+  size_t need = nw + (p.with_bias ? (size_t)p.out_channels : 0);
+  D3D_REQUIRE((len - 19) / 4 >= need, D3D_ERR_BAD_BLOB);
+  d3d_spconv_mm_s* h = new (std::nothrow) d3d_spconv_mm_s();
+  D3D_REQUIRE(h, D3D_ERR_INVALID_ARGUMENT);
+  h->p = p;
+  h->wb.resize((len - 19) / 4);  // keeps trailing floats for a faithful serialize() (mm_trt.cu:61-74)
+  memcpy(h->wb.data(), b + 19, h->wb.size() * 4);
+  *handle = h;
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_mm_get_params(d3d_spconv_mm_t h, d3d_spconv_mm_params* p) {
+  D3D_REQUIRE(h && p, D3D_ERR_INVALID_ARGUMENT);
+  *p = h->p;
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_mm_serialize(d3d_spconv_mm_t h, void* buffer, size_t* len) {
+  D3D_REQUIRE(h && len, D3D_ERR_INVALID_ARGUMENT);
+  size_t need = 19 + h->wb.size() * 4;
+  if (buffer) {
+    D3D_REQUIRE(*len >= need, D3D_ERR_INVALID_ARGUMENT);
+    uint8_t* b = reinterpret_cast<uint8_t*>(buffer);
+    memcpy(b + 0, &h->p.kernel_vol, 4);
+    memcpy(b + 4, &h->p.in_channels, 4);
+    memcpy(b + 8, &h->p.out_channels, 4);
+    memcpy(b + 12, &h->p.max_num_act_out, 4);
+    b[16] = h->p.subm != 0, b[17] = h->p.inverse != 0, b[18] = h->p.with_bias != 0;
+    memcpy(b + 19, h->wb.data(), h->wb.size() * 4);
+  }
+  *len = need;
+  return D3D_OK;
+}
+
+static void release_device(d3d_spconv_mm_s* h) {
+  spconv_mm_tc_release(h);
+  if (h->w_dev) cudaFree(h->w_dev);
+  if (h->wt_dev) cudaFree(h->wt_dev);
+  if (h->b_dev) cudaFree(h->b_dev);
+  h->w_dev = h->wt_dev = nullptr;
+  h->b_dev = nullptr;
+  h->dtype = -1;
+}
+
+template <class T, class Cvt> static int upload_weights(d3d_spconv_mm_s* h, Cvt cvt) {
+  const int kvol = h->p.kernel_vol, cin = h->p.in_channels, cout = h->p.out_channels;
+  size_t nw = (size_t)kvol * cin * cout;
+  std::vector<T> w(nw), wt(nw);
+  for (size_t i = 0; i < nw; ++i) w[i] = cvt(h->wb[i]);
+  for (int k = 0; k < kvol; ++k)
+    for (int ci = 0; ci < cin; ++ci)
+      for (int co = 0; co < cout; ++co)
+        wt[((size_t)k * cout + co) * cin + ci] = w[((size_t)k * cin + ci) * cout + co];
+  if (cudaMalloc(&h->w_dev, nw * sizeof(T)) != cudaSuccess) return D3D_ERR_CUDA;
+  if (cudaMalloc(&h->wt_dev, nw * sizeof(T)) != cudaSuccess) return D3D_ERR_CUDA;
+  if (cudaMemcpy(h->w_dev, w.data(), nw * sizeof(T), cudaMemcpyHostToDevice) != cudaSuccess) return D3D_ERR_CUDA;
+  if (cudaMemcpy(h->wt_dev, wt.data(), nw * sizeof(T), cudaMemcpyHostToDevice) != cudaSuccess) return D3D_ERR_CUDA;
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_mm_configure(d3d_spconv_mm_t h, int dtype) {
+  D3D_REQUIRE(h, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(dtype == D3D_FLOAT || dtype == D3D_HALF || dtype == D3D_BF16, D3D_ERR_UNSUPPORTED_DTYPE);
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return D3D_ERR_CUDA;
+  if (h->dtype == dtype && h->device == dev) return D3D_OK;
+  release_device(h);
+  int rc;
+  if (dtype == D3D_FLOAT) rc = upload_weights<float>(h, [](float v) { return v; });
+  else if (dtype == D3D_HALF) rc = upload_weights<__half>(h, [](float v) { return __float2half_rn(v); });
+  else rc = upload_weights<__nv_bfloat16>(h, [](float v) { return __float2bfloat16_rn(v); });
+  if (rc != D3D_OK) {
+    release_device(h);
+    return rc;
+  }
+  // Bias is applied in fp32 after rounding it to the compute dtype, matching the half-precision upload of the
+  // reference (mm_trt.cu:131-139).
+  const int cout = h->p.out_channels;
+  std::vector<float> bias(cout, 0.f);
+  if (h->p.with_bias) {
+    const float* src = h->wb.data() + (size_t)h->p.kernel_vol * h->p.in_channels * cout;
+    for (int c = 0; c < cout; ++c) {
+      float v = src[c];
+      if (dtype == D3D_HALF) v = __half2float(__float2half_rn(v));
+      if (dtype == D3D_BF16) v = __bfloat162float(__float2bfloat16_rn(v));
+      bias[c] = v;
+    }
+  }
+  if (cudaMalloc(&h->b_dev, cout * sizeof(float)) != cudaSuccess ||
+      cudaMemcpy(h->b_dev, bias.data(), cout * sizeof(float), cudaMemcpyHostToDevice) != cudaSuccess) {
+    release_device(h);
+    return D3D_ERR_CUDA;
+  }
+  h->dtype = dtype;
+  h->device = dev;
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_mm_destroy(d3d_spconv_mm_t h) {
+  if (!h) return D3D_OK;
+  release_device(h);
+  delete h;
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t h, int which) {
+  D3D_REQUIRE(h && which >= 0 && which <= 2, D3D_ERR_INVALID_ARGUMENT);
+  h->kernel_choice = which;
+  return D3D_OK;
+}
+
+extern "C" size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out) {
+  // rows are padded to a multiple of 128 entries so every 128-output tile can be read as a whole
+  int64_t pitch = (max_num_act_out + 127) / 128 * 128;
+  return align_up((size_t)kernel_vol * (size_t)pitch * sizeof(int32_t), 256);
+}
+
+extern "C" int d3d_spconv_mm_workspace(d3d_spconv_mm_t h, const d3d_tensor_desc* in, int n_in, size_t* bytes) {
+  D3D_REQUIRE(h && bytes, D3D_ERR_INVALID_ARGUMENT);
+  (void)in, (void)n_in;
+  *bytes = d3d_spconv_mm_table_bytes(h->p.kernel_vol, h->p.max_num_act_out);
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_num_act_out, const int32_t* index,
+                                     int64_t index_row_len, const int32_t* num_index, void* table, void* stream) {
+  D3D_REQUIRE(kernel_vol >= 1 && max_num_act_out >= 0 && index_row_len >= 0, D3D_ERR_INVALID_ARGUMENT);
+  if (max_num_act_out == 0) return D3D_OK;
+  D3D_REQUIRE(index && num_index && table, D3D_ERR_INVALID_ARGUMENT);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int64_t pitch = (max_num_act_out + 127) / 128 * 128;
+  int64_t n16 = (int64_t)kernel_vol * pitch / 4;
+  table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16);
+  if (index_row_len > 0)
+    table_scatter_kernel<<<(unsigned)ceil_div(index_row_len, 256), 256, 0, st>>>(
+        index, index_row_len, num_index, inverse, kernel_vol, pitch, reinterpret_cast<int32_t*>(table));
+  D3D_CHECK_LAUNCH();
+  return D3D_OK;
+}
+
+extern "C" int d3d_spconv_mm_run(d3d_spconv_mm_t h, int dtype, const void* in_feats, int64_t max_num_act_in,
+                                 const int32_t* num_act_out, const void* table, void* out_feats,
+                                 const d3d_spconv_mm_epilogue* epilogue, void* stream) {
+  D3D_REQUIRE(h, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(dtype == D3D_FLOAT || dtype == D3D_HALF || dtype == D3D_BF16, D3D_ERR_UNSUPPORTED_DTYPE);
+  D3D_REQUIRE(h->dtype == dtype, D3D_ERR_INVALID_ARGUMENT);  // configure() must have run for this dtype
+  if (h->p.max_num_act_out == 0) return D3D_OK;
+  D3D_REQUIRE(in_feats && table && out_feats, D3D_ERR_INVALID_ARGUMENT);
+  MmLaunch a;
+  a.h = h, a.dtype = dtype, a.in_feats = in_feats, a.max_num_act_in = max_num_act_in, a.num_act_out = num_act_out;
+  a.table = reinterpret_cast<const int32_t*>(table), a.out_feats = out_feats;
+  a.relu = epilogue ? epilogue->relu : 0;
+  a.residual = epilogue ? epilogue->residual : nullptr;
+  a.stream = stream;
+  bool tc_ok = spconv_mm_tc_eligible(h, dtype);
+  if (h->kernel_choice == 2) {
+    D3D_REQUIRE(tc_ok, D3D_ERR_INVALID_ARGUMENT);
+    return launch_spconv_mm_tc(a);
+  }
+  if (h->kernel_choice == 0 && tc_ok) return launch_spconv_mm_tc(a);
+  return launch_spconv_mm_simt(a);
+}
+
+extern "C" int d3d_spconv_mm_enqueue(d3d_spconv_mm_t h, const d3d_tensor_desc* in, int n_in,
+                                     const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                                     void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  D3D_REQUIRE(h && in && out && inputs && outputs && n_in >= 5 && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
+  int dtype = in[0].dtype;
+  D3D_REQUIRE(dtype == D3D_FLOAT || dtype == D3D_HALF || dtype == D3D_BF16, D3D_ERR_UNSUPPORTED_DTYPE);
+  D3D_REQUIRE(out[0].dtype == dtype, D3D_ERR_UNSUPPORTED_DTYPE);
+  D3D_REQUIRE(in[0].nb_dims == 2 && in[0].dims[1] == h->p.in_channels, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(in[3].nb_dims == 2 && in[3].dims[0] == 3, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(out[0].nb_dims == 2 && out[0].dims[0] == h->p.max_num_act_out && out[0].dims[1] == h->p.out_channels,
+              D3D_ERR_INVALID_ARGUMENT);
+  size_t need = d3d_spconv_mm_table_bytes(h->p.kernel_vol, h->p.max_num_act_out);
+  D3D_REQUIRE(h->p.max_num_act_out == 0 || (workspace && workspace_bytes >= need), D3D_ERR_WORKSPACE_TOO_SMALL);
+  int rc = d3d_spconv_mm_configure(h, dtype);  // no-op when already configured for this dtype
+  if (rc != D3D_OK) return rc;
+  rc = d3d_spconv_mm_prepare(h->p.kernel_vol, h->p.inverse, h->p.max_num_act_out,
+                             reinterpret_cast<const int32_t*>(inputs[3]), in[3].dims[1],
+                             reinterpret_cast<const int32_t*>(inputs[4]), workspace, stream);
+  if (rc != D3D_OK) return rc;
+  return d3d_spconv_mm_run(h, dtype, inputs[0], in[0].dims[0], reinterpret_cast<const int32_t*>(inputs[2]),
+                           workspace, outputs[0], nullptr, stream);
+}

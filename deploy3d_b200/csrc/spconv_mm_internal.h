@@ -1,0 +1,43 @@
+// Internal contract between the SPConvMM host code (spconv_mm.cu) and its two kernels:
+// the SIMT fp32-FMA kernel (any dtype, any channel count) and the tcgen05/TMEM kernel
+// (fp16 / bf16, channel counts that are multiples of 16).
+#pragma once
+#include <stdint.h>
+#include <vector>
+
+#include "../../include/deploy3d_b200.h"
+
+struct d3d_spconv_mm_s {
+  d3d_spconv_mm_params p;
+  std::vector<float> wb;     // host copy: weights [kVol][Cin][Cout] then bias [Cout] (as in the data_s blob)
+  int dtype = -1;            // dtype of the device copy, -1 before configure
+  int device = -1;
+  void* w_dev = nullptr;     // [kVol][Cin][Cout] in `dtype` (reference layout; SIMT kernel)
+  void* wt_dev = nullptr;    // [kVol][Cout][Cin] in `dtype` (K-major B operand of the tcgen05 kernel)
+  float* b_dev = nullptr;    // bias in fp32 (zeros when the blob has no bias)
+  int kernel_choice = 0;     // 0 auto, 1 SIMT, 2 tcgen05
+  void* tc_state = nullptr;  // tensor maps of the tcgen05 path (owned by spconv_mm_tc.cu)
+};
+
+namespace d3d {
+
+struct MmLaunch {
+  const d3d_spconv_mm_s* h;
+  int dtype;
+  const void* in_feats;
+  int64_t max_num_act_in;
+  const int32_t* num_act_out;
+  const int32_t* table;  // [kVol][pitch] input row per (offset, output), -1 = none; pitch = max_num_act_out rounded up to 128
+  void* out_feats;
+  int relu;
+  const void* residual;
+  void* stream;
+};
+
+int launch_spconv_mm_simt(const MmLaunch& a);
+// Returns D3D_ERR_INVALID_ARGUMENT when the shape/dtype is not eligible for the tensor-core path.
+bool spconv_mm_tc_eligible(const d3d_spconv_mm_s* h, int dtype);
+int launch_spconv_mm_tc(const MmLaunch& a);
+void spconv_mm_tc_release(d3d_spconv_mm_s* h);
+
+}  // namespace d3d

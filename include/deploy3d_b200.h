@@ -1,0 +1,264 @@
+/*
+ * deploy3d_b200 -- C ABI of the B200-native sparse-convolution hot path.
+ *
+ * Every entry point is what a TensorRT plugin shell (IPluginV2DynamicExt) of the reference
+ * project would bind for the corresponding plugin: <op>_parse  <-> the deserialising
+ * constructor, <op>_workspace <-> getWorkspaceSize, <op>_enqueue <-> enqueue.  Tensors are
+ * plain device pointers described by d3d_tensor_desc (dtype + dims, dense row-major), in the
+ * same order and with the same shapes the reference plugins use.  Citations are
+ * file:line inside the reference project (zhanggefan/deploy3d).
+ *
+ * Conventions
+ *   - all functions return D3D_OK (0) or a negative d3d_status;
+ *   - no entry point synchronises the stream or reads device memory on the host;
+ *     voxel counts stay on the device (the reference blocks on a D2H copy,
+ *     trt/spconv/index_trt.cu:207-209, trt/spconv/bev_densify_trt.cu:152-155);
+ *   - `stream` is a cudaStream_t passed as void*;
+ *   - spatial shapes travel as the dims of zero-element tensors [B, 0, D0, D1, ...]
+ *     exactly as in the reference (trt/spconv/index_trt.cu:216-226).
+ */
+#ifndef DEPLOY3D_B200_H_
+#define DEPLOY3D_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define D3D_MAX_DIMS 8
+#define D3D_MAX_NDIM 4 /* SPConvIdx1d..4d, trt/spconv/index_trt.cu:279-290 */
+
+typedef enum {
+  D3D_OK = 0,
+  D3D_ERR_INVALID_ARGUMENT = -1,
+  D3D_ERR_UNSUPPORTED_DTYPE = -2, /* enqueue of the reference returns -1 (trt/spconv/mm_trt.cu:204) */
+  D3D_ERR_WORKSPACE_TOO_SMALL = -3,
+  D3D_ERR_CUDA = -4,
+  D3D_ERR_BAD_BLOB = -5, /* truncated data_s; the reference only prints (trt/include/common/refnd.h:279-283) */
+  D3D_ERR_TOO_LARGE = -6
+} d3d_status;
+
+/* Values follow nvinfer1::DataType so a plugin shell can pass PluginTensorDesc::type through. */
+typedef enum {
+  D3D_FLOAT = 0,
+  D3D_HALF = 1,
+  D3D_INT8 = 2,
+  D3D_INT32 = 3,
+  D3D_BOOL = 4,
+  D3D_BF16 = 7
+} d3d_dtype;
+
+/* Mirror of the fields of nvinfer1::PluginTensorDesc the reference reads (format is always kLINEAR). */
+typedef struct {
+  int32_t dtype;
+  int32_t nb_dims;
+  int64_t dims[D3D_MAX_DIMS];
+} d3d_tensor_desc;
+
+const char* d3d_version(void);
+const char* d3d_status_string(int status);
+
+/* ---------------------------------------------------------------------------------------------
+ * SPConvIdx{1,2,3,4}d -- rulebook generation.
+ * Replaces spconv::SPConvIdxPlugin<NDim> (trt/spconv/index_trt.cu:52-249) and
+ * spconv::func::createSparse{SubM,Conv}Index (trt/spconv/index.cu:253-476).
+ * data_s layout (trt/spconv/index_trt.cu:39-50, written by deploy3d/symfun/ops/spconv/spconv_index.py:94-101):
+ *   int32 kernelSize[NDim], stride[NDim], padding[NDim], dilation[NDim], outPadding[NDim];
+ *   int32 maxNumActOut; bool subM; bool transpose      (packed, 66 bytes for NDim = 3)
+ * Inputs : 0 inCoors int32 [maxNumActIn, NDim+1] (b, d0, ...), 1 numActIn int32 [1],
+ *          2 inSpatialShape [B, 0, D0, ...] (shape only)
+ * Outputs: 0 index int32 [3, kVol*(maxNumActIn+128)] rows gatherIn | scatterOut | kernelOffset,
+ *          1 numIndex int32 [1]; when !subM also 2 outCoors int32 [maxNumActOut, NDim+1],
+ *          3 numActOut int32 [1], 4 outSpatialShape [B, 0, D0', ...] (shape only).
+ * Layout of `index` is bit-identical to the reference: segments of ascending kernel offset, each
+ * starting at a multiple of 128, ascending input index inside, every other entry -1.
+ * Output voxels of a strided/transposed rulebook are numbered by first touch (smallest
+ * inputIndex*kVol + kernelOffset that produces them); the reference's order is hash-slot order.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t ndim;
+  int32_t kernel_size[D3D_MAX_NDIM];
+  int32_t stride[D3D_MAX_NDIM];
+  int32_t padding[D3D_MAX_NDIM];
+  int32_t dilation[D3D_MAX_NDIM];
+  int32_t out_padding[D3D_MAX_NDIM];
+  int32_t max_num_act_out;
+  int32_t subm;
+  int32_t transpose;
+} d3d_spconv_index_params;
+
+int d3d_spconv_index_parse(int ndim, const void* data_s, size_t len, d3d_spconv_index_params* p);
+/* getNbOutputs (index_trt.cu:97-100) */
+int d3d_spconv_index_num_outputs(const d3d_spconv_index_params* p);
+/* getOutputDimensions (index_trt.cu:101-152) with concrete dims */
+int d3d_spconv_index_output_desc(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
+                                 int out_index, d3d_tensor_desc* out);
+/* getWorkspaceSize (index_trt.cu:174-187) */
+int d3d_spconv_index_workspace(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
+                               size_t* bytes);
+/* enqueue (index_trt.cu:188-248) */
+int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
+                             const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                             void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * SPConvMM -- gather / GEMM / scatter over the rulebook.
+ * Replaces spconv::SPConvMMPlugin (trt/spconv/mm_trt.cu:39-206) and
+ * spconv::func::indexedSpConv (trt/spconv/mm.h:35-71).
+ * data_s layout (mm_trt.cu:27-37, deploy3d/symfun/ops/spconv/spconv_mm.py:54-63):
+ *   int32 kernelVol, inChannels, outChannels, maxNumActOut; bool subM, inverse, withBias;
+ *   float weight[kernelVol][inChannels][outChannels]; float bias[outChannels] (if withBias)
+ * Inputs : 0 inFeats [maxNumActIn, Cin] half | bf16 | float, 1 numActIn int32[1], 2 numActOut int32[1],
+ *          3 index int32 [3, L], 4 numIndex int32[1]
+ * Output : 0 outFeats [maxNumActOut, Cout], same dtype as inFeats.
+ * The handle owns the host copy of the weights (the plugin object of the reference) and, after
+ * d3d_spconv_mm_configure, their device copy in the compute dtype (configurePlugin, mm_trt.cu:127-142).
+ * Accumulation is fp32 for every dtype (the reference accumulates in fp16, mm/config_tensorop.h:77).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct d3d_spconv_mm_s* d3d_spconv_mm_t;
+
+typedef struct {
+  int32_t kernel_vol;
+  int32_t in_channels;
+  int32_t out_channels;
+  int32_t max_num_act_out;
+  int32_t subm; /* deprecated in the reference, kept for the round trip */
+  int32_t inverse;
+  int32_t with_bias;
+} d3d_spconv_mm_params;
+
+/* Epilogue fused after bias; all zero == the reference plugin (activation is a separate graph op there,
+ * tests/cylinder/test_cylinder3d.py:91-92). `residual` (same dtype/shape as outFeats) is added before ReLU. */
+typedef struct {
+  int32_t relu;
+  const void* residual;
+} d3d_spconv_mm_epilogue;
+
+int d3d_spconv_mm_create(const void* data_s, size_t len, d3d_spconv_mm_t* handle);
+int d3d_spconv_mm_get_params(d3d_spconv_mm_t handle, d3d_spconv_mm_params* p);
+/* serialize (mm_trt.cu:71-74): writes the blob back; *len receives the size (buffer may be NULL). */
+int d3d_spconv_mm_serialize(d3d_spconv_mm_t handle, void* buffer, size_t* len);
+/* configurePlugin: convert weights to `dtype` and upload them to the current device (allocates). */
+int d3d_spconv_mm_configure(d3d_spconv_mm_t handle, int dtype);
+int d3d_spconv_mm_destroy(d3d_spconv_mm_t handle);
+/* The reference needs no workspace (mm_trt.cu:143-148); this implementation keeps an
+ * output-stationary neighbour table [kVol, maxNumActOut] there. */
+int d3d_spconv_mm_workspace(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int n_in, size_t* bytes);
+/* enqueue (mm_trt.cu:149-205) == prepare + run below with the table in `workspace`. */
+int d3d_spconv_mm_enqueue(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int n_in,
+                          const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                          void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+/* Two-step form for callers that run several SPConvMM layers over one rulebook (the reference
+ * shares rulebooks through an indice_key dictionary, tests/cylinder/test_cylinder3d.py:52-75):
+ * prepare builds the neighbour table once, run consumes it.  `table` must hold
+ * d3d_spconv_mm_table_bytes(kVol, maxNumActOut) bytes. */
+size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out);
+int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_num_act_out, const int32_t* index,
+                          int64_t index_row_len, const int32_t* num_index, void* table, void* stream);
+int d3d_spconv_mm_run(d3d_spconv_mm_t handle, int dtype, const void* in_feats, int64_t max_num_act_in,
+                      const int32_t* num_act_out, const void* table, void* out_feats,
+                      const d3d_spconv_mm_epilogue* epilogue, void* stream);
+/* Kernel choice for tests and profiling: 0 = automatic, 1 = SIMT fp32-FMA path, 2 = tcgen05 path
+ * (fails with D3D_ERR_INVALID_ARGUMENT at run time when the shape is not eligible). */
+int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t handle, int which);
+
+/* ---------------------------------------------------------------------------------------------
+ * BEVDensify.  Replaces spconv::BEVDensifyPlugin (trt/spconv/bev_densify_trt.cu:52-178).
+ * data_s: int32 outChannels (= Cin * Z).
+ * Inputs : 0 inFeats [maxNumActIn, C] float | half | bf16, 1 inCoors int32 [maxNumActIn, 4] (b,z,y,x),
+ *          2 numActIn int32[1], 3 inSpatialShape [B, 0, Z, Y, X]
+ * Output : 0 outFeatMaps [B, C*Z, Y, X]
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t out_channels;
+} d3d_bev_densify_params;
+int d3d_bev_densify_parse(const void* data_s, size_t len, d3d_bev_densify_params* p);
+int d3d_bev_densify_workspace(const d3d_bev_densify_params* p, const d3d_tensor_desc* in, int n_in, size_t* bytes);
+int d3d_bev_densify_enqueue(const d3d_bev_densify_params* p, const d3d_tensor_desc* in, int n_in,
+                            const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                            void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * SimpleMeanEncoder.  Replaces voxel_encoder::SimpleMeanEncoderPlugin
+ * (trt/voxel_encoder/simple_mean_trt.cu:121-168, :181-314).  data_s: int32 maxNumActOut.
+ * Inputs : 0 batchPointFeats float [N, C], 1 batchIndices int32 [N] (<0: ignore point),
+ *          2 voxelConfig float [6] = (xmin,ymin,zmin,dx,dy,dz), 3 inSpatialShape [B, 0, Z, Y, X]
+ * Outputs: 0 outFeats float [maxNumActOut, C], 1 outCoors int32 [maxNumActOut, 4] (b,z,y,x), 2 numActOut int32[1]
+ * Voxels are numbered by first touch (smallest point index); the reference uses hash-slot order.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t max_num_act_out;
+} d3d_voxel_encoder_params;
+int d3d_simple_mean_encoder_parse(const void* data_s, size_t len, d3d_voxel_encoder_params* p);
+int d3d_simple_mean_encoder_workspace(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
+                                      size_t* bytes);
+int d3d_simple_mean_encoder_enqueue(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
+                                    const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                                    void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * CylinderEncoder.  Replaces voxel_encoder::CylinderEncoderPlugin
+ * (trt/voxel_encoder/cylinder_trt.cu:130-174, :187-333).  data_s: int32 maxNumActOut.
+ * Inputs : 0 batchPointFeats float [N, C], 1 batchIndices int32 [N],
+ *          2 cylinderConfig float [6] = (zmin,phimin,rhomin,zmax,phimax,rhomax), 3 inSpatialShape [B, 0, RHO, PHI, Z]
+ * Outputs: 0 outFeats float [N, C+5], 1 scatterTo int32 [N], 2 scatterCount int32 [maxNumActOut],
+ *          3 outCoors int32 [maxNumActOut, 4] (b,rho,phi,z), 4 numActOut int32[1]
+ * ------------------------------------------------------------------------------------------- */
+int d3d_cylinder_encoder_parse(const void* data_s, size_t len, d3d_voxel_encoder_params* p);
+int d3d_cylinder_encoder_workspace(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
+                                   size_t* bytes);
+int d3d_cylinder_encoder_enqueue(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
+                                 const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                                 void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * ScatterTo / GatherBack.  Replace point_voxel_mapping::ScatterToPlugin
+ * (trt/point_voxel_mapping/scatter_to.cu:83-103, :120-214) and GatherBackPlugin
+ * (trt/point_voxel_mapping/gather_back.cu:51-62, :77-184).  Both honour `stream`
+ * (the reference launches them on the default stream, scatter_to.cu:212, gather_back.cu:173).
+ * ScatterTo  data_s: int8 reduceType (0 max, otherwise mean).
+ *   Inputs : 0 batchPointFeats float [N, C], 1 scatterTo int32 [N], 2 scatterCount int32 [M]
+ *   Output : 0 reducedFeats float [M, C]
+ * GatherBack data_s: bool fill; float fillVal.
+ *   Inputs : 0 reducedFeats float [M, ...], 1 scatterTo int32 [N]
+ *   Output : 0 batchPointFeats float [N, ...]
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t reduce_type;
+} d3d_scatter_to_params;
+typedef struct {
+  int32_t fill;
+  float fill_val;
+} d3d_gather_back_params;
+int d3d_scatter_to_parse(const void* data_s, size_t len, d3d_scatter_to_params* p);
+int d3d_scatter_to_enqueue(const d3d_scatter_to_params* p, const d3d_tensor_desc* in, int n_in,
+                           const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                           void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+int d3d_gather_back_parse(const void* data_s, size_t len, d3d_gather_back_params* p);
+int d3d_gather_back_enqueue(const d3d_gather_back_params* p, const d3d_tensor_desc* in, int n_in,
+                            const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                            void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * NMS3d -- rotated-BEV non-maximum suppression.  Replaces decoder::NMS3dPlugin
+ * (trt/decoder/nms3d.cu:58-127, :135-236).  The reference has no data_s and hard-codes the
+ * IoU threshold 0.1 (nms3d.cu:138); a plugin shell passes iou_threshold = 0.1f.
+ * Inputs : 0 inScores float [B, K] sorted descending per row, 1 boxes float [B, K, 7+a] (cx,cy,cz,dx,dy,dz,yaw,..)
+ * Output : 0 outScores float [B, K], suppressed entries set to -1.
+ * Workspace: B*K*ceil(K/64) 64-bit mask words (same as the reference, nms3d.cu:195-199).
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  float iou_threshold;
+} d3d_nms3d_params;
+int d3d_nms3d_parse(const void* data_s, size_t len, d3d_nms3d_params* p);
+int d3d_nms3d_workspace(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in, size_t* bytes);
+int d3d_nms3d_enqueue(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in, const d3d_tensor_desc* out,
+                      int n_out, const void* const* inputs, void* const* outputs, void* workspace,
+                      size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEPLOY3D_B200_H_ */
