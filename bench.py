@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the sparse-convolution hot path: CenterPoint-shaped frames per second.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W]            this implementation (one process per GPU)
+    python bench.py --impl reference [--steps K] [--warmup W]      the CPU restatement of the reference on host cores
+
+One step = one frame of BASELINE config 4 (300 000 points x 5 channels -> mean voxel encoder -> VoxelResBackBone8x
+16/32/64/128 in fp16 -> BEV densify, plus rotated-BEV NMS over 10 x 1000 boxes at IoU 0.2) on synthetic, seeded
+data.  Prints ONE JSON line (rank 0).  `value` is measured with the inputs resident in HBM (CUDA-graph replay,
+CUDA events); `e2e` drives the same frames from pinned host memory through the public pipeline object, with the
+H2D copy of every frame's inputs and the D2H read of its results inside the timed region.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "sparse backbone frames/s (CenterPoint-shaped frame, fp16)"
+UNIT = "frames/s"
+WORKLOAD = "config4: 300000 pts x5 -> mean VFE -> VoxelResBackBone8x 16/32/64/128 fp16 -> BEVDensify + NMS3d 10x1000 @0.2"
+N_ROTATE = 4  # distinct synthetic frames cycled through the input buffers
+CPU_FRACTION = 1.0 / 16  # share of one frame (an azimuth sector) the CPU arm processes per thread and step
+CPU_DENOM = 16
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured (MEASURED_PEAKS.json)")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback (earlier measurement on this pool)")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.FIELDS,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx = float(parts[1])
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle restatement on host cores
+# ------------------------------------------------------------------------------------------------------------------
+def sector_sample(frame, fraction, which=0):
+    """Points of an azimuth sector holding `fraction` of the frame: keeps local density and neighbourhoods intact,
+    so the work per point matches the full frame."""
+    pts = frame["points"]
+    az = np.arctan2(pts[:, 1], pts[:, 0])
+    edges = np.quantile(az, np.linspace(0, 1, int(round(1 / fraction)) + 1))
+    lo, hi = edges[which % (len(edges) - 1)], edges[which % (len(edges) - 1) + 1]
+    m = (az >= lo) & (az < hi)
+    return pts[m], frame["batch"][m]
+
+
+def cpu_frames_per_second(threads, fraction, steps, warmup):
+    """Runs `threads` sector samples concurrently per step; returns (frames/s, seconds per step)."""
+    from concurrent.futures import ThreadPoolExecutor
+    from deploy3d_b200 import synth
+    from oracle import pipeline_cpu
+    frame = synth.config4_points()
+    boxes = synth.config4_boxes()
+    nbox = max(1, int(round(10 * fraction)))  # the NMS rows are independent: take the same fraction of them
+    sub_boxes = dict(scores=boxes["scores"][:nbox], boxes=boxes["boxes"][:nbox])
+    samples = [sector_sample(frame, fraction, i) for i in range(threads)]
+
+    def one(i):
+        p, b = samples[i]
+        pipeline_cpu.run_frame("centerpoint", p, b, frame["voxel_config"], frame["spatial_shape"], sub_boxes, 0.2)
+
+    def step():
+        with ThreadPoolExecutor(max_workers=threads) as ex:
+            list(ex.map(one, range(threads)))
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return threads * fraction / dt, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = len(os.sched_getaffinity(0))
+    fraction = CPU_FRACTION
+    # keep the whole run within a few minutes whatever K and W are: one step of a 1/16 sector costs some 15 s
+    # of single-core work per thread, so clamp the number of timed steps the arm actually executes
+    steps = max(1, min(args.steps, 3))
+    warmup = 1 if args.warmup > 0 else 0
+    fps, dt = cpu_frames_per_second(cores, fraction, steps, warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": fps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32 accumulate over fp16-rounded operands", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": "1/%d azimuth sector of the frame per thread" % CPU_DENOM},
+        "cpu_baseline": {"value": fps, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "%d threads x (1/%d azimuth sector of one config-4 frame, 1 of the 10 NMS rows) "
+                                   "per step, frames/s = threads/%d/t; requested steps %d clamped to %d"
+                                   % (cores, CPU_DENOM, CPU_DENOM, args.steps, steps)},
+        "e2e": {"value": fps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ------------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ------------------------------------------------------------------------------------------------------------------
+def conv_launch_times(pipe, frames, reps):
+    """CUDA-event duration of every SPConvMM launch of a frame (eager replay of the layer list), averaged over
+    `reps` frames.  Returns per-layer dicts with dense-equivalent and pair FLOPs."""
+    import torch
+    from deploy3d_b200.plugins import SPConvMMPlugin
+    net = pipe.net
+    n_layers = len(net.layers)
+    acc = np.zeros(n_layers)
+    work = None
+    for r in range(reps):
+        pipe.load_frame(frames[r % len(frames)])
+        pipe.enqueue()
+        torch.cuda.synchronize()
+        if work is None:
+            work = net.layer_work()
+        saved, x = {}, pipe.vox_feats_lp
+        for li, (L, (plug, out_buf, out_set)) in enumerate(zip(net.layers, net.mm)):
+            if L.source is not None:
+                x = saved[L.source]
+            rb = net.rulebooks[L.key]
+            table = rb.table_inv if L.kind == "inverse" else rb.table_fwd
+            res = saved[L.residual] if L.residual else None
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            x = plug.run(x, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu, residual=res)
+            e1.record()
+            e1.synchronize()
+            acc[li] += e0.elapsed_time(e1) * 1e-3
+            if L.save:
+                saved[L.save] = x
+    out = []
+    for li, (cin, cout, kvol, m, pairs) in enumerate(work):
+        t = acc[li] / reps
+        esz = 2
+        out.append(dict(layer=li, cin=cin, cout=cout, kvol=kvol, m=m, pairs=pairs, seconds=t,
+                        flops_dense=2.0 * m * kvol * cin * cout, flops_pair=2.0 * pairs * cin * cout,
+                        bytes=m * cin * esz + m * cout * esz + kvol * cin * cout * esz + 4.0 * kvol * m))
+    return out
+
+
+def run_ours(args):
+    import torch
+    from deploy3d_b200 import _lib, synth
+    from deploy3d_b200.pipeline import DetectionPipeline
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus != world:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus %d needs one process per GPU: launch with python -m torch.distributed.run "
+                             "--nproc-per-node %d bench.py --gpus %d ..." % (args.gpus, args.gpus, args.gpus))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    _lib.lib()  # fails loudly when the CUDA library is missing
+    torch.cuda.set_device(local)
+    dev = "cuda:%d" % local
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device(dev))
+
+    frames = [synth.config4_points(i) for i in range(N_ROTATE)]
+    boxes = synth.config4_boxes()
+    probe = DetectionPipeline("centerpoint", dev, kernel=args.kernel)
+    probe.load_frame(frames[0], boxes)
+    caps = probe.calibrate(frames)
+    del probe
+    torch.cuda.empty_cache()
+    pipe = DetectionPipeline("centerpoint", dev, caps=caps, kernel=args.kernel)
+    pipe.load_frame(frames[0], boxes)
+    pipe.capture()
+    torch.cuda.synchronize()
+    dev_pts = [torch.from_numpy(f["points"]).to(dev) for f in frames]
+    working_set = pipe.buffer_bytes()
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident throughput: graph replay, inputs already in HBM ------------------------------------------
+    def device_loop(n):
+        for i in range(n):
+            pipe.points.copy_(dev_pts[i % N_ROTATE], non_blocking=True)
+            pipe.replay()
+
+    device_loop(args.warmup)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    device_loop(args.steps)
+    e1.record()
+    barrier()
+    elapsed = e0.elapsed_time(e1) * 1e-3
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- end to end: pinned host -> device -> pipeline -> host ----------------------------------------------------
+    host_pts = [torch.from_numpy(f["points"]).pin_memory() for f in frames]
+    host_batch = torch.from_numpy(frames[0]["batch"]).pin_memory()
+    host_scores = torch.from_numpy(boxes["scores"]).pin_memory()
+    host_boxes = torch.from_numpy(boxes["boxes"]).pin_memory()
+    out_scores = torch.empty_like(host_scores).pin_memory()
+    out_counts = torch.zeros(8, dtype=torch.int32).pin_memory()
+    count_tensors = [pipe.vox_num] + [s["num"] for k, s in pipe.net.sets.items() if k != "in"]
+    h2d = host_pts[0].numel() * 4 + host_batch.numel() * 4 + host_scores.numel() * 4 + host_boxes.numel() * 4
+    d2h = out_scores.numel() * 4 + 4 * len(count_tensors)
+
+    def e2e_loop(n):
+        for i in range(n):
+            pipe.points.copy_(host_pts[i % N_ROTATE], non_blocking=True)
+            pipe.batch.copy_(host_batch, non_blocking=True)
+            pipe.scores.copy_(host_scores, non_blocking=True)
+            pipe.boxes.copy_(host_boxes, non_blocking=True)
+            pipe.replay()
+            out_scores.copy_(pipe.nms_scores, non_blocking=True)
+            for j, t in enumerate(count_tensors):
+                out_counts[j:j + 1].copy_(t, non_blocking=True)
+            torch.cuda.current_stream().synchronize()  # the caller holds the frame's result before the next frame
+
+    e2e_loop(args.warmup)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    e2e_loop(args.steps)
+    f1.record()
+    barrier()
+    e2e_elapsed = f0.elapsed_time(f1) * 1e-3
+
+    if dist is not None:
+        t = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed, e2e_elapsed = float(t[0]), float(t[1])
+
+    line = None
+    if rank == 0:
+        peaks = measured_peaks()
+        layers = conv_launch_times(pipe, frames, reps=3)
+        tc = [l for l in layers if l["cin"] % 16 == 0 and l["cout"] % 16 == 0]
+        t_conv = sum(l["seconds"] for l in tc)
+        f_dense = sum(l["flops_dense"] for l in tc)
+        achieved = f_dense / t_conv / 1e12
+        launches_per_frame = count_launches(pipe)
+        cpu = None
+        if world == 1 and not args.no_cpu_baseline:
+            fps, dt = cpu_frames_per_second(1, CPU_FRACTION, 1, 0)
+            cpu = {"value": fps, "unit": UNIT, "cores": 1, "kind": "port",
+                   "sample": "one 1/%d azimuth sector of a config-4 frame (and 1 of the 10 NMS rows) on one core, "
+                             "frames/s = (1/%d)/t, t = %.1f s" % (CPU_DENOM, CPU_DENOM, dt)}
+        line = {
+            "metric": METRIC, "value": world * args.steps / elapsed, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD, "frames_per_gpu_per_step": 1, "parallelism": "frame replicas x%d" % world,
+                       "voxels": {k: int(v) for k, v in pipe.net.counts().items()},
+                       "l2": "no flush: a frame rewrites %.0f MB of rulebooks/tables/activations (> 126 MB L2) and "
+                             "inputs rotate over %d frames" % (working_set / 1e6, N_ROTATE),
+                       "kernel": {0: "auto", 1: "simt", 2: "tcgen05"}[args.kernel]},
+            "clocks": clocks,
+            "e2e": {"value": world * args.steps / e2e_elapsed, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_elapsed / args.steps * 1e3},
+            "gpu_launches": launches_per_frame * args.steps,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                         "kernel": "SPConvMM over the %d layers with 16-multiple channels, dense-equivalent FLOPs "
+                                   "2*M*kVol*Cin*Cout per launch" % len(tc),
+                         "peak_source": peaks["source"] + ", burst bf16",
+                         "useful_tflops": sum(l["flops_pair"] for l in tc) / t_conv / 1e12,
+                         "conv_ms_per_frame": t_conv * 1e3},
+            "cpu_baseline": cpu,
+        }
+        if args.layers:
+            for l in layers:
+                sys.stderr.write("layer %2d  %3d->%3d k%2d  M=%7d P=%8d  %8.1f us  %7.2f TF/s dense  %6.2f TF/s pair\n"
+                                 % (l["layer"], l["cin"], l["cout"], l["kvol"], l["m"], l["pairs"], l["seconds"] * 1e6,
+                                    l["flops_dense"] / l["seconds"] / 1e12, l["flops_pair"] / l["seconds"] / 1e12))
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return line
+
+
+def count_launches(pipe):
+    """Kernels of this library launched per frame (every enqueue is a fixed launch list; counted from the plan)."""
+    n = 7  # SimpleMeanEncoder: reset, voxelize, owners, scan, number, accumulate, divide
+    built = set()
+    for L in pipe.net.layers:
+        if L.key not in built:
+            built.add(L.key)
+            n += (6 if L.kind == "subm" else 9) + 2  # rulebook passes + neighbour-table fill/scatter
+        n += 1  # SPConvMM
+    n += 3  # BEVDensify: map fill, map scatter, densify
+    n += 2  # NMS3d: overlap mask, suppression
+    return n
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--kernel", type=int, default=0, help="SPConvMM kernel: 0 auto, 1 SIMT, 2 tcgen05")
+    ap.add_argument("--layers", action="store_true", help="print the per-layer SPConvMM table to stderr")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,216 @@
+"""Sparse backbones composed from the plugins, the way the reference's tests compose them
+(tests/cylinder/test_cylinder3d.py:11-99: one SPConvIdx per ``indice_key`` shared by several SPConvMM
+layers, batch-norm folded into weight and bias, activation after the plugin).
+
+A ``SparseNet`` is built once ("engine build": plugin handles, weights uploaded, every buffer and
+workspace allocated at its static maximum size, exactly as TensorRT would own them) and then run
+frame after frame with no allocation and no host synchronisation, so a whole frame can be captured
+in a CUDA graph.  Layers that share a rulebook also share one output-stationary neighbour table.
+"""
+import numpy as np
+import torch
+
+from . import synth
+from .ops import data_s_spconv_index, data_s_spconv_mm
+from .plugins import SPConvMMPlugin, deserialize_plugin
+
+
+class Layer:
+    """One sparse convolution.
+
+    kind      'subm' | 'conv' (strided, creates a new voxel set) | 'inverse' (back to the inputs of `key`'s conv)
+    key       rulebook name (``indice_key``); the first layer naming a key builds it
+    residual  name of a saved activation added before the ReLU (fused epilogue), or None
+    save      name under which the output is kept for a later residual / skip connection
+    """
+
+    def __init__(self, kind, key, cin, cout, ksize=(3, 3, 3), stride=(1, 1, 1), padding=None, relu=True,
+                 residual=None, save=None, source=None):
+        self.kind, self.key, self.cin, self.cout = kind, key, cin, cout
+        self.ksize, self.stride = tuple(ksize), tuple(stride)
+        self.padding = tuple(k // 2 for k in ksize) if padding is None else tuple(padding)
+        self.relu, self.residual, self.save, self.source = relu, residual, save, source
+
+
+def res_block(key, c, tag):
+    """SparseBasicBlock: relu(conv2(relu(conv1(x))) + x), both SubM over the same rulebook."""
+    return [Layer("subm", key, c, c, save=None, source=None, relu=True, residual=None),
+            Layer("subm", key, c, c, relu=True, residual=tag)]
+
+
+def voxel_res_backbone_8x(cin):
+    """CenterPoint-shaped VoxelResBackBone8x, channels 16/32/64/128: input SubM, then per stage a strided conv
+    (stage 1 has none) followed by two residual blocks, then the (3,1,1)/(2,1,1) output conv."""
+    L = [Layer("subm", "subm1", cin, 16, save="s1")]
+    for i in range(2):
+        blk = res_block("subm1", 16, "s1")
+        blk[1].save = "s1"
+        L += blk
+    chans = [16, 32, 64, 128]
+    pads = [None, (1, 1, 1), (1, 1, 1), (0, 1, 1)]
+    for s in range(1, 4):
+        tag = "s%d" % (s + 1)
+        L.append(Layer("conv", "down%d" % (s + 1), chans[s - 1], chans[s], stride=(2, 2, 2), padding=pads[s], save=tag))
+        for i in range(2):
+            blk = res_block("subm%d" % (s + 1), chans[s], tag)
+            blk[1].save = tag
+            L += blk
+    L.append(Layer("conv", "out", 128, 128, ksize=(3, 1, 1), stride=(2, 1, 1), padding=(0, 0, 0)))
+    return L
+
+
+def voxel_backbone_8x(cin):
+    """SECOND-shaped VoxelBackBone8x, channels 16/32/64/64, ending in the (3,1,1)/(2,1,1) conv to 128."""
+    L = [Layer("subm", "subm1", cin, 16), Layer("subm", "subm1", 16, 16)]
+    chans = [16, 32, 64, 64]
+    pads = [None, (1, 1, 1), (1, 1, 1), (0, 1, 1)]
+    for s in range(1, 4):
+        L.append(Layer("conv", "down%d" % (s + 1), chans[s - 1], chans[s], stride=(2, 2, 2), padding=pads[s]))
+        L.append(Layer("subm", "subm%d" % (s + 1), chans[s], chans[s]))
+        L.append(Layer("subm", "subm%d" % (s + 1), chans[s], chans[s]))
+    L.append(Layer("conv", "out", 64, 128, ksize=(3, 1, 1), stride=(2, 1, 1), padding=(0, 0, 0)))
+    return L
+
+
+def make_weights(layers, seed=0):
+    """Seeded Kaiming weights [kVol, Cin, Cout] and small biases (batch-norm folded) for every layer, in order."""
+    rng = np.random.Generator(np.random.PCG64(4242 + seed))
+    out = []
+    for L in layers:
+        kvol = int(np.prod(L.ksize))
+        w = synth.kaiming_weight(rng, kvol, L.cin, L.cout)
+        b = (rng.standard_normal(L.cout) * 0.05).astype(np.float32)
+        out.append((w, b))
+    return out
+
+
+class _Rulebook:
+    pass
+
+
+class SparseNet:
+    """Executable sparse network with static buffers.
+
+    layers      list of Layer
+    spatial     [B, Z, Y, X] of the input voxel grid
+    caps        dict voxel-set name -> maximum active voxels ('in' for the input set, otherwise the key of the
+                'conv' layer that creates the set); missing entries default to `default_cap`
+    """
+
+    def __init__(self, layers, spatial, caps, dtype=torch.float16, device="cuda:0", seed=0, kernel=0):
+        self.layers, self.device, self.dtype = layers, torch.device(device), dtype
+        self.kernel = kernel
+        weights = make_weights(layers, seed)
+        self.rulebooks = {}
+        self.mm = []
+        self.bufs = []
+        self.sets = {"in": dict(cap=int(caps["in"]), shape=[int(v) for v in spatial], coors=None, num=None)}
+        cur = "in"
+        set_of_tag = {}
+        with torch.cuda.device(self.device):
+            for li, L in enumerate(layers):
+                if L.source is not None:
+                    cur = set_of_tag[L.source]
+                src = self.sets[cur]
+                if L.key not in self.rulebooks:
+                    assert L.kind != "inverse", "an inverse layer needs the rulebook of its conv"
+                    rb = _Rulebook()
+                    rb.kind, rb.in_set, rb.ksize = L.kind, cur, L.ksize
+                    rb.kvol = int(np.prod(L.ksize))
+                    subm = L.kind == "subm"
+                    if subm:
+                        rb.out_set = cur
+                    else:
+                        shp = src["shape"]
+                        oshape = [shp[0]] + [(shp[d + 1] + 2 * L.padding[d] - (L.ksize[d] - 1) - 1) // L.stride[d] + 1
+                                             for d in range(3)]
+                        cap = int(caps[L.key])
+                        self.sets[L.key] = dict(cap=cap, shape=oshape, coors=None, num=None)
+                        rb.out_set = L.key
+                    out = self.sets[rb.out_set]
+                    rb.plugin = deserialize_plugin("SPConvIdx3d", data_s_spconv_index(
+                        L.ksize, L.stride, L.padding, (1, 1, 1), (0, 0, 0), out["cap"], subm, False))
+                    rb.shape_tensor = torch.empty([src["shape"][0], 0] + src["shape"][1:], dtype=torch.int32,
+                                                  device=self.device)
+                    row_len = rb.kvol * (src["cap"] + 128)
+                    rb.out_shape_tensor = torch.empty([out["shape"][0], 0] + out["shape"][1:], dtype=torch.int32,
+                                                      device=self.device)
+                    rb.index = torch.empty((3, row_len), dtype=torch.int32, device=self.device)
+                    rb.num_index = torch.zeros(1, dtype=torch.int32, device=self.device)
+                    if not subm:
+                        out["coors"] = torch.zeros((out["cap"], 4), dtype=torch.int32, device=self.device)
+                        out["num"] = torch.zeros(1, dtype=torch.int32, device=self.device)
+                    rb.table_fwd = torch.empty(max(SPConvMMPlugin.table_bytes(rb.kvol, out["cap"]), 16),
+                                               dtype=torch.uint8, device=self.device)
+                    rb.table_inv = None
+                    self.rulebooks[L.key] = rb
+                rb = self.rulebooks[L.key]
+                if L.kind == "inverse":
+                    out_set, in_set = rb.in_set, rb.out_set
+                    if rb.table_inv is None:
+                        rb.table_inv = torch.empty(
+                            max(SPConvMMPlugin.table_bytes(rb.kvol, self.sets[out_set]["cap"]), 16),
+                            dtype=torch.uint8, device=self.device)
+                else:
+                    out_set, in_set = rb.out_set, rb.in_set
+                assert in_set == cur, "layer %d expects voxel set %s but the data is on %s" % (li, in_set, cur)
+                w, b = weights[li]
+                plug = deserialize_plugin("SPConvMM", data_s_spconv_mm(
+                    L.ksize, L.cin, L.cout, self.sets[out_set]["cap"], L.kind == "subm", L.kind == "inverse", w, b))
+                plug.configure(dtype)
+                plug.set_kernel(kernel)
+                out_buf = torch.zeros((self.sets[out_set]["cap"], L.cout), dtype=dtype, device=self.device)
+                self.mm.append((plug, out_buf, out_set))
+                cur = out_set
+                if L.save:
+                    set_of_tag[L.save] = cur
+            self.out_set = cur
+
+    def set_input(self, coors, num):
+        self.sets["in"]["coors"], self.sets["in"]["num"] = coors, num
+
+    def forward(self, feats):
+        """feats [cap_in, Cin] in the net dtype; coordinates / count as given to set_input.  Returns
+        (out_feats, out_coors, num_act_out); every tensor is a static buffer of the net."""
+        built = set()
+        saved = {}
+        x = feats
+        for L, (plug, out_buf, out_set) in zip(self.layers, self.mm):
+            if L.source is not None:
+                x = saved[L.source]
+            rb = self.rulebooks[L.key]
+            if L.key not in built:
+                src, dst = self.sets[rb.in_set], self.sets[rb.out_set]
+                if rb.kind == "subm":
+                    rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor, outputs=[rb.index, rb.num_index])
+                else:
+                    rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor,
+                                      outputs=[rb.index, rb.num_index, dst["coors"], dst["num"],
+                                               rb.out_shape_tensor])
+                SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd)
+                if rb.table_inv is not None:
+                    SPConvMMPlugin.prepare(rb.kvol, True, src["cap"], rb.index, rb.num_index, table=rb.table_inv)
+                built.add(L.key)
+            table = rb.table_inv if L.kind == "inverse" else rb.table_fwd
+            res = saved[L.residual] if L.residual else None
+            x = plug.run(x, self.sets[out_set]["num"], table, out=out_buf, relu=L.relu, residual=res)
+            if L.save:
+                saved[L.save] = x
+        o = self.sets[self.out_set]
+        return x, o["coors"], o["num"]
+
+    def counts(self):
+        """Active voxels of every set (host sync; for calibration and reporting only)."""
+        return {k: int(v["num"].item()) for k, v in self.sets.items() if v["num"] is not None}
+
+    def layer_work(self):
+        """Per layer: (Cin, Cout, kVol, M, pairs P) after a forward pass (host sync)."""
+        out = []
+        pairs = {}
+        for L, (plug, _, out_set) in zip(self.layers, self.mm):
+            rb = self.rulebooks[L.key]
+            if L.key not in pairs:
+                k = rb.index[2, :int(rb.num_index.item())]
+                pairs[L.key] = int((k >= 0).sum().item())
+            out.append((L.cin, L.cout, rb.kvol, int(self.sets[out_set]["num"].item()), pairs[L.key]))
+        return out

@@ -1,0 +1,144 @@
+"""Whole-frame detection pipeline on one GPU: voxel encoder -> sparse backbone -> BEV densify, plus the
+rotated-BEV NMS of the detection head -- the chain of plugins a deploy3d engine runs per frame
+(deploy3d/symfun/models/lidar_detect.py:53-96 feeds points in and reads boxes out; the plugin chain
+in between is what TensorRT enqueues).  Everything between the input copy and the output copy is
+enqueued on one stream without host synchronisation and is captured into a CUDA graph.
+"""
+import numpy as np
+import torch
+
+from . import backbone, synth
+from .ops import data_s_bev_densify, data_s_voxel_encoder
+from .plugins import deserialize_plugin
+
+
+def _roundup(v, m):
+    return (int(v) + m - 1) // m * m
+
+
+class DetectionPipeline:
+    """CenterPoint-shaped (``kind='centerpoint'``) or SECOND-shaped (``kind='second'``) frame pipeline."""
+
+    def __init__(self, kind="centerpoint", device="cuda:0", caps=None, kernel=0, n_class=10, topk=1000,
+                 iou_threshold=0.2, dtype=torch.float16):
+        self.kind, self.device, self.dtype = kind, torch.device(device), dtype
+        if kind == "centerpoint":
+            frame = synth.config4_points()
+            self.layers = backbone.voxel_res_backbone_8x(5)
+        elif kind == "second":
+            frame = synth.config3_points()
+            self.layers = backbone.voxel_backbone_8x(4)
+        else:
+            raise ValueError(kind)
+        self.n_pts, self.c_pts = frame["points"].shape
+        self.spatial = frame["spatial_shape"]
+        self.voxel_config = frame["voxel_config"]
+        self.caps = caps or self.default_caps()
+        dev = self.device
+        with torch.cuda.device(dev):
+            self.points = torch.zeros((self.n_pts, self.c_pts), dtype=torch.float32, device=dev)
+            self.batch = torch.zeros(self.n_pts, dtype=torch.int32, device=dev)
+            self.cfg = torch.from_numpy(self.voxel_config).to(dev)
+            self.shape_tensor = torch.empty(self.spatial, dtype=torch.int32, device=dev)
+            cap_in = self.caps["in"]
+            self.vfe = deserialize_plugin("SimpleMeanEncoder", data_s_voxel_encoder(cap_in))
+            self.vox_feats = torch.zeros((cap_in, self.c_pts), dtype=torch.float32, device=dev)
+            self.vox_coors = torch.zeros((cap_in, 4), dtype=torch.int32, device=dev)
+            self.vox_num = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.vox_feats_lp = torch.zeros((cap_in, self.c_pts), dtype=dtype, device=dev)
+            spatial_b = [self.spatial[0]] + list(self.spatial[2:])
+            self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel)
+            self.net.set_input(self.vox_coors, self.vox_num)
+            out = self.net.sets[self.net.out_set]
+            self.out_shape = out["shape"]
+            c_out = self.layers[-1].cout
+            self.densify = deserialize_plugin("BEVDensify", data_s_bev_densify(c_out * self.out_shape[1]))
+            self.out_shape_tensor = torch.empty([self.out_shape[0], 0] + self.out_shape[1:], dtype=torch.int32,
+                                                device=dev)
+            self.bev = torch.zeros((self.out_shape[0], c_out * self.out_shape[1], self.out_shape[2],
+                                    self.out_shape[3]), dtype=dtype, device=dev)
+            self.nms = deserialize_plugin("NMS3d", b"")
+            self.nms.p.iou_threshold = iou_threshold
+            self.scores = torch.zeros((n_class, topk), dtype=torch.float32, device=dev)
+            self.boxes = torch.zeros((n_class, topk, 7), dtype=torch.float32, device=dev)
+            self.nms_scores = torch.zeros((n_class, topk), dtype=torch.float32, device=dev)
+        self.graph = None
+
+    def default_caps(self):
+        """Static buffer sizes (the reference fixes them per model, e.g. [131072, 65536, 32768, 16384] in
+        tests/cylinder/test_cylinder3d.py:391): generous here, tightened by calibrate()."""
+        n = self.n_pts
+        return {"in": n, "down2": 4 * n, "down3": 4 * n, "down4": 3 * n, "out": 3 * n}
+
+    def calibrate(self, frames, margin=1.15):
+        """Run `frames` once with generous buffers, read the voxel counts back and return tight caps."""
+        peak = {}
+        for f in frames:
+            self.load_frame(f)
+            self.enqueue()
+            torch.cuda.synchronize(self.device)
+            cnt = self.net.counts()
+            cnt["in"] = int(self.vox_num.item())
+            for k, v in cnt.items():
+                if v >= self.caps[k]:
+                    raise RuntimeError("voxel set %s filled its buffer (%d): raise the calibration caps" % (k, v))
+                peak[k] = max(peak.get(k, 0), v)
+        return {k: _roundup(v * margin + 256, 1024) for k, v in peak.items()}
+
+    def load_frame(self, frame, boxes=None):
+        """Synchronous convenience copy of one synthetic frame into the static input buffers."""
+        self.points.copy_(torch.from_numpy(frame["points"]))
+        self.batch.copy_(torch.from_numpy(frame["batch"]))
+        if boxes is not None:
+            self.scores.copy_(torch.from_numpy(boxes["scores"]))
+            self.boxes.copy_(torch.from_numpy(boxes["boxes"]))
+
+    def enqueue(self):
+        """Enqueue one frame on the current stream (no host sync, no allocation after the first call)."""
+        self.vfe.enqueue(self.points, self.batch, self.cfg, self.shape_tensor,
+                         outputs=[self.vox_feats, self.vox_coors, self.vox_num])
+        self.vox_feats_lp.copy_(self.vox_feats)  # fp32 -> fp16 reformat (TensorRT inserts this layer itself)
+        feats, coors, num = self.net.forward(self.vox_feats_lp)
+        self.densify.enqueue(feats, coors, num, self.out_shape_tensor, outputs=[self.bev])
+        self.nms.enqueue(self.scores, self.boxes, outputs=[self.nms_scores])
+        return feats, coors, num
+
+    def capture(self):
+        """Capture enqueue() into a CUDA graph (after a warm-up call so every workspace exists)."""
+        with torch.cuda.device(self.device):
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self.enqueue()
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self._graph_out = self.enqueue()
+        return self.graph
+
+    def replay(self):
+        self.graph.replay()
+
+    def buffer_bytes(self):
+        """Bytes of every static buffer a frame touches (inputs, rulebooks, tables, activations, workspaces)."""
+        total = 0
+        seen = set()
+
+        def add(t):
+            nonlocal total
+            if t is not None and t.data_ptr() not in seen and t.numel():
+                seen.add(t.data_ptr())
+                total += t.numel() * t.element_size()
+
+        for t in (self.points, self.batch, self.vox_feats, self.vox_coors, self.vox_feats_lp, self.bev, self.boxes,
+                  self.scores, self.nms_scores, self.vfe._workspace, self.densify._workspace, self.nms._workspace):
+            add(t)
+        for rb in self.net.rulebooks.values():
+            for t in (rb.index, rb.table_fwd, rb.table_inv, rb.plugin._workspace):
+                add(t)
+        for _, buf, _ in self.net.mm:
+            add(buf)
+        for s in self.net.sets.values():
+            add(s["coors"])
+        return total
