@@ -116,6 +116,8 @@ SIGNATURES = {
     "d3d_nms3d_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(Nms3dParams)]),
     "d3d_nms3d_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(Nms3dParams))),
     "d3d_nms3d_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(Nms3dParams))),
+    "d3d_nms3d_enqueue_static": (ctypes.c_int, [ctypes.POINTER(Nms3dParams), _descp, ctypes.c_int, _descp,
+                                                 ctypes.c_int, _vpp, _vpp, _vp]),
 }
 
 _LIB = None

@@ -278,3 +278,56 @@ extern "C" int d3d_nms3d_enqueue(const d3d_nms3d_params* p, const d3d_tensor_des
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }
+
+// ---------------------------------------------------------------------------------------------
+// NMS3d without a caller-provided workspace.
+//
+// Some hosts of this library hand a plugin nothing but its input and output pointers and a stream, and are not
+// allowed to obtain device memory themselves: a real-time perception loop that bans allocator calls once it is
+// running, an engine that was built before the plugin asked for workspace, a thin C caller that owns no memory
+// pool.  For them the overlap-mask scratch of NMS3d lives in the library image itself: a file-scope device
+// array of fixed size.  Every GPU that loads the library keeps those 2 MiB until the process exits.
+//
+// `g_nms_static_mask` below is, in host code, only a handle for the symbol -- not a device address.  The address
+// a kernel can use is looked up once per device with cudaGetSymbolAddress (with that device current) and cached;
+// that look-up happens inside the first call on a device, which therefore should be made before any stream
+// capture is started.  Nothing in the array has to start at zero: the mask kernel overwrites every word the
+// suppression kernel reads, so stale contents of an earlier call are harmless.  All calls on one GPU share the
+// one array: two calls that overlap on the GPU (different streams, or different threads) race on it.
+// ---------------------------------------------------------------------------------------------
+// D3D_NMS3D_STATIC_MAX_WORDS (include/deploy3d_b200.h): 256 Ki 64-bit mask words = 2 MiB; 10 x 1000 boxes need 160 000
+static __device__ __align__(256) unsigned long long g_nms_static_mask[D3D_NMS3D_STATIC_MAX_WORDS];
+
+namespace {
+constexpr int kMaxStaticDevices = 64;
+unsigned long long* g_nms_static_ptr[kMaxStaticDevices];  // per-device address of g_nms_static_mask, 0 = not yet known
+}  // namespace
+
+extern "C" int d3d_nms3d_enqueue_static(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in,
+                                        const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                                        void* const* outputs, void* stream) {
+  D3D_REQUIRE(p && out && inputs && outputs && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
+  int b, k, bd;
+  int rc = nms_dims(in, n_in, &b, &k, &bd);
+  if (rc != D3D_OK) return rc;
+  if (b == 0 || k == 0) return D3D_OK;
+  const int nw = (int)ceil_div(k, kNmsBlock);
+  // the scratch is fixed: larger problems are refused, never truncated
+  D3D_REQUIRE((size_t)b * k * nw <= (size_t)D3D_NMS3D_STATIC_MAX_WORDS, D3D_ERR_TOO_LARGE);
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxStaticDevices) return D3D_ERR_CUDA;
+  unsigned long long* mask = g_nms_static_ptr[dev];
+  if (!mask) {
+    void* addr = nullptr;
+    if (cudaGetSymbolAddress(&addr, g_nms_static_mask) != cudaSuccess || !addr) return D3D_ERR_CUDA;
+    mask = reinterpret_cast<unsigned long long*>(addr);
+    g_nms_static_ptr[dev] = mask;  // same value whichever thread stores it first
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  overlap_mask_kernel<<<dim3(nw, nw, b), 256, 0, st>>>(reinterpret_cast<const float*>(inputs[1]), k, bd,
+                                                       p->iou_threshold, nw, mask);
+  suppress_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
+                                    reinterpret_cast<float*>(outputs[0]));
+  D3D_CHECK_LAUNCH();
+  return D3D_OK;
+}

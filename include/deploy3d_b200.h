@@ -257,6 +257,17 @@ int d3d_nms3d_workspace(const d3d_nms3d_params* p, const d3d_tensor_desc* in, in
 int d3d_nms3d_enqueue(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in, const d3d_tensor_desc* out,
                       int n_out, const void* const* inputs, void* const* outputs, void* workspace,
                       size_t workspace_bytes, void* stream);
+/* NMS3d for callers that cannot supply a workspace and may not allocate device memory (a control loop that forbids
+ * allocator calls after start-up, an engine built without plugin workspace, a bare C host with no memory pool).
+ * This entry point has no counterpart in the reference.  Same inputs, outputs and results as d3d_nms3d_enqueue; the
+ * overlap-mask scratch is a fixed 2 MiB array inside the library (held by every GPU that loads it), so
+ * B*K*ceil(K/64) must not exceed D3D_NMS3D_STATIC_MAX_WORDS or the call returns D3D_ERR_TOO_LARGE.  The call
+ * performs no device allocation.  The first call on a device resolves the array's device address; make that call
+ * before starting a stream capture.  All calls on a GPU share the array: calls that overlap on the GPU race. */
+#define D3D_NMS3D_STATIC_MAX_WORDS (256 * 1024)
+int d3d_nms3d_enqueue_static(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in,
+                             const d3d_tensor_desc* out, int n_out, const void* const* inputs, void* const* outputs,
+                             void* stream);
 
 #ifdef __cplusplus
 }
