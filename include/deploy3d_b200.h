@@ -59,6 +59,10 @@ typedef struct {
 
 const char* d3d_version(void);
 const char* d3d_status_string(int status);
+/* Debug aid (no reference counterpart; the reference only prints CUDA errors, trt/include/common/macros.h:14-34):
+ * synchronises the device, returns in *code the error word a kernel of this library raised when one of its bounded
+ * waits expired (0 = none) and clears it. */
+int d3d_debug_take_kernel_error(int* code);
 
 /* ---------------------------------------------------------------------------------------------
  * SPConvIdx{1,2,3,4}d -- rulebook generation.

@@ -1,0 +1,118 @@
+"""GPU parity of the tcgen05/TMEM SPConvMM kernel: forced through set_kernel(2), compared with the fp32-accumulating
+oracle at 1e-2 (fp16 / bf16) and with the SIMT kernel of the same library; the kernel's bounded waits must not
+have expired (error word 0)."""
+import ctypes
+
+import numpy as np
+import pytest
+import torch
+
+from tests._util import assert_feats_close, rng, round_to, unique_coors
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _t(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+    return t if dtype is None else t.to(dtype)
+
+
+def _kernel_error():
+    from deploy3d_b200 import _lib
+    code = ctypes.c_int(-1)
+    _lib.check("d3d_debug_take_kernel_error", _lib.lib().d3d_debug_take_kernel_error(ctypes.byref(code)))
+    return code.value
+
+
+def _rulebook(d3d, coors, shape_b, ks, st, pd, subm, max_out):
+    n = coors.shape[0]
+    num_in = torch.tensor([n], dtype=torch.int32, device=DEV)
+    outs = d3d.spconv_index(_t(coors), num_in, torch.empty([shape_b[0], 0] + shape_b[1:], dtype=torch.int32,
+                                                           device=DEV),
+                            ks, st, pd, (1, 1, 1), (0, 0, 0), max_out, subm, False)
+    return outs, num_in
+
+
+def _run(d3d, orc, outs, num_in, num_out, n_in, n_out_max, cin, cout, ks, inverse, dtype, seed, relu=False,
+         residual=False):
+    from deploy3d_b200.plugins import SPConvMMPlugin, deserialize_plugin
+    r = rng(seed)
+    kvol = int(np.prod(ks))
+    feats = r.standard_normal((n_in, cin)).astype(np.float32)
+    w = (r.standard_normal((kvol, cin, cout)) * np.sqrt(2.0 / (kvol * cin))).astype(np.float32)
+    b = r.standard_normal(cout).astype(np.float32)
+    res = r.standard_normal((n_out_max, cout)).astype(np.float32) if residual else None
+    tdt = torch.float16 if dtype == "fp16" else torch.bfloat16
+    table = SPConvMMPlugin.prepare(kvol, inverse, n_out_max, outs[0], outs[1])
+    got = {}
+    for which in (2, 1):
+        plug = deserialize_plugin("SPConvMM", d3d.data_s_spconv_mm(ks, cin, cout, n_out_max, False, inverse, w, b))
+        plug.configure(tdt)
+        plug.set_kernel(which)
+        y = plug.run(_t(feats, tdt), num_out, table, relu=relu, residual=None if res is None else _t(res, tdt))
+        assert _kernel_error() == 0, "a bounded wait of the tensor-core kernel expired"
+        got[which] = y.float().cpu().numpy()
+    want = orc.spconv_mm(round_to(feats, dtype), round_to(w, dtype), round_to(b, dtype), outs[0].cpu().numpy(),
+                         int(outs[1].item()), inverse, n_out_max)
+    if res is not None:
+        want = want + round_to(res, dtype)
+    if relu:
+        want = np.maximum(want, 0)
+    assert_feats_close(got[2], want, 1e-2, "tcgen05 vs oracle")
+    assert_feats_close(got[2], got[1], 1e-2, "tcgen05 vs SIMT")
+    return got[2]
+
+
+def test_smallest_case(d3d, orc):
+    """One tile, 16 -> 16 channels: the first thing to run on a new box."""
+    coors = unique_coors(rng(1), 100, [1, 6, 6, 6])
+    outs, num_in = _rulebook(d3d, coors, [1, 6, 6, 6], (3, 3, 3), (1, 1, 1), (1, 1, 1), True, 100)
+    _run(d3d, orc, outs, num_in, num_in, 100, 100, 16, 16, (3, 3, 3), False, "fp16", 2)
+
+
+@pytest.mark.parametrize("cin,cout", [(16, 16), (16, 32), (32, 32), (32, 64), (64, 64), (64, 128), (128, 128),
+                                      (128, 64), (64, 32), (32, 16), (64, 48), (128, 256), (256, 128), (256, 256),
+                                      (16, 80)])
+@pytest.mark.parametrize("dtype", ["fp16", "bf16"])
+def test_channel_grid_subm(d3d, orc, cin, cout, dtype):
+    coors = unique_coors(rng(3), 5000, [2, 24, 30, 20])
+    outs, num_in = _rulebook(d3d, coors, [2, 24, 30, 20], (3, 3, 3), (1, 1, 1), (1, 1, 1), True, 5000)
+    _run(d3d, orc, outs, num_in, num_in, 5000, 5000, cin, cout, (3, 3, 3), False, dtype, cin * 1000 + cout)
+
+
+@pytest.mark.parametrize("ks,pd", [((3, 1, 3), (1, 0, 1)), ((1, 3, 3), (0, 1, 1)), ((3, 1, 1), (1, 0, 0)),
+                                   ((1, 1, 1), (0, 0, 0))])
+def test_asymmetric_kernels(d3d, orc, ks, pd):
+    coors = unique_coors(rng(4), 9000, [2, 48, 36, 16])
+    outs, num_in = _rulebook(d3d, coors, [2, 48, 36, 16], ks, (1, 1, 1), pd, True, 9100)
+    _run(d3d, orc, outs, num_in, num_in, 9000, 9100, 32, 64, ks, False, "fp16", 5)
+
+
+def test_strided_inverse_padded_and_epilogue(d3d, orc):
+    """Strided conv with buffers larger than the live counts, its inverse, and the fused residual + ReLU epilogue."""
+    coors = unique_coors(rng(6), 20000, [2, 120, 90, 8])
+    outs, num_in = _rulebook(d3d, coors, [2, 120, 90, 8], (3, 3, 3), (2, 2, 1), (1, 1, 1), False, 50000)
+    nout = int(outs[3].item())
+    down = _run(d3d, orc, outs, num_in, outs[3], 20000, 50000, 32, 64, (3, 3, 3), False, "fp16", 7, relu=True)
+    assert (down[nout:] == down[nout]).all()  # rows beyond numActOut hold relu(bias)
+    _run(d3d, orc, outs, outs[3], num_in, 50000, 20000, 64, 32, (3, 3, 3), True, "fp16", 8, relu=True, residual=True)
+    _run(d3d, orc, outs, outs[3], num_in, 50000, 20000, 64, 32, (3, 3, 3), True, "bf16", 9, relu=False, residual=True)
+
+
+def test_config2_through_tensor_cores(d3d, orc):
+    """BASELINE config 2 at full size: 2 x 60 000 LiDAR-like voxels, 32 -> 64 strided then 64 -> 32 inverse."""
+    from deploy3d_b200 import synth
+    c = synth.config2()
+    n = c["coors"].shape[0]
+    outs, num_in = _rulebook(d3d, c["coors"], [2, 41, 1600, 1408], c["ksize"], c["stride"], c["padding"], False, n)
+    _run(d3d, orc, outs, num_in, outs[3], n, n, 32, 64, c["ksize"], False, "fp16", 10)
+    _run(d3d, orc, outs, outs[3], num_in, n, n, 64, 32, c["ksize"], True, "fp16", 11)
+
+
+def test_ragged_and_empty_tiles(d3d, orc):
+    """M not a multiple of 128, all-empty tiles in the middle (outputs without any neighbour), single row."""
+    for n in (1, 127, 129, 1000):
+        coors = unique_coors(rng(20 + n), n, [1, 40, 40, 40])
+        outs, num_in = _rulebook(d3d, coors, [1, 40, 40, 40], (3, 3, 3), (1, 1, 1), (1, 1, 1), True, n + 300)
+        _run(d3d, orc, outs, num_in, num_in, n, n + 300, 16, 32, (3, 3, 3), False, "fp16", 30 + n)
