@@ -293,10 +293,7 @@ def run_ours(args):
     barrier()
     e2e_elapsed = f0.elapsed_time(f1) * 1e-3
 
-    if dist is not None:
-        t = torch.tensor([elapsed, e2e_elapsed], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed, e2e_elapsed = float(t[0]), float(t[1])
+    elapsed, e2e_elapsed = max_over_ranks([elapsed, e2e_elapsed], dist, dev)
 
     line = None
     if rank == 0:
@@ -346,6 +343,22 @@ def run_ours(args):
         dist.barrier()
         dist.destroy_process_group()
     return line
+
+
+def max_over_ranks(values, dist, device):
+    """Slowest rank decides: element-wise maximum of `values` over all ranks (identity without a process group).
+    The frames are independent replicas, so this reduction of the timings is the only inter-rank exchange."""
+    if dist is None:
+        return [float(v) for v in values]
+    import torch
+    t = torch.tensor([float(v) for v in values], dtype=torch.float64, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def aggregate_frames_per_second(world, steps, frames_per_step, elapsed_max):
+    """Whole-job throughput: every rank processed steps x frames_per_step frames within the slowest rank's time."""
+    return world * steps * frames_per_step / elapsed_max
 
 
 def count_launches(pipe):

@@ -41,7 +41,8 @@ __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t 
   int g = __ldg(index + (inverse ? row_len : 0) + p);
   int s = __ldg(index + (inverse ? 0 : row_len) + p);
   if (g < 0 || s < 0 || s >= m_max) return;
-  table[(int64_t)k * m_max + s] = g;
+  // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
+  table[((int64_t)(s >> 7) * kvol + k) * 128 + (s & 127)] = g;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -77,7 +78,7 @@ spconv_mm_simt_kernel(const T* __restrict__ in_feats, int64_t n_in_max, const T*
 
   for (int k = warp; k < kvol; k += kSimtThreads / 32) {
     int64_t o = tile0 + lane;
-    int v = o < m_max ? __ldg(table + (int64_t)k * pitch + o) : -1;
+    int v = o < m_max ? __ldg(table + ((o >> 7) * kvol + k) * 128 + (o & 127)) : -1;
     if (v >= n_in_max) v = -1;
     idx_s[k * kTileM + lane] = v;
     unsigned any = __ballot_sync(0xffffffffu, v >= 0);
@@ -300,7 +301,7 @@ extern "C" int d3d_spconv_mm_destroy(d3d_spconv_mm_t h) {
 }
 
 extern "C" int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t h, int which) {
-  D3D_REQUIRE(h && which >= 0 && which <= 2, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(h && which >= 0 && which <= 3, D3D_ERR_INVALID_ARGUMENT);
   h->kernel_choice = which;
   return D3D_OK;
 }
@@ -349,7 +350,7 @@ extern "C" int d3d_spconv_mm_run(d3d_spconv_mm_t h, int dtype, const void* in_fe
   a.residual = epilogue ? epilogue->residual : nullptr;
   a.stream = stream;
   bool tc_ok = spconv_mm_tc_eligible(h, dtype);
-  if (h->kernel_choice == 2) {
+  if (h->kernel_choice == 2 || h->kernel_choice == 3) {
     D3D_REQUIRE(tc_ok, D3D_ERR_INVALID_ARGUMENT);
     return launch_spconv_mm_tc(a);
   }

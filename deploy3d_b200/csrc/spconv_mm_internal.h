@@ -27,7 +27,7 @@ struct MmLaunch {
   const void* in_feats;
   int64_t max_num_act_in;
   const int32_t* num_act_out;
-  const int32_t* table;  // [kVol][pitch] input row per (offset, output), -1 = none; pitch = max_num_act_out rounded up to 128
+  const int32_t* table;  // [tiles][kVol][128] input row per (output tile, offset, row in tile), -1 = none; tiles = ceil(max_num_act_out / 128)
   void* out_feats;
   int relu;
   const void* residual;

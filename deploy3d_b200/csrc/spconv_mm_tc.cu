@@ -1,8 +1,8 @@
 // SPConvMM on the 5th-generation tensor cores: output-stationary implicit GEMM.
 //
 // For a tile of 128 consecutive output voxels and every kernel offset k that feeds at least one of them:
-//   A = the 128 input rows named by the neighbour table, gathered by TMA (tile::gather4, four arbitrary rows per
-//       instruction, missing neighbours addressed out of bounds so the TMA zero-fills them without touching memory),
+//   A = the 128 input rows named by the neighbour table (zero rows where the neighbour is missing), staged in shared
+//       memory in the K-major swizzled layout the tensor core reads,
 //   B = W[k]^T, K-major, loaded by a tiled TMA copy,
 //   D += A * B with tcgen05.mma (M = 128, N = Cout, K = 16 per instruction), fp32 accumulator in tensor memory.
 // All offsets of a tile accumulate into the same TMEM columns; the epilogue reads them once with tcgen05.ld, adds
@@ -10,10 +10,17 @@
 // (The reference: gather iterator + mma.sync tiles of 64 pairs of one offset, fp16 accumulate, half2 atomicAdd
 // scatter, trt/spconv/mm/kernel.h:84-179, mm/output_iterator.h:189-206.)
 //
-// CTA = 6 warps, persistent over tiles (tile = blockIdx.x, += gridDim.x):
-//   warp 0    producer: scans the tile's offsets, issues the gathers and the weight loads into an smem ring
-//   warp 1    MMA issuer (one elected lane); owns the TMEM allocation (two accumulators, double buffered)
-//   warps 2-5 epilogue: TMEM -> registers -> global
+// Two producers exist for the A operand, same consumer side:
+//   * TMA gather   tile::gather4, four arbitrary rows per instruction issued by one warp; missing neighbours are
+//                  addressed out of bounds so the TMA zero-fills them.  Measured on B200: about 11 ns per gathered
+//                  row whatever its width (a request-rate limit of the TMA unit), i.e. ~1.4 us per (tile, offset).
+//   * cp.async     four producer warps, 16-byte LDGSTS per thread with zero-fill for missing rows, written straight
+//                  into the swizzled layout; an order of magnitude more row requests in flight.  This is the default.
+// CTA roles (persistent over tiles: tile = blockIdx.x, += gridDim.x):
+//   producer warp(s)  prefetch the tile's neighbour ids into smem (one bulk copy), find the offsets that occur,
+//                     fill the smem ring: up to `group` offsets per stage
+//   MMA warp          one elected lane issues tcgen05.mma; owns the TMEM allocation (two accumulators)
+//   4 epilogue warps  TMEM -> registers -> global
 // Stages and accumulators are handed over through mbarriers; every wait is bounded (about one second) and on
 // expiry raises an error word, lets the CTA drain and return instead of spinning.
 #include <cuda.h>
@@ -24,10 +31,10 @@
 namespace d3d {
 namespace {
 
-constexpr int kTcThreads = 192;
 constexpr int kTileRows = 128;
 constexpr int kMaxStages = 8;
 constexpr int kNumAcc = 2;
+constexpr int kMaxGroup = 8;  // kernel offsets that may share one pipeline stage
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
 __device__ int g_tc_error;  // 0 ok; otherwise the code of the first wait that gave up
@@ -35,21 +42,24 @@ __device__ int g_tc_error;  // 0 ok; otherwise the code of the first wait that g
 enum StageFlags : int { kFirst = 1, kLast = 2, kEmptyTile = 4, kStop = 8 };
 
 struct TcParams {
-  const int32_t* table;  // [kvol][pitch]
-  int64_t pitch;
+  const int32_t* table;  // [tiles][kvol][128]
+  const void* in_feats;  // [n_in_rows][cin]
   int64_t m_max;
   int32_t n_in_rows;  // rows of the gathered tensor (out-of-range row index = zero fill)
   int kvol, cin, cout;
   int num_tiles;
   int stages;
-  uint32_t a_bytes, b_bytes;  // per stage, each a multiple of 1024
+  int group;                  // kernel offsets per stage (> 1 only when kparts == 1)
+  uint32_t a_bytes, b_bytes;  // per (offset, K part) block, each a multiple of 1024
+  uint32_t idx_bytes;         // kvol * 512: neighbour ids of one tile
   int row_bytes;              // bytes of one smem row = min(cin, 64) * 2
-  int kchunk;                 // input channels per stage (cin, or a 64-multiple part of it when cin is large)
-  int kparts;                 // cin / kchunk: stages per kernel offset
-  int chunks;                 // kchunk / 64 (at least 1): swizzle-span wide column blocks per stage
+  int kchunk;                 // input channels per block (cin, or a 64-multiple part of it when cin is large)
+  int kparts;                 // cin / kchunk: blocks per kernel offset
+  int chunks;                 // kchunk / 64 (at least 1): swizzle-span wide column blocks per block
   uint32_t idesc;
   uint32_t layout_type;  // UMMA smem layout code: 6 = 32B, 4 = 64B, 2 = 128B swizzle
   uint32_t tmem_cols;
+  uint32_t full_count;  // arrivals that complete a `full` barrier (1 for the TMA producer, 129 for cp.async)
   const float* bias;
   void* out;
   const void* residual;
@@ -118,6 +128,23 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* ba
       : "r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
+// Contiguous global -> shared copy (both 16-byte aligned, size a multiple of 16) signalled on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(uint64_t* bar, void* dst, const void* src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               :
+               : "r"(smem_u32(dst)), "l"((uint64_t)src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+// 16-byte asynchronous copy; src_bytes = 0 writes 16 zero bytes without reading global memory.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+// The barrier receives one arrival (counted in its expected arrivals) once all cp.async issued so far by this
+// thread have landed.
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
@@ -179,12 +206,34 @@ struct __align__(8) Shared {
   uint64_t empty[kMaxStages];
   uint64_t acc_full[kNumAcc];
   uint64_t acc_empty[kNumAcc];
-  int stage_k[kMaxStages];
+  uint64_t idx_full[2];
+  uint64_t idx_free[2];
+  int stage_cnt[kMaxStages];  // (offset, K part) blocks in the stage
   int stage_flags[kMaxStages];
   int acc_empty_tile[kNumAcc];
   uint32_t tmem_base;
   int abort_flag;
 };
+
+// Carved dynamic shared memory: [stages x (group A blocks | group B blocks)] aligned to 1024, two neighbour-id
+// buffers [kvol][128], the bias, the control block.
+struct Smem {
+  unsigned char* tiles;
+  int32_t* idx;
+  float* bias;
+  Shared* sh;
+  uint32_t stage_bytes;
+};
+__device__ __forceinline__ Smem carve_smem(unsigned char* raw, const TcParams& p) {
+  Smem s;
+  const uint32_t raw_addr = smem_u32(raw);
+  s.tiles = raw + ((1024u - (raw_addr & 1023u)) & 1023u);
+  s.stage_bytes = (uint32_t)p.group * (p.a_bytes + p.b_bytes);
+  s.idx = reinterpret_cast<int32_t*>(s.tiles + (size_t)p.stages * s.stage_bytes);
+  s.bias = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(s.idx) + 2 * (size_t)p.idx_bytes);
+  s.sh = reinterpret_cast<Shared*>(s.bias + ((p.cout + 1) & ~1));
+  return s;
+}
 
 template <bool kBf16>
 __device__ __forceinline__ void store_chunk(const uint32_t* acc, int n, const float* bias_s, int col0, void* out_row,
@@ -237,190 +286,303 @@ __device__ __forceinline__ void store_chunk(const uint32_t* acc, int n, const fl
   }
 }
 
-__global__ void __launch_bounds__(kTcThreads, 1)
-spconv_mm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    const TcParams p) {
-  extern __shared__ __align__(1024) unsigned char smem_raw[];
-  // dynamic smem: [stages x (A | B)] aligned to 1024, then the bias, then the control block
-  const uint32_t raw_addr = smem_u32(smem_raw);
-  unsigned char* tiles = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  const uint32_t stage_bytes = p.a_bytes + p.b_bytes;
-  float* bias_s = reinterpret_cast<float*>(tiles + (size_t)p.stages * stage_bytes);
-  Shared* sh = reinterpret_cast<Shared*>(bias_s + ((p.cout + 1) & ~1));
-  volatile int* abort_flag = &sh->abort_flag;
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
+// Barrier initialisation, bias staging and the TMEM allocation (by warp `mma_warp`); returns the TMEM base address.
+__device__ __forceinline__ uint32_t cta_setup(const TcParams& p, const Smem& s, int producer_warps, int mma_warp) {
+  Shared* sh = s.sh;
   if (threadIdx.x == 0) {
-    for (int s = 0; s < p.stages; ++s) mbar_init(&sh->full[s], 1), mbar_init(&sh->empty[s], 1);
+    for (int i = 0; i < p.stages; ++i) mbar_init(&sh->full[i], (int)p.full_count), mbar_init(&sh->empty[i], 1);
     for (int a = 0; a < kNumAcc; ++a) mbar_init(&sh->acc_full[a], 1), mbar_init(&sh->acc_empty[a], 4);
+    for (int b = 0; b < 2; ++b) mbar_init(&sh->idx_full[b], 1), mbar_init(&sh->idx_free[b], producer_warps);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int c = threadIdx.x; c < p.cout; c += kTcThreads) bias_s[c] = p.bias[c];
-  if (warp == 1) tmem_alloc(&sh->tmem_base, p.tmem_cols);
+  for (int c = threadIdx.x; c < p.cout; c += blockDim.x) s.bias[c] = p.bias[c];
+  if ((int)(threadIdx.x >> 5) == mma_warp) tmem_alloc(&sh->tmem_base, p.tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  const uint32_t tmem_base = sh->tmem_base;
+  return sh->tmem_base;
+}
 
-  if (warp == 0) {
-    // ------------------------------------------------------------------ producer
-    int stage = 0;
-    uint32_t phase = 0;
-    bool ok = true;
-    const uint32_t tx_bytes = (uint32_t)kTileRows * p.kchunk * 2 + (uint32_t)p.cout * p.kchunk * 2;
-    for (int tile = blockIdx.x; ok; tile += gridDim.x) {
-      const bool stop = tile >= p.num_tiles;
-      uint32_t mask = 0;
-      if (!stop) {
-        const int32_t* trow = p.table + (int64_t)tile * kTileRows + 4 * lane;
-        for (int k = 0; k < p.kvol; ++k) {
-          int4 r = __ldg(reinterpret_cast<const int4*>(trow + (int64_t)k * p.pitch));
-          bool any = (r.x >= 0) | (r.y >= 0) | (r.z >= 0) | (r.w >= 0);
-          if (__ballot_sync(0xffffffffu, any)) mask |= 1u << k;
-        }
-      }
-      if (stop || mask == 0) {  // a control stage: nothing to load
-        ok = mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag, 11);
-        if (!ok) break;
-        if (lane == 0) {
-          sh->stage_k[stage] = 0;
-          sh->stage_flags[stage] = stop ? kStop : (kEmptyTile | kFirst | kLast);
-          mbar_arrive(&sh->full[stage]);
-        }
-        __syncwarp();
-        if (++stage == p.stages) stage = 0, phase ^= 1;
-        if (stop) break;
-        continue;
-      }
-      const int first_k = __ffs(mask) - 1, last_k = 31 - __clz(mask);
-      for (uint32_t m = mask; m && ok; m &= m - 1) {
-        const int k = __ffs(m) - 1;
-        int4 r = __ldg(reinterpret_cast<const int4*>(p.table + (int64_t)k * p.pitch + (int64_t)tile * kTileRows +
-                                                     4 * lane));
-        // a missing neighbour (or a stale id beyond the gathered tensor) is addressed one row past the end:
-        // the TMA fills that row with zeros
-        r.x = (r.x < 0 || r.x >= p.n_in_rows) ? p.n_in_rows : r.x;
-        r.y = (r.y < 0 || r.y >= p.n_in_rows) ? p.n_in_rows : r.y;
-        r.z = (r.z < 0 || r.z >= p.n_in_rows) ? p.n_in_rows : r.z;
-        r.w = (r.w < 0 || r.w >= p.n_in_rows) ? p.n_in_rows : r.w;
-        for (int part = 0; part < p.kparts; ++part) {
-          ok = mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag, 12);
-          if (!ok) break;
-          unsigned char* a_dst = tiles + (size_t)stage * stage_bytes;
-          unsigned char* b_dst = a_dst + p.a_bytes;
-          const int x0 = part * p.kchunk;
-          if (lane == 0) {
-            sh->stage_k[stage] = k;
-            sh->stage_flags[stage] = ((k == first_k && part == 0) ? kFirst : 0) |
-                                     ((k == last_k && part == p.kparts - 1) ? kLast : 0);
-            mbar_arrive_expect_tx(&sh->full[stage], tx_bytes);
-            for (int c = 0; c < p.chunks; ++c)
-              tma_load_2d(&map_b, &sh->full[stage], b_dst + (size_t)c * p.cout * p.row_bytes, x0 + c * 64,
-                          k * p.cout);
-          }
-          __syncwarp();
-          for (int c = 0; c < p.chunks; ++c)
-            tma_gather4(&map_a, &sh->full[stage],
-                        a_dst + (size_t)c * kTileRows * p.row_bytes + 4 * lane * p.row_bytes, x0 + c * 64, r);
-          if (++stage == p.stages) stage = 0, phase ^= 1;
-        }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    int stage = 0, acc = 0;
-    uint32_t phase = 0, acc_phase = 0;
-    const uint32_t sbo = 8u * p.row_bytes;
-    const int ksteps = p.kchunk / 16;
-    bool ok = true;
-    while (ok) {
-      ok = mbar_wait(&sh->full[stage], phase, abort_flag, 21);
+// MMA issuer warp: consumes the stages in ring order until the stop stage.
+__device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint32_t tmem_base) {
+  Shared* sh = s.sh;
+  volatile int* abort_flag = &sh->abort_flag;
+  const int lane = threadIdx.x & 31;
+  int stage = 0, acc = 0;
+  uint32_t phase = 0, acc_phase = 0;
+  const uint32_t sbo = 8u * p.row_bytes;
+  const int ksteps = p.kchunk / 16;
+  bool ok = true;
+  while (ok) {
+    ok = mbar_wait(&sh->full[stage], phase, abort_flag, 21);
+    if (!ok) break;
+    fence_proxy_async();  // operand rows written through the generic proxy (cp.async) -> tensor-core reads
+    tc_fence_after();
+    const int flags = sh->stage_flags[stage];
+    if (flags & kStop) break;
+    if (flags & kFirst) {
+      ok = mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1, abort_flag, 22);
       if (!ok) break;
       tc_fence_after();
-      const int flags = sh->stage_flags[stage];
-      if (flags & kStop) break;
-      if (flags & kFirst) {
-        ok = mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1, abort_flag, 22);
-        if (!ok) break;
-        tc_fence_after();
-      }
-      if (lane == 0) {
-        if (flags & kEmptyTile) {
-          sh->acc_empty_tile[acc] = 1;
-          mbar_arrive(&sh->empty[stage]);
-          mbar_arrive(&sh->acc_full[acc]);
-        } else {
-          const uint32_t a_addr = smem_u32(tiles + (size_t)stage * stage_bytes);
-          const uint32_t b_addr = a_addr + p.a_bytes;
-          const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.cout);
+    }
+    if (lane == 0) {
+      if (flags & kEmptyTile) {
+        sh->acc_empty_tile[acc] = 1;
+        mbar_arrive(&sh->empty[stage]);
+        mbar_arrive(&sh->acc_full[acc]);
+      } else {
+        const uint32_t a_base = smem_u32(s.tiles + (size_t)stage * s.stage_bytes);
+        const uint32_t b_base = a_base + (uint32_t)p.group * p.a_bytes;
+        const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.cout);
+        const int cnt = sh->stage_cnt[stage];
+        uint32_t accumulate = (flags & kFirst) ? 0u : 1u;
+        for (int e = 0; e < cnt; ++e) {
+          const uint32_t a_addr = a_base + (uint32_t)e * p.a_bytes, b_addr = b_base + (uint32_t)e * p.b_bytes;
           for (int ks = 0; ks < ksteps; ++ks) {
             const int chunk = ks >> 2, within = (ks & 3) * 32;
             uint64_t da = make_desc(a_addr + chunk * kTileRows * p.row_bytes + within, sbo, p.layout_type);
             uint64_t db = make_desc(b_addr + chunk * p.cout * p.row_bytes + within, sbo, p.layout_type);
-            umma_f16(d_addr, da, db, p.idesc, ((flags & kFirst) && ks == 0) ? 0u : 1u);
-          }
-          umma_commit(&sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
-          if (flags & kLast) {
-            sh->acc_empty_tile[acc] = 0;
-            umma_commit(&sh->acc_full[acc]);
+            umma_f16(d_addr, da, db, p.idesc, accumulate);
+            accumulate = 1u;
           }
         }
+        umma_commit(&sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
+        if (flags & kLast) {
+          sh->acc_empty_tile[acc] = 0;
+          umma_commit(&sh->acc_full[acc]);
+        }
       }
-      __syncwarp();
-      if (flags & kLast) {
-        if (++acc == kNumAcc) acc = 0, acc_phase ^= 1;
-      }
-      if (++stage == p.stages) stage = 0, phase ^= 1;
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue (warps 2..5)
-    const int quad = warp & 3;  // TMEM lanes [32*quad, 32*quad+32) belong to this warp
-    int acc = 0;
-    uint32_t acc_phase = 0;
-    bool ok = true;
-    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-      ok = mbar_wait(&sh->acc_full[acc], acc_phase, abort_flag, 31);
-      if (!ok) break;
-      tc_fence_after();
-      const bool empty_tile = sh->acc_empty_tile[acc] != 0;
-      const int64_t row = (int64_t)tile * kTileRows + quad * 32 + lane;
-      const bool row_ok = row < p.m_max;
-      unsigned short* out_row = reinterpret_cast<unsigned short*>(p.out) + row * p.cout;
-      const unsigned short* res_row =
-          (p.residual && row_ok) ? reinterpret_cast<const unsigned short*>(p.residual) + row * p.cout : nullptr;
-      const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.cout);
-      for (int c0 = 0; c0 < p.cout; c0 += 32) {
-        const int n = p.cout - c0 >= 32 ? 32 : 16;
-        uint32_t v[32];
-        if (empty_tile) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) v[j] = 0u;
-        } else {
-          if (n == 32) tmem_ld32(taddr + c0, v);
-          else tmem_ld16(taddr + c0, v);
-          tmem_ld_wait();
-        }
-        if (row_ok) {
-          if (p.is_bf16) store_chunk<true>(v, n, bias_s, c0, out_row, res_row, p.relu);
-          else store_chunk<false>(v, n, bias_s, c0, out_row, res_row, p.relu);
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
+    __syncwarp();
+    if (flags & kLast) {
       if (++acc == kNumAcc) acc = 0, acc_phase ^= 1;
     }
+    if (++stage == p.stages) stage = 0, phase ^= 1;
   }
+}
 
-  // teardown: everyone meets, then the allocating warp returns the tensor memory
+// Epilogue warp `quad` (= warp index mod 4: it may touch TMEM lanes [32*quad, 32*quad + 32)).
+__device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, uint32_t tmem_base, int quad) {
+  Shared* sh = s.sh;
+  volatile int* abort_flag = &sh->abort_flag;
+  const int lane = threadIdx.x & 31;
+  int acc = 0;
+  uint32_t acc_phase = 0;
+  bool ok = true;
+  for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+    ok = mbar_wait(&sh->acc_full[acc], acc_phase, abort_flag, 31);
+    if (!ok) break;
+    tc_fence_after();
+    const bool empty_tile = sh->acc_empty_tile[acc] != 0;
+    const int64_t row = (int64_t)tile * kTileRows + quad * 32 + lane;
+    const bool row_ok = row < p.m_max;
+    unsigned short* out_row = reinterpret_cast<unsigned short*>(p.out) + row * p.cout;
+    const unsigned short* res_row =
+        (p.residual && row_ok) ? reinterpret_cast<const unsigned short*>(p.residual) + row * p.cout : nullptr;
+    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.cout);
+    for (int c0 = 0; c0 < p.cout; c0 += 32) {
+      const int n = p.cout - c0 >= 32 ? 32 : 16;
+      uint32_t v[32];
+      if (empty_tile) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = 0u;
+      } else {
+        if (n == 32) tmem_ld32(taddr + c0, v);
+        else tmem_ld16(taddr + c0, v);
+        tmem_ld_wait();
+      }
+      if (row_ok) {
+        if (p.is_bf16) store_chunk<true>(v, n, s.bias, c0, out_row, res_row, p.relu);
+        else store_chunk<false>(v, n, s.bias, c0, out_row, res_row, p.relu);
+      }
+    }
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
+    if (++acc == kNumAcc) acc = 0, acc_phase ^= 1;
+  }
+}
+
+// All roles meet, then the allocating warp returns the tensor memory.
+__device__ __forceinline__ void cta_teardown(const TcParams& p, uint32_t tmem_base, int mma_warp) {
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if ((int)(threadIdx.x >> 5) == mma_warp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
+}
+
+// Producer warps (1 for the TMA gather, 4 for cp.async).  Every producer warp walks the same tiles and stages; the
+// leader (warp 0, lane 0) additionally prefetches neighbour ids, publishes the stage descriptors and loads B.
+template <bool kTma>
+__device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, const CUtensorMap* map_a,
+                                              const CUtensorMap* map_b, int pw) {
+  Shared* sh = s.sh;
+  volatile int* abort_flag = &sh->abort_flag;
+  const int lane = threadIdx.x & 31;
+  const bool leader = pw == 0 && lane == 0;
+  const int pt = pw * 32 + lane;  // producer thread 0..127 (cp.async mapping)
+  int stage = 0;
+  uint32_t phase = 0;
+  bool ok = true;
+  const uint32_t a_tx = (uint32_t)kTileRows * p.kchunk * 2, b_tx = (uint32_t)p.cout * p.kchunk * 2;
+  const int ids_per_tile = p.kvol * kTileRows;
+  const int cpr = p.kchunk / 8;  // 16-byte pieces per gathered row
+  const int swz_shift = p.row_bytes == 128 ? 0 : p.row_bytes == 64 ? 1 : 2;
+  const int swz_mask = p.row_bytes == 128 ? 7 : p.row_bytes == 64 ? 3 : 1;
+  int buf = 0;
+  uint32_t idx_phase = 0;   // bit b: parity to wait for on idx_full[b]
+  uint32_t free_phase = 0;  // bit b: parity to wait for on idx_free[b] (leader only)
+  if (leader && (int)blockIdx.x < p.num_tiles) {
+    mbar_arrive_expect_tx(&sh->idx_full[0], p.idx_bytes);
+    bulk_load_1d(&sh->idx_full[0], s.idx, p.table + (int64_t)blockIdx.x * ids_per_tile, p.idx_bytes);
+  }
+  for (int tile = blockIdx.x; ok; tile += gridDim.x) {
+    const bool stop = tile >= p.num_tiles;
+    uint32_t mask = 0;
+    const int32_t* ids = s.idx + (size_t)buf * ids_per_tile;
+    if (!stop) {
+      // prefetch the ids of this CTA's next tile into the other buffer once all producer warps have released it
+      const int next = tile + gridDim.x;
+      if (leader && next < p.num_tiles) {
+        bool free_ok = true;
+        if (tile != (int)blockIdx.x) {
+          free_ok = mbar_wait(&sh->idx_free[buf ^ 1], (free_phase >> (buf ^ 1)) & 1u, abort_flag, 14);
+          free_phase ^= 1u << (buf ^ 1);
+        }
+        if (free_ok) {
+          mbar_arrive_expect_tx(&sh->idx_full[buf ^ 1], p.idx_bytes);
+          bulk_load_1d(&sh->idx_full[buf ^ 1], s.idx + (size_t)(buf ^ 1) * ids_per_tile,
+                       p.table + (int64_t)next * ids_per_tile, p.idx_bytes);
+        }
+      }
+      __syncwarp();
+      ok = mbar_wait(&sh->idx_full[buf], (idx_phase >> buf) & 1u, abort_flag, 13);
+      if (!ok) break;
+      idx_phase ^= 1u << buf;
+      for (int k = 0; k < p.kvol; ++k) {
+        int4 r = *reinterpret_cast<const int4*>(ids + k * kTileRows + 4 * lane);
+        bool any = (r.x >= 0) | (r.y >= 0) | (r.z >= 0) | (r.w >= 0);
+        if (__ballot_sync(0xffffffffu, any)) mask |= 1u << k;
+      }
+    }
+    if (stop || mask == 0) {  // a control stage: nothing to load
+      ok = mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag, 11);
+      if (!ok) break;
+      if (leader) {
+        sh->stage_cnt[stage] = 0;
+        sh->stage_flags[stage] = stop ? kStop : (kEmptyTile | kFirst | kLast);
+        mbar_arrive(&sh->full[stage]);
+      }
+      if (!kTma) mbar_arrive(&sh->full[stage]);
+      __syncwarp();
+      if (++stage == p.stages) stage = 0, phase ^= 1;
+      if (stop) break;
+    }
+    // data stages: up to `group` offsets per stage (one offset, one K part when Cin is split)
+    uint32_t m = mask;
+    int part = 0;
+    while (m && ok) {
+      ok = mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag, 12);
+      if (!ok) break;
+      const bool first = (m == mask) && part == 0;
+      uint32_t take = 0, rest = m;
+      int cnt = 0;
+      if (p.kparts == 1) {
+        for (; cnt < p.group && rest; ++cnt) take |= rest & (0u - rest), rest &= rest - 1;
+      } else {
+        take = m & (0u - m), cnt = 1;
+        if (part == p.kparts - 1) rest &= rest - 1;
+      }
+      const int x0 = part * p.kchunk;
+      unsigned char* a_base = s.tiles + (size_t)stage * s.stage_bytes;
+      unsigned char* b_base = a_base + (size_t)p.group * p.a_bytes;
+      if (leader) {
+        sh->stage_cnt[stage] = cnt;
+        sh->stage_flags[stage] = (first ? kFirst : 0) | (rest == 0 ? kLast : 0);
+        mbar_arrive_expect_tx(&sh->full[stage], (uint32_t)cnt * (b_tx + (kTma ? a_tx : 0u)));
+        int e = 0;
+        for (uint32_t t = take; t; t &= t - 1, ++e) {
+          const int k = __ffs(t) - 1;
+          for (int c = 0; c < p.chunks; ++c)
+            tma_load_2d(map_b, &sh->full[stage], b_base + (size_t)e * p.b_bytes + (size_t)c * p.cout * p.row_bytes,
+                        x0 + c * 64, k * p.cout);
+        }
+      }
+      __syncwarp();
+      int e = 0;
+      for (uint32_t t = take; t; t &= t - 1, ++e) {
+        const int k = __ffs(t) - 1;
+        unsigned char* a_blk = a_base + (size_t)e * p.a_bytes;
+        if (kTma) {
+          int4 r = *reinterpret_cast<const int4*>(ids + k * kTileRows + 4 * lane);
+          // a missing neighbour (or a stale id beyond the gathered tensor) is addressed one row past the end:
+          // the TMA fills that row with zeros
+          r.x = (r.x < 0 || r.x >= p.n_in_rows) ? p.n_in_rows : r.x;
+          r.y = (r.y < 0 || r.y >= p.n_in_rows) ? p.n_in_rows : r.y;
+          r.z = (r.z < 0 || r.z >= p.n_in_rows) ? p.n_in_rows : r.z;
+          r.w = (r.w < 0 || r.w >= p.n_in_rows) ? p.n_in_rows : r.w;
+          for (int c = 0; c < p.chunks; ++c)
+            tma_gather4(map_a, &sh->full[stage], a_blk + (size_t)c * kTileRows * p.row_bytes + 4 * lane * p.row_bytes,
+                        x0 + c * 64, r);
+        } else {
+          // consecutive threads take consecutive 16-byte pieces of a row: coalesced global reads, conflict-free
+          // shared-memory writes; the piece index is XOR-swizzled with the row as the tensor core expects
+          const uint32_t a_addr = smem_u32(a_blk);
+          for (int it = 0; it < cpr; ++it) {
+            const int q = it * kTileRows + pt;
+            const int row = q / cpr, j = q - row * cpr;
+            const int id = ids[k * kTileRows + row];
+            const bool valid = id >= 0 && id < p.n_in_rows;
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(p.in_feats) +
+                                       ((size_t)(valid ? id : 0) * p.cin + x0 + j * 8) * 2;
+            const int blk = j >> 3, jj = j & 7;
+            const uint32_t dst = a_addr + blk * kTileRows * p.row_bytes + row * p.row_bytes +
+                                 ((jj ^ ((row >> swz_shift) & swz_mask)) << 4);
+            cp_async_16(dst, src, valid ? 16u : 0u);
+          }
+        }
+      }
+      if (!kTma) cp_async_arrive(&sh->full[stage]);
+      if (p.kparts > 1 && ++part == p.kparts) part = 0;
+      m = rest;
+      if (++stage == p.stages) stage = 0, phase ^= 1;
+    }
+    if (!stop) {  // this warp is done with the id buffer of the tile
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->idx_free[buf]);
+      buf ^= 1;
+    }
+  }
+}
+
+// TMA-gather variant: warp 0 producer, warp 1 MMA, warps 2-5 epilogue.
+__global__ void __launch_bounds__(192, 1)
+spconv_mm_tc_tma_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                        const TcParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const Smem s = carve_smem(smem_raw, p);
+  const int warp = threadIdx.x >> 5;
+  const uint32_t tmem_base = cta_setup(p, s, 1, 1);
+  if (warp == 0) producer_role<true>(p, s, &map_a, &map_b, 0);
+  else if (warp == 1) mma_role(p, s, tmem_base);
+  else epilogue_role(p, s, tmem_base, warp & 3);
+  cta_teardown(p, tmem_base, 1);
+}
+
+// cp.async variant: warps 0-3 producers, warp 4 MMA, warps 5-8 epilogue.
+__global__ void __launch_bounds__(288, 1)
+spconv_mm_tc_cpasync_kernel(const __grid_constant__ CUtensorMap map_b, const TcParams p) {
+  extern __shared__ __align__(1024) unsigned char smem_raw[];
+  const Smem s = carve_smem(smem_raw, p);
+  const int warp = threadIdx.x >> 5;
+  const uint32_t tmem_base = cta_setup(p, s, 4, 4);
+  if (warp < 4) producer_role<false>(p, s, nullptr, &map_b, warp);
+  else if (warp == 4) mma_role(p, s, tmem_base);
+  else epilogue_role(p, s, tmem_base, warp & 3);
+  cta_teardown(p, tmem_base, 4);
 }
 
 // ---- host --------------------------------------------------------------------------------------------------------
@@ -478,6 +640,7 @@ void spconv_mm_tc_release(d3d_spconv_mm_s* h) {
 
 int launch_spconv_mm_tc(const MmLaunch& a) {
   d3d_spconv_mm_s* h = const_cast<d3d_spconv_mm_s*>(a.h);
+  const bool use_tma_gather = h->kernel_choice == 3;
   const int cin = h->p.in_channels, cout = h->p.out_channels, kvol = h->p.kernel_vol;
   const int64_t m_max = h->p.max_num_act_out;
   if (m_max == 0) return D3D_OK;
@@ -492,22 +655,24 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
     st->map_b_ok = make_map(&st->map_b, a.dtype, h->wt_dev, cin, (uint64_t)kvol * cout, box_cols, cout);
     D3D_REQUIRE(st->map_b_ok, D3D_ERR_CUDA);
   }
-  CUtensorMap map_a;
-  D3D_REQUIRE(make_map(&map_a, a.dtype, a.in_feats, cin, (uint64_t)a.max_num_act_in, box_cols, 1), D3D_ERR_CUDA);
 
   TcParams p;
   p.table = a.table;
-  p.pitch = (m_max + 127) / 128 * 128;
+  p.in_feats = a.in_feats;
   p.m_max = m_max;
   p.n_in_rows = (int32_t)a.max_num_act_in;
   p.kvol = kvol, p.cin = cin, p.cout = cout;
-  p.num_tiles = (int)(p.pitch / kTileRows);
+  p.num_tiles = (int)((m_max + kTileRows - 1) / kTileRows);
   p.row_bytes = (int)box_cols * 2;
-  // a stage holds `kchunk` input channels of one kernel offset; split large Cin so that at least two stages fit
-  const size_t ctrl = 1024 + align_up((size_t)cout * 4 + 8, 16) + sizeof(Shared);
+  p.idx_bytes = (uint32_t)kvol * kTileRows * 4;
+  p.full_count = use_tma_gather ? 1u : 129u;
+  // shared-memory budget: 227 KB per CTA minus alignment slack, the two neighbour-id buffers, bias and control block
+  const size_t ctrl = 1024 + 2 * (size_t)p.idx_bytes + align_up((size_t)cout * 4 + 8, 16) + sizeof(Shared);
+  const size_t budget = 227 * 1024 - ctrl;
+  // a block holds `kchunk` input channels of one kernel offset; split large Cin so that at least two stages fit
   int kchunk = cin;
-  while (kchunk > 64 && 2 * (align_up((size_t)kTileRows * kchunk * 2, 1024) + align_up((size_t)cout * kchunk * 2, 1024)) >
-                            200 * 1024 - ctrl)
+  while (kchunk > 64 &&
+         2 * (align_up((size_t)kTileRows * kchunk * 2, 1024) + align_up((size_t)cout * kchunk * 2, 1024)) > budget)
     kchunk /= 2;
   p.kchunk = kchunk;
   p.kparts = cin / kchunk;
@@ -525,26 +690,41 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.residual = a.residual;
   p.relu = a.relu;
   p.is_bf16 = a.dtype == D3D_BF16;
-  // shared memory: as many stages as fit in ~200 KB (at least 2, at most kMaxStages); never less than 120 KB so that
-  // one CTA owns an SM and its tensor memory
-  const size_t stage_bytes = (size_t)p.a_bytes + p.b_bytes;
-  int stages = (int)((200 * 1024 - ctrl) / stage_bytes);
+  // several offsets share a stage when their blocks are small, so that the per-stage hand-over cost is amortised
+  const size_t blk_bytes = (size_t)p.a_bytes + p.b_bytes;
+  int group = 1;
+  if (p.kparts == 1) {
+    group = (int)(40 * 1024 / blk_bytes);
+    group = group < 1 ? 1 : group > kMaxGroup ? kMaxGroup : group;
+  }
+  p.group = group;
+  const size_t stage_bytes = (size_t)group * blk_bytes;
+  int stages = (int)(budget / stage_bytes);
   stages = stages > kMaxStages ? kMaxStages : stages;
   D3D_REQUIRE(stages >= 2, D3D_ERR_TOO_LARGE);
   p.stages = stages;
   size_t smem = ctrl + (size_t)stages * stage_bytes;
-  if (smem < 120 * 1024) smem = 120 * 1024;
+  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it owns the SM's tensor memory
   static bool attr_set[64] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return D3D_ERR_CUDA;
   if (!attr_set[dev]) {
-    if (cudaFuncSetAttribute(spconv_mm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(spconv_mm_tc_tma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(spconv_mm_tc_cpasync_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+            cudaSuccess)
       return D3D_ERR_CUDA;
     attr_set[dev] = true;
   }
-  int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
-  spconv_mm_tc_kernel<<<grid, kTcThreads, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(map_a, st->map_b, p);
+  const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(a.stream);
+  if (use_tma_gather) {
+    CUtensorMap map_a;
+    D3D_REQUIRE(make_map(&map_a, a.dtype, a.in_feats, cin, (uint64_t)a.max_num_act_in, box_cols, 1), D3D_ERR_CUDA);
+    spconv_mm_tc_tma_kernel<<<grid, 192, smem, stream>>>(map_a, st->map_b, p);
+  } else {
+    spconv_mm_tc_cpasync_kernel<<<grid, 288, smem, stream>>>(st->map_b, p);
+  }
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }

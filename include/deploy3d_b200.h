@@ -148,7 +148,7 @@ int d3d_spconv_mm_serialize(d3d_spconv_mm_t handle, void* buffer, size_t* len);
 int d3d_spconv_mm_configure(d3d_spconv_mm_t handle, int dtype);
 int d3d_spconv_mm_destroy(d3d_spconv_mm_t handle);
 /* The reference needs no workspace (mm_trt.cu:143-148); this implementation keeps an
- * output-stationary neighbour table [kVol, maxNumActOut] there. */
+ * output-stationary neighbour table [ceil(maxNumActOut/128), kVol, 128] there. */
 int d3d_spconv_mm_workspace(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int n_in, size_t* bytes);
 /* enqueue (mm_trt.cu:149-205) == prepare + run below with the table in `workspace`. */
 int d3d_spconv_mm_enqueue(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int n_in,
@@ -164,8 +164,9 @@ int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_num_act_out, 
 int d3d_spconv_mm_run(d3d_spconv_mm_t handle, int dtype, const void* in_feats, int64_t max_num_act_in,
                       const int32_t* num_act_out, const void* table, void* out_feats,
                       const d3d_spconv_mm_epilogue* epilogue, void* stream);
-/* Kernel choice for tests and profiling: 0 = automatic, 1 = SIMT fp32-FMA path, 2 = tcgen05 path
- * (fails with D3D_ERR_INVALID_ARGUMENT at run time when the shape is not eligible). */
+/* Kernel choice for tests and profiling: 0 = automatic, 1 = SIMT fp32-FMA path, 2 = tcgen05 path with the cp.async
+ * row gather (what "automatic" picks for eligible shapes), 3 = tcgen05 path with the TMA gather4 row gather
+ * (2 and 3 fail with D3D_ERR_INVALID_ARGUMENT at run time when the shape is not eligible). */
 int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t handle, int which);
 
 /* ---------------------------------------------------------------------------------------------
