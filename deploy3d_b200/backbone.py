@@ -97,7 +97,8 @@ class SparseNet:
                 'conv' layer that creates the set); missing entries default to `default_cap`
     """
 
-    def __init__(self, layers, spatial, caps, dtype=torch.float16, device="cuda:0", seed=0, kernel=0):
+    def __init__(self, layers, spatial, caps, dtype=torch.float16, device="cuda:0", seed=0, kernel=0,
+                 pad_input=True):
         self.layers, self.device, self.dtype = layers, torch.device(device), dtype
         self.kernel = kernel
         weights = make_weights(layers, seed)
@@ -155,8 +156,18 @@ class SparseNet:
                     out_set, in_set = rb.out_set, rb.in_set
                 assert in_set == cur, "layer %d expects voxel set %s but the data is on %s" % (li, in_set, cur)
                 w, b = weights[li]
+                cin = L.cin
+                if li == 0:
+                    # a first layer with 4 or 5 input channels is run with its input zero-padded to 16 channels (and
+                    # zero weight rows), which makes it eligible for the tensor-core kernel; the result is unchanged
+                    self.in_channels = cin
+                    if dtype != torch.float32 and cin % 16 != 0 and pad_input:
+                        self.in_channels = (cin + 15) // 16 * 16
+                        wp = np.zeros((w.shape[0], self.in_channels, w.shape[2]), dtype=np.float32)
+                        wp[:, :cin] = w
+                        w, cin = wp, self.in_channels
                 plug = deserialize_plugin("SPConvMM", data_s_spconv_mm(
-                    L.ksize, L.cin, L.cout, self.sets[out_set]["cap"], L.kind == "subm", L.kind == "inverse", w, b))
+                    L.ksize, cin, L.cout, self.sets[out_set]["cap"], L.kind == "subm", L.kind == "inverse", w, b))
                 plug.configure(dtype)
                 plug.set_kernel(kernel)
                 out_buf = torch.zeros((self.sets[out_set]["cap"], L.cout), dtype=dtype, device=self.device)

@@ -60,6 +60,7 @@ struct TcParams {
   uint32_t layout_type;  // UMMA smem layout code: 6 = 32B, 4 = 64B, 2 = 128B swizzle
   uint32_t tmem_cols;
   uint32_t full_count;  // arrivals that complete a `full` barrier (1 for the TMA producer, 129 for cp.async)
+  int b_resident;       // all kvol weight blocks stay in smem for the whole kernel (small layers)
   const float* bias;
   void* out;
   const void* residual;
@@ -208,8 +209,10 @@ struct __align__(8) Shared {
   uint64_t acc_empty[kNumAcc];
   uint64_t idx_full[2];
   uint64_t idx_free[2];
+  uint64_t b_ready;           // resident weights have landed
   int stage_cnt[kMaxStages];  // (offset, K part) blocks in the stage
   int stage_flags[kMaxStages];
+  unsigned char stage_k[kMaxStages][kMaxGroup];  // kernel offset of each block
   int acc_empty_tile[kNumAcc];
   uint32_t tmem_base;
   int abort_flag;
@@ -219,6 +222,7 @@ struct __align__(8) Shared {
 // buffers [kvol][128], the bias, the control block.
 struct Smem {
   unsigned char* tiles;
+  unsigned char* bres;  // resident weights [kvol][b_bytes] (when p.b_resident)
   int32_t* idx;
   float* bias;
   Shared* sh;
@@ -228,8 +232,9 @@ __device__ __forceinline__ Smem carve_smem(unsigned char* raw, const TcParams& p
   Smem s;
   const uint32_t raw_addr = smem_u32(raw);
   s.tiles = raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  s.stage_bytes = (uint32_t)p.group * (p.a_bytes + p.b_bytes);
-  s.idx = reinterpret_cast<int32_t*>(s.tiles + (size_t)p.stages * s.stage_bytes);
+  s.stage_bytes = (uint32_t)p.group * (p.a_bytes + (p.b_resident ? 0u : p.b_bytes));
+  s.bres = s.tiles + (size_t)p.stages * s.stage_bytes;
+  s.idx = reinterpret_cast<int32_t*>(s.bres + (p.b_resident ? (size_t)p.kvol * p.b_bytes : 0));
   s.bias = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(s.idx) + 2 * (size_t)p.idx_bytes);
   s.sh = reinterpret_cast<Shared*>(s.bias + ((p.cout + 1) & ~1));
   return s;
@@ -293,6 +298,7 @@ __device__ __forceinline__ uint32_t cta_setup(const TcParams& p, const Smem& s, 
     for (int i = 0; i < p.stages; ++i) mbar_init(&sh->full[i], (int)p.full_count), mbar_init(&sh->empty[i], 1);
     for (int a = 0; a < kNumAcc; ++a) mbar_init(&sh->acc_full[a], 1), mbar_init(&sh->acc_empty[a], 4);
     for (int b = 0; b < 2; ++b) mbar_init(&sh->idx_full[b], 1), mbar_init(&sh->idx_free[b], producer_warps);
+    mbar_init(&sh->b_ready, 1);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -304,6 +310,24 @@ __device__ __forceinline__ uint32_t cta_setup(const TcParams& p, const Smem& s, 
   return sh->tmem_base;
 }
 
+// Low word of a K-major operand descriptor: start address in 16-byte units, leading byte offset 1 (unused for the
+// swizzled K-major layouts).  Advancing the operand by `d` bytes adds d / 16 to this word.
+__device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16); }
+
+// The kSteps tcgen05.mma instructions (K = 16 each) of one (offset, K part) block.
+template <int kSteps>
+__device__ __forceinline__ void issue_block(uint32_t d_addr, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                            uint32_t idesc, uint32_t& accumulate, uint32_t cs_a, uint32_t cs_b) {
+#pragma unroll
+  for (int ks = 0; ks < kSteps; ++ks) {
+    const uint32_t within = (uint32_t)(ks & 3) * 2u;  // 32 bytes per K step inside the swizzle span
+    const uint64_t da = ((uint64_t)desc_hi << 32) | (a_lo + (uint32_t)(ks >> 2) * cs_a + within);
+    const uint64_t db = ((uint64_t)desc_hi << 32) | (b_lo + (uint32_t)(ks >> 2) * cs_b + within);
+    umma_f16(d_addr, da, db, idesc, accumulate);
+    accumulate = 1u;
+  }
+}
+
 // MMA issuer warp: consumes the stages in ring order until the stop stage.
 __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint32_t tmem_base) {
   Shared* sh = s.sh;
@@ -311,13 +335,17 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
   const int lane = threadIdx.x & 31;
   int stage = 0, acc = 0;
   uint32_t phase = 0, acc_phase = 0;
-  const uint32_t sbo = 8u * p.row_bytes;
   const int ksteps = p.kchunk / 16;
+  // descriptor pieces that never change: high word (group stride, version, swizzle), and the distance in 16-byte
+  // units between the 64-column blocks of the A and the B operand
+  const uint32_t desc_hi = ((8u * p.row_bytes) >> 4) | (1u << 14) | (p.layout_type << 29);
+  const uint32_t cs_a = (uint32_t)(kTileRows * p.row_bytes) >> 4, cs_b = (uint32_t)(p.cout * p.row_bytes) >> 4;
   bool ok = true;
+  if (p.b_resident) ok = mbar_wait(&sh->b_ready, 0, abort_flag, 23);
+  const uint32_t bres_addr = smem_u32(s.bres);
   while (ok) {
     ok = mbar_wait(&sh->full[stage], phase, abort_flag, 21);
     if (!ok) break;
-    fence_proxy_async();  // operand rows written through the generic proxy (cp.async) -> tensor-core reads
     tc_fence_after();
     const int flags = sh->stage_flags[stage];
     if (flags & kStop) break;
@@ -327,6 +355,7 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
       tc_fence_after();
     }
     if (lane == 0) {
+      fence_proxy_async();  // rows written by cp.async (generic proxy) -> tensor-core reads (async proxy)
       if (flags & kEmptyTile) {
         sh->acc_empty_tile[acc] = 1;
         mbar_arrive(&sh->empty[stage]);
@@ -338,13 +367,15 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
         const int cnt = sh->stage_cnt[stage];
         uint32_t accumulate = (flags & kFirst) ? 0u : 1u;
         for (int e = 0; e < cnt; ++e) {
-          const uint32_t a_addr = a_base + (uint32_t)e * p.a_bytes, b_addr = b_base + (uint32_t)e * p.b_bytes;
-          for (int ks = 0; ks < ksteps; ++ks) {
-            const int chunk = ks >> 2, within = (ks & 3) * 32;
-            uint64_t da = make_desc(a_addr + chunk * kTileRows * p.row_bytes + within, sbo, p.layout_type);
-            uint64_t db = make_desc(b_addr + chunk * p.cout * p.row_bytes + within, sbo, p.layout_type);
-            umma_f16(d_addr, da, db, p.idesc, accumulate);
-            accumulate = 1u;
+          const uint32_t a_addr = a_base + (uint32_t)e * p.a_bytes;
+          const uint32_t b_addr = p.b_resident ? bres_addr + (uint32_t)sh->stage_k[stage][e] * p.b_bytes
+                                               : b_base + (uint32_t)e * p.b_bytes;
+          const uint32_t a_lo = desc_lo(a_addr), b_lo = desc_lo(b_addr);
+          switch (ksteps) {
+            case 1: issue_block<1>(d_addr, a_lo, b_lo, desc_hi, p.idesc, accumulate, cs_a, cs_b); break;
+            case 2: issue_block<2>(d_addr, a_lo, b_lo, desc_hi, p.idesc, accumulate, cs_a, cs_b); break;
+            case 4: issue_block<4>(d_addr, a_lo, b_lo, desc_hi, p.idesc, accumulate, cs_a, cs_b); break;
+            default: issue_block<8>(d_addr, a_lo, b_lo, desc_hi, p.idesc, accumulate, cs_a, cs_b); break;
           }
         }
         umma_commit(&sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
@@ -414,6 +445,31 @@ __device__ __forceinline__ void cta_teardown(const TcParams& p, uint32_t tmem_ba
   }
 }
 
+// Copy the 32 operand rows [row0, row0 + 32) of one (offset, K part) block with 16-byte cp.async pieces.
+// kPieces = 16-byte pieces per row (row bytes / 16).  Consecutive lanes take consecutive pieces of a row, so one
+// warp instruction reads 32 / kPieces whole rows: few cache lines per instruction on the global side, whole
+// 128-byte lines on the shared side.  Piece j of row r lands at the XOR-swizzled position the tensor core expects;
+// pieces 8.. belong to the next 64-column block (`blk_stride` bytes further).
+template <int kPieces>
+__device__ __forceinline__ void copy_rows(uint32_t a_addr, const int32_t* ids_k, const unsigned char* feats,
+                                          int row_src_bytes, int n_in_rows, int row0, int lane, int row_bytes,
+                                          int swz_shift, int swz_mask, uint32_t blk_stride) {
+  constexpr int kRowsPerInstr = 32 / kPieces;
+  const int j = lane % kPieces, rsub = lane / kPieces;
+  int id[kPieces];
+#pragma unroll
+  for (int it = 0; it < kPieces; ++it) id[it] = ids_k[row0 + it * kRowsPerInstr + rsub];
+  const uint32_t dst0 = a_addr + (uint32_t)(j >> 3) * blk_stride;
+#pragma unroll
+  for (int it = 0; it < kPieces; ++it) {
+    const int row = row0 + it * kRowsPerInstr + rsub;
+    const bool valid = id[it] >= 0 && id[it] < n_in_rows;
+    const unsigned char* src = feats + (size_t)(valid ? id[it] : 0) * row_src_bytes + j * 16;
+    const uint32_t dst = dst0 + row * row_bytes + ((((uint32_t)j & 7u) ^ (uint32_t)((row >> swz_shift) & swz_mask)) << 4);
+    cp_async_16(dst, src, valid ? 16u : 0u);
+  }
+}
+
 // Producer warps (1 for the TMA gather, 4 for cp.async).  Every producer warp walks the same tiles and stages; the
 // leader (warp 0, lane 0) additionally prefetches neighbour ids, publishes the stage descriptors and loads B.
 template <bool kTma>
@@ -423,7 +479,6 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   volatile int* abort_flag = &sh->abort_flag;
   const int lane = threadIdx.x & 31;
   const bool leader = pw == 0 && lane == 0;
-  const int pt = pw * 32 + lane;  // producer thread 0..127 (cp.async mapping)
   int stage = 0;
   uint32_t phase = 0;
   bool ok = true;
@@ -438,6 +493,13 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   if (leader && (int)blockIdx.x < p.num_tiles) {
     mbar_arrive_expect_tx(&sh->idx_full[0], p.idx_bytes);
     bulk_load_1d(&sh->idx_full[0], s.idx, p.table + (int64_t)blockIdx.x * ids_per_tile, p.idx_bytes);
+    if (p.b_resident) {  // all weight blocks once, in the layout the per-stage loads would have produced
+      mbar_arrive_expect_tx(&sh->b_ready, (uint32_t)p.kvol * b_tx);
+      for (int k = 0; k < p.kvol; ++k)
+        for (int c = 0; c < p.chunks; ++c)
+          tma_load_2d(map_b, &sh->b_ready, s.bres + (size_t)k * p.b_bytes + (size_t)c * p.cout * p.row_bytes, c * 64,
+                      k * p.cout);
+    }
   }
   for (int tile = blockIdx.x; ok; tile += gridDim.x) {
     const bool stop = tile >= p.num_tiles;
@@ -502,13 +564,18 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
       if (leader) {
         sh->stage_cnt[stage] = cnt;
         sh->stage_flags[stage] = (first ? kFirst : 0) | (rest == 0 ? kLast : 0);
-        mbar_arrive_expect_tx(&sh->full[stage], (uint32_t)cnt * (b_tx + (kTma ? a_tx : 0u)));
         int e = 0;
+        for (uint32_t t = take; t; t &= t - 1, ++e) sh->stage_k[stage][e] = (unsigned char)(__ffs(t) - 1);
+        const uint32_t tx = (uint32_t)cnt * ((p.b_resident ? 0u : b_tx) + (kTma ? a_tx : 0u));
+        if (tx) mbar_arrive_expect_tx(&sh->full[stage], tx);
+        else mbar_arrive(&sh->full[stage]);
+        e = 0;
         for (uint32_t t = take; t; t &= t - 1, ++e) {
           const int k = __ffs(t) - 1;
-          for (int c = 0; c < p.chunks; ++c)
-            tma_load_2d(map_b, &sh->full[stage], b_base + (size_t)e * p.b_bytes + (size_t)c * p.cout * p.row_bytes,
-                        x0 + c * 64, k * p.cout);
+          if (!p.b_resident)
+            for (int c = 0; c < p.chunks; ++c)
+              tma_load_2d(map_b, &sh->full[stage],
+                          b_base + (size_t)e * p.b_bytes + (size_t)c * p.cout * p.row_bytes, x0 + c * 64, k * p.cout);
         }
       }
       __syncwarp();
@@ -528,24 +595,28 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
             tma_gather4(map_a, &sh->full[stage], a_blk + (size_t)c * kTileRows * p.row_bytes + 4 * lane * p.row_bytes,
                         x0 + c * 64, r);
         } else {
-          // consecutive threads take consecutive 16-byte pieces of a row: coalesced global reads, conflict-free
-          // shared-memory writes; the piece index is XOR-swizzled with the row as the tensor core expects
+          // this warp copies rows [32 * pw, 32 * pw + 32) of the block
+          const unsigned char* feats = reinterpret_cast<const unsigned char*>(p.in_feats) + (size_t)x0 * 2;
+          const int32_t* ids_k = ids + k * kTileRows;
           const uint32_t a_addr = smem_u32(a_blk);
-          for (int it = 0; it < cpr; ++it) {
-            const int q = it * kTileRows + pt;
-            const int row = q / cpr, j = q - row * cpr;
-            const int id = ids[k * kTileRows + row];
-            const bool valid = id >= 0 && id < p.n_in_rows;
-            const unsigned char* src = reinterpret_cast<const unsigned char*>(p.in_feats) +
-                                       ((size_t)(valid ? id : 0) * p.cin + x0 + j * 8) * 2;
-            const int blk = j >> 3, jj = j & 7;
-            const uint32_t dst = a_addr + blk * kTileRows * p.row_bytes + row * p.row_bytes +
-                                 ((jj ^ ((row >> swz_shift) & swz_mask)) << 4);
-            cp_async_16(dst, src, valid ? 16u : 0u);
+          switch (cpr) {
+            case 2:
+              copy_rows<2>(a_addr, ids_k, feats, p.cin * 2, p.n_in_rows, 32 * pw, lane, 32, swz_shift, swz_mask, 0);
+              break;
+            case 4:
+              copy_rows<4>(a_addr, ids_k, feats, p.cin * 2, p.n_in_rows, 32 * pw, lane, 64, swz_shift, swz_mask, 0);
+              break;
+            case 8:
+              copy_rows<8>(a_addr, ids_k, feats, p.cin * 2, p.n_in_rows, 32 * pw, lane, 128, swz_shift, swz_mask, 0);
+              break;
+            default:
+              copy_rows<16>(a_addr, ids_k, feats, p.cin * 2, p.n_in_rows, 32 * pw, lane, 128, swz_shift, swz_mask,
+                            kTileRows * 128);
+              break;
           }
         }
       }
-      if (!kTma) cp_async_arrive(&sh->full[stage]);
+      if (!kTma) cp_async_arrive(&sh->full[stage]);  // one arrival per producer thread once its copies land
       if (p.kparts > 1 && ++part == p.kparts) part = 0;
       m = rest;
       if (++stage == p.stages) stage = 0, phase ^= 1;
@@ -665,7 +736,7 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.num_tiles = (int)((m_max + kTileRows - 1) / kTileRows);
   p.row_bytes = (int)box_cols * 2;
   p.idx_bytes = (uint32_t)kvol * kTileRows * 4;
-  p.full_count = use_tma_gather ? 1u : 129u;
+  p.full_count = use_tma_gather ? 1u : 129u;  // leader + (cp.async) every producer thread
   // shared-memory budget: 227 KB per CTA minus alignment slack, the two neighbour-id buffers, bias and control block
   const size_t ctrl = 1024 + 2 * (size_t)p.idx_bytes + align_up((size_t)cout * 4 + 8, 16) + sizeof(Shared);
   const size_t budget = 227 * 1024 - ctrl;
@@ -690,20 +761,24 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.residual = a.residual;
   p.relu = a.relu;
   p.is_bf16 = a.dtype == D3D_BF16;
+  // small layers keep all weight blocks in shared memory for the whole kernel instead of reloading one per stage
+  const size_t bres_bytes = (size_t)kvol * p.b_bytes;
+  p.b_resident = (p.kparts == 1 && bres_bytes <= 64 * 1024) ? 1 : 0;
+  const size_t ring_budget = budget - (p.b_resident ? bres_bytes : 0);
   // several offsets share a stage when their blocks are small, so that the per-stage hand-over cost is amortised
-  const size_t blk_bytes = (size_t)p.a_bytes + p.b_bytes;
+  const size_t blk_bytes = (size_t)p.a_bytes + (p.b_resident ? 0 : p.b_bytes);
   int group = 1;
   if (p.kparts == 1) {
-    group = (int)(40 * 1024 / blk_bytes);
+    group = (int)(48 * 1024 / blk_bytes);
     group = group < 1 ? 1 : group > kMaxGroup ? kMaxGroup : group;
   }
   p.group = group;
   const size_t stage_bytes = (size_t)group * blk_bytes;
-  int stages = (int)(budget / stage_bytes);
+  int stages = (int)(ring_budget / stage_bytes);
   stages = stages > kMaxStages ? kMaxStages : stages;
   D3D_REQUIRE(stages >= 2, D3D_ERR_TOO_LARGE);
   p.stages = stages;
-  size_t smem = ctrl + (size_t)stages * stage_bytes;
+  size_t smem = ctrl + (size_t)stages * stage_bytes + (p.b_resident ? bres_bytes : 0);
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it owns the SM's tensor memory
   static bool attr_set[64] = {};
   int dev = 0;

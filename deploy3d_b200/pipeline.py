@@ -20,7 +20,7 @@ class DetectionPipeline:
     """CenterPoint-shaped (``kind='centerpoint'``) or SECOND-shaped (``kind='second'``) frame pipeline."""
 
     def __init__(self, kind="centerpoint", device="cuda:0", caps=None, kernel=0, n_class=10, topk=1000,
-                 iou_threshold=0.2, dtype=torch.float16):
+                 iou_threshold=0.2, dtype=torch.float16, n_pts=None):
         self.kind, self.device, self.dtype = kind, torch.device(device), dtype
         if kind == "centerpoint":
             frame = synth.config4_points()
@@ -31,6 +31,8 @@ class DetectionPipeline:
         else:
             raise ValueError(kind)
         self.n_pts, self.c_pts = frame["points"].shape
+        if n_pts is not None:  # smaller point buffers (tests); the frame given to load_frame must have n_pts points
+            self.n_pts = int(n_pts)
         self.spatial = frame["spatial_shape"]
         self.voxel_config = frame["voxel_config"]
         self.caps = caps or self.default_caps()
@@ -45,9 +47,10 @@ class DetectionPipeline:
             self.vox_feats = torch.zeros((cap_in, self.c_pts), dtype=torch.float32, device=dev)
             self.vox_coors = torch.zeros((cap_in, 4), dtype=torch.int32, device=dev)
             self.vox_num = torch.zeros(1, dtype=torch.int32, device=dev)
-            self.vox_feats_lp = torch.zeros((cap_in, self.c_pts), dtype=dtype, device=dev)
             spatial_b = [self.spatial[0]] + list(self.spatial[2:])
             self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel)
+            # low-precision copy of the voxel features, zero-padded to the channel count the first layer runs with
+            self.vox_feats_lp = torch.zeros((cap_in, self.net.in_channels), dtype=dtype, device=dev)
             self.net.set_input(self.vox_coors, self.vox_num)
             out = self.net.sets[self.net.out_set]
             self.out_shape = out["shape"]
@@ -97,7 +100,8 @@ class DetectionPipeline:
         """Enqueue one frame on the current stream (no host sync, no allocation after the first call)."""
         self.vfe.enqueue(self.points, self.batch, self.cfg, self.shape_tensor,
                          outputs=[self.vox_feats, self.vox_coors, self.vox_num])
-        self.vox_feats_lp.copy_(self.vox_feats)  # fp32 -> fp16 reformat (TensorRT inserts this layer itself)
+        # fp32 -> fp16 reformat (TensorRT inserts this layer itself); padding columns stay zero
+        self.vox_feats_lp[:, :self.c_pts].copy_(self.vox_feats)
         feats, coors, num = self.net.forward(self.vox_feats_lp)
         self.densify.enqueue(feats, coors, num, self.out_shape_tensor, outputs=[self.bev])
         self.nms.enqueue(self.scores, self.boxes, outputs=[self.nms_scores])
