@@ -22,27 +22,40 @@ namespace {
 // ---------------------------------------------------------------------------------------------
 // Neighbour table
 // ---------------------------------------------------------------------------------------------
-__global__ void table_fill_kernel(int4* table, int64_t n16) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x)
+__global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* tile_mask, int64_t tiles) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
     table[i] = make_int4(-1, -1, -1, -1);
+    if (i < tiles) tile_mask[i] = 0u;
+  }
 }
 
 // index rows: gatherIn | scatterOut | kernelOffset (trt/spconv/index_trt.cu:211-213); `inverse` swaps the
 // first two (trt/spconv/mm_trt.cu:174-177).
+// Besides the ids, every tile of 128 outputs gets a bit mask of the kernel offsets (< 32) that feed it, so that the
+// convolution kernel can skip the others without scanning the ids.
 __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t row_len,
                                      const int32_t* __restrict__ num_index, int inverse, int kvol, int64_t m_max,
-                                     int32_t* __restrict__ table) {
+                                     int32_t* __restrict__ table, uint32_t* __restrict__ tile_mask) {
   int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t n = *num_index;
   n = n > row_len ? row_len : n;
-  if (p >= n) return;
-  int k = __ldg(index + 2 * row_len + p);
-  if (k < 0 || k >= kvol) return;  // padding entry
-  int g = __ldg(index + (inverse ? row_len : 0) + p);
-  int s = __ldg(index + (inverse ? 0 : row_len) + p);
-  if (g < 0 || s < 0 || s >= m_max) return;
+  bool valid = p < n;
+  int k = -1, g = -1, s = -1;
+  if (valid) {
+    k = __ldg(index + 2 * row_len + p);
+    valid = k >= 0 && k < kvol;  // else a padding entry
+  }
+  if (valid) {
+    g = __ldg(index + (inverse ? row_len : 0) + p);
+    s = __ldg(index + (inverse ? 0 : row_len) + p);
+    valid = g >= 0 && s >= 0 && s < m_max;
+  }
   // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
-  table[((int64_t)(s >> 7) * kvol + k) * 128 + (s & 127)] = g;
+  if (valid) table[((int64_t)(s >> 7) * kvol + k) * 128 + (s & 127)] = g;
+  // one atomicOr per distinct (tile, offset) of the warp: neighbouring entries mostly share both
+  const unsigned key = (valid && k < 32) ? ((unsigned)(s >> 7) << 5) | (unsigned)k : 0xFFFFFFFFu;
+  const unsigned peers = __match_any_sync(0xffffffffu, key);
+  if (key != 0xFFFFFFFFu && (int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicOr(tile_mask + (s >> 7), 1u << k);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -301,15 +314,16 @@ extern "C" int d3d_spconv_mm_destroy(d3d_spconv_mm_t h) {
 }
 
 extern "C" int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t h, int which) {
-  D3D_REQUIRE(h && which >= 0 && which <= 3, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(h && which >= 0 && which <= 2, D3D_ERR_INVALID_ARGUMENT);
   h->kernel_choice = which;
   return D3D_OK;
 }
 
 extern "C" size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out) {
   // rows are padded to a multiple of 128 entries so every 128-output tile can be read as a whole
+  // followed by one 32-bit offset mask per tile (zero-filled together with the -1 ids: see prepare)
   int64_t pitch = (max_num_act_out + 127) / 128 * 128;
-  return align_up((size_t)kernel_vol * (size_t)pitch * sizeof(int32_t), 256);
+  return table_ids_bytes(kernel_vol, max_num_act_out) + align_up((size_t)(pitch / 128) * sizeof(uint32_t), 256);
 }
 
 extern "C" int d3d_spconv_mm_workspace(d3d_spconv_mm_t h, const d3d_tensor_desc* in, int n_in, size_t* bytes) {
@@ -327,10 +341,13 @@ extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_nu
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int64_t pitch = (max_num_act_out + 127) / 128 * 128;
   int64_t n16 = (int64_t)kernel_vol * pitch / 4;
-  table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16);
+  uint32_t* tile_mask = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(table) +
+                                                    table_ids_bytes(kernel_vol, max_num_act_out));
+  table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16, tile_mask,
+                                                           pitch / 128);
   if (index_row_len > 0)
     table_scatter_kernel<<<(unsigned)ceil_div(index_row_len, 256), 256, 0, st>>>(
-        index, index_row_len, num_index, inverse, kernel_vol, pitch, reinterpret_cast<int32_t*>(table));
+        index, index_row_len, num_index, inverse, kernel_vol, pitch, reinterpret_cast<int32_t*>(table), tile_mask);
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }
@@ -350,7 +367,7 @@ extern "C" int d3d_spconv_mm_run(d3d_spconv_mm_t h, int dtype, const void* in_fe
   a.residual = epilogue ? epilogue->residual : nullptr;
   a.stream = stream;
   bool tc_ok = spconv_mm_tc_eligible(h, dtype);
-  if (h->kernel_choice == 2 || h->kernel_choice == 3) {
+  if (h->kernel_choice == 2) {
     D3D_REQUIRE(tc_ok, D3D_ERR_INVALID_ARGUMENT);
     return launch_spconv_mm_tc(a);
   }

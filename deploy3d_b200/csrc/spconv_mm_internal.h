@@ -27,12 +27,18 @@ struct MmLaunch {
   const void* in_feats;
   int64_t max_num_act_in;
   const int32_t* num_act_out;
-  const int32_t* table;  // [tiles][kVol][128] input row per (output tile, offset, row in tile), -1 = none; tiles = ceil(max_num_act_out / 128)
+  const int32_t* table;  // [tiles][kVol][128] input row per (output tile, offset, row in tile), -1 = none; tiles = ceil(max_num_act_out / 128); then one offset mask per tile
   void* out_feats;
   int relu;
   const void* residual;
   void* stream;
 };
+
+// Bytes of the id part of the neighbour table; the per-tile offset masks (one uint32 per tile) start right after.
+inline size_t table_ids_bytes(int kernel_vol, int64_t max_num_act_out) {
+  const size_t pitch = (size_t)((max_num_act_out + 127) / 128 * 128);
+  return ((size_t)kernel_vol * pitch * sizeof(int32_t) + 255) / 256 * 256;
+}
 
 int launch_spconv_mm_simt(const MmLaunch& a);
 // Returns D3D_ERR_INVALID_ARGUMENT when the shape/dtype is not eligible for the tensor-core path.

@@ -47,7 +47,12 @@ def test_frame_matches_cpu_pipeline(d3d, kind, denom, graph):
     ref = want["bev"]
     assert got.shape == ref.shape
     assert ((got != 0) == (ref != 0)).mean() > 0.999  # same occupied cells (ReLU zeros may differ by rounding)
-    scale = np.sqrt((ref ** 2).mean()) + 1e-12
+    # 21 (or 12) fp16 layers deep: every layer rounds its output to fp16 on both sides, in different summation
+    # orders.  Tolerance 1e-2 of the feature scale (RMS over occupied cells) in the L2 sense, 2e-2 per element.
+    scale = np.sqrt((ref[ref != 0] ** 2).mean()) + 1e-12
     err = np.abs(got - ref)
-    assert (err <= 2e-2 * (np.abs(ref) + scale)).all(), "worst %.3e at scale %.3e" % (err.max(), scale)
+    rel_l2 = np.sqrt((err ** 2).sum() / ((ref ** 2).sum() + 1e-30))
+    assert rel_l2 < 1e-2, "relative L2 error %.3e" % rel_l2
+    bad = err > 2e-2 * (np.abs(ref) + scale)
+    assert not bad.any(), "%d cells off, worst %.3e at scale %.3e" % (bad.sum(), err[bad].max(), scale)
     assert (pipe.nms_scores.cpu().numpy() == want["nms_scores"]).all()
