@@ -228,6 +228,51 @@ suppress_kernel(const unsigned long long* __restrict__ mask, const float* __rest
   }
 }
 
+// Same sweep for K <= 2048 boxes (nw <= 32: lane w owns mask word w).  The mask rows of the 64 boxes of a block
+// are first staged in shared memory with independent, coalesced loads; the serial part then touches shared memory
+// only, instead of waiting for one global load per kept box.
+constexpr int kStagedMaxWords = 32;
+
+__global__ void __launch_bounds__(32)
+suppress_staged_kernel(const unsigned long long* __restrict__ mask, const float* __restrict__ in_scores, int k, int nw,
+                       float* __restrict__ out_scores) {
+  __shared__ unsigned long long rows[kNmsBlock * kStagedMaxWords];
+  const int b = blockIdx.x, lane = threadIdx.x;
+  const unsigned long long* mk = mask + (int64_t)b * k * nw;
+  unsigned long long remv = 0ull;  // word `lane` of the removed set
+  for (int blk = 0; blk < nw; ++blk) {
+    const int base = blk * kNmsBlock;
+    const int nbox = min(k - base, kNmsBlock);
+    const unsigned long long* src = mk + (int64_t)base * nw;  // nbox consecutive rows of nw words
+    const int words = nbox * nw;
+    __syncwarp();
+#pragma unroll 8
+    for (int f = lane; f < words; f += 32) rows[f] = __ldg(src + f);
+    __syncwarp();
+    const unsigned long long d0 = lane < nbox ? rows[lane * nw + blk] : 0ull;
+    const unsigned long long d1 = lane + 32 < nbox ? rows[(lane + 32) * nw + blk] : 0ull;
+    unsigned long long cur = __shfl_sync(0xffffffffu, remv, blk);
+    for (int i = 0; i < nbox; ++i) {
+      const unsigned long long di = __shfl_sync(0xffffffffu, i < 32 ? d0 : d1, i & 31);
+      if (!((cur >> i) & 1ull)) cur |= di;
+    }
+    const unsigned long long valid = nbox == 64 ? ~0ull : ((1ull << nbox) - 1ull);
+    unsigned long long kept = ~cur & valid;
+    for (int i = lane; i < nbox; i += 32) {
+      const float s = in_scores[(int64_t)b * k + base + i];
+      out_scores[(int64_t)b * k + base + i] = ((cur >> i) & 1ull) ? -1.0f : s;
+    }
+    // OR the rows of the kept boxes into the words behind this block
+    if (lane > blk && lane < nw) {
+      while (kept) {
+        const int i = __ffsll((long long)kept) - 1;
+        kept &= kept - 1;
+        remv |= rows[i * nw + lane];
+      }
+    }
+  }
+}
+
 }  // namespace
 }  // namespace d3d
 
@@ -273,8 +318,12 @@ extern "C" int d3d_nms3d_enqueue(const d3d_nms3d_params* p, const d3d_tensor_des
   unsigned long long* mask = reinterpret_cast<unsigned long long*>(workspace);
   overlap_mask_kernel<<<dim3(nw, nw, b), 256, 0, st>>>(reinterpret_cast<const float*>(inputs[1]), k, bd,
                                                        p->iou_threshold, nw, mask);
-  suppress_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
-                                    reinterpret_cast<float*>(outputs[0]));
+  if (nw <= kStagedMaxWords)
+    suppress_staged_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
+                                             reinterpret_cast<float*>(outputs[0]));
+  else
+    suppress_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
+                                      reinterpret_cast<float*>(outputs[0]));
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }

@@ -118,7 +118,8 @@ __global__ void subm_insert_kernel(unsigned long long* table, const int32_t* __r
 __global__ void subm_probe_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ coors,
                                   const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
                                   int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk) {
-  __shared__ int warp_cnt[kIdxThreads / 32];
+  constexpr int kBatch = 4;  // lookups in flight per thread
+  __shared__ int cnt[kBatch];
   int n = live_count(num_act_in, n_max);
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
   uint32_t mask = hash_capacity(n, cap_max) - 1;
@@ -132,22 +133,83 @@ __global__ void subm_probe_kernel(const unsigned long long* __restrict__ table, 
     row_ok = row_prefix(g, c, row, &prefix);
   }
   int dl = g.ndim - 1;
-  for (int kl = 0; kl < g.klast; ++kl) {
-    int k = row * g.klast + kl;
-    int v = -1, o;
-    if (row_ok && out_coord(g, dl, c[dl + 1], kl, &o))
-      v = hash_lookup(table, mask, prefix * (uint32_t)g.shape[dl + 1] + (uint32_t)o);
-    if (i < n) pair_out[(int64_t)k * n_max + i] = v;
-    unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
-    if (lane_id() == 0) warp_cnt[threadIdx.x >> 5] = __popc(hits);
+  for (int kl0 = 0; kl0 < g.klast; kl0 += kBatch) {
+    if (threadIdx.x < kBatch) cnt[threadIdx.x] = 0;
     __syncthreads();
-    if (threadIdx.x == 0) {
-      int s = 0;
-      for (int w = 0; w < kIdxThreads / 32; ++w) s += warp_cnt[w];
-      block_counts[(int64_t)k * nblk + blockIdx.x] = s;
+    int v[kBatch];
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {  // independent probes: their memory latencies overlap
+      int o;
+      v[b] = -1;
+      if (kl0 + b < g.klast && row_ok && out_coord(g, dl, c[dl + 1], kl0 + b, &o))
+        v[b] = hash_lookup(table, mask, prefix * (uint32_t)g.shape[dl + 1] + (uint32_t)o);
+    }
+#pragma unroll
+    for (int b = 0; b < kBatch; ++b) {
+      if (kl0 + b < g.klast) {
+        int k = row * g.klast + kl0 + b;
+        if (i < n) pair_out[(int64_t)k * n_max + i] = v[b];
+        unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
+        if (lane_id() == 0 && hits) atomicAdd(&cnt[b], __popc(hits));
+      }
     }
     __syncthreads();
+    if (threadIdx.x < kBatch && kl0 + threadIdx.x < g.klast)
+      block_counts[(int64_t)(row * g.klast + kl0 + threadIdx.x) * nblk + blockIdx.x] = cnt[threadIdx.x];
+    __syncthreads();
   }
+}
+
+// 3-D specialisation of the SubM probe, same outputs.  One thread per input voxel walks all kernel offsets with
+// its coordinates in registers; the probes of one kernel row are independent loads in flight together, and the
+// per-(offset, CTA) counts are collected in shared memory with a single barrier at the end.
+__global__ void __launch_bounds__(kIdxThreads)
+subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ coors,
+                   const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
+                   int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk) {
+  constexpr int kBatch = 4;
+  __shared__ int cnt[kMaxKernelVol];
+  const int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  for (int t = threadIdx.x; t < g.kvol; t += kIdxThreads) cnt[t] = 0;
+  __syncthreads();
+  const uint32_t mask = hash_capacity(n, cap_max) - 1;
+  const int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  const bool live = i < n;
+  int4 c = make_int4(-1, 0, 0, 0);
+  if (live) c = __ldg(reinterpret_cast<const int4*>(coors) + i);
+  const bool batch_ok = live && c.x >= 0 && c.x < g.shape[0];
+  int k = 0;
+  for (int k0 = 0; k0 < g.ksize[0]; ++k0) {
+    int o0;
+    const bool ok0 = out_coord(g, 0, c.y, k0, &o0) && batch_ok;
+    for (int k1 = 0; k1 < g.ksize[1]; ++k1) {
+      int o1;
+      const bool ok1 = out_coord(g, 1, c.z, k1, &o1) && ok0;
+      const uint32_t prefix = ((uint32_t)c.x * (uint32_t)g.shape[1] + (uint32_t)o0) * (uint32_t)g.shape[2] + (uint32_t)o1;
+      for (int k2 = 0; k2 < g.klast; k2 += kBatch) {
+        int v[kBatch];
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          int o2;
+          v[b] = -1;
+          if (k2 + b < g.klast && out_coord(g, 2, c.w, k2 + b, &o2) && ok1)
+            v[b] = hash_lookup(table, mask, prefix * (uint32_t)g.shape[3] + (uint32_t)o2);
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          if (k2 + b < g.klast) {
+            if (live) pair_out[(int64_t)(k + b) * n_max + i] = v[b];
+            const unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
+            if (lane_id() == 0 && hits) atomicAdd(&cnt[k + b], __popc(hits));
+          }
+        }
+        k += (g.klast - k2 < kBatch) ? g.klast - k2 : kBatch;
+      }
+    }
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < g.kvol; t += kIdxThreads) block_counts[(int64_t)t * nblk + blockIdx.x] = cnt[t];
 }
 
 // Conv insert: every valid (input, offset) inserts its output key with value = i*kvol + k; the smallest pair id
@@ -320,6 +382,40 @@ __global__ void compact_kernel(const int32_t* __restrict__ pair_out, const int32
   index[2 * row_len + pos] = k;
 }
 
+// Same result for small kernels (kvol <= kCompactAllMaxVol): one CTA per input block walks all offsets, with a
+// single barrier between counting and writing instead of two per (block, offset).
+constexpr int kCompactAllMaxVol = 64;
+__global__ void __launch_bounds__(kIdxThreads)
+compact_all_kernel(const int32_t* __restrict__ pair_out, const int32_t* __restrict__ block_prefix,
+                   const int32_t* __restrict__ seg, const int32_t* num_act_in, int64_t n_max, int nblk, int kvol,
+                   int32_t* __restrict__ index, int64_t row_len) {
+  constexpr int kWarps = kIdxThreads / 32;
+  __shared__ int warp_cnt[kCompactAllMaxVol][kWarps];
+  const int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  const int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  const int warp = threadIdx.x >> 5;
+  for (int k = 0; k < kvol; ++k) {
+    const int v = i < n ? __ldg(pair_out + (int64_t)k * n_max + i) : -1;
+    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+    if (lane_id() == 0) warp_cnt[k][warp] = __popc(hits);
+  }
+  __syncthreads();
+  for (int k = 0; k < kvol; ++k) {
+    const int v = i < n ? __ldg(pair_out + (int64_t)k * n_max + i) : -1;
+    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+    if (v < 0) continue;
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += warp_cnt[k][w];
+    const int64_t pos = (int64_t)seg[k] + block_prefix[(int64_t)k * nblk + blockIdx.x] + before +
+                        __popc(hits & lanemask_lt());
+    if (pos >= row_len) continue;
+    index[pos] = i;
+    index[row_len + pos] = v;
+    index[2 * row_len + pos] = k;
+  }
+}
+
 // Everything that is not a pair is -1: the unused tail of each 128-aligned segment and the rows beyond
 // numIndex (the reference memsets the three rows beforehand, trt/spconv/index.cu:352-354).
 __global__ void fill_padding_kernel(const int32_t* __restrict__ seg, int kvol, int32_t* __restrict__ index,
@@ -337,10 +433,19 @@ __global__ void fill_padding_kernel(const int32_t* __restrict__ seg, int kvol, i
       index[2 * row_len + pos] = -1;
     }
   }
-  int64_t tail = row_len - num_index;
-  for (int64_t t = tid; t < 3 * tail; t += nthreads) {
-    int64_t r = t / tail, p = t % tail;
-    index[r * row_len + num_index + p] = -1;
+  // tail of the three rows; num_index is a multiple of 128, so 16-byte stores work whenever the rows themselves
+  // start 16-byte aligned
+  const int64_t tail = row_len - num_index;
+  if (tail <= 0) return;
+  if ((row_len & 3) == 0 && (reinterpret_cast<uintptr_t>(index) & 15) == 0) {
+    const int64_t tail4 = tail >> 2;
+    for (int r = 0; r < 3; ++r) {
+      int4* dst = reinterpret_cast<int4*>(index + r * row_len + num_index);
+      for (int64_t p = tid; p < tail4; p += nthreads) dst[p] = make_int4(-1, -1, -1, -1);
+    }
+  } else {
+    for (int r = 0; r < 3; ++r)
+      for (int64_t p = tid; p < tail; p += nthreads) index[r * row_len + num_index + p] = -1;
   }
 }
 
@@ -512,8 +617,13 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
                                                                          plan.cap_max);
   if (p->subm) {
     subm_insert_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max);
-    subm_probe_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
-                                                                  plan.cap_max, plan.pair_out, plan.block_counts, nblk);
+    if (g.ndim == 3)
+      subm_probe3_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
+                                                       plan.pair_out, plan.block_counts, nblk);
+    else
+      subm_probe_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
+                                                                    plan.cap_max, plan.pair_out, plan.block_counts,
+                                                                    nblk);
   } else {
     int32_t* out_coors = reinterpret_cast<int32_t*>(outputs[2]);
     int32_t* num_act_out = reinterpret_cast<int32_t*>(outputs[3]);
@@ -530,8 +640,12 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
                                                                       plan.block_counts, nblk);
   }
   segment_scan_kernel<<<1, 1024, 0, st>>>(plan.block_counts, nblk, g.kvol, num_act_in, n_max, plan.seg, num_index);
-  compact_kernel<<<dim3(nblk, g.kvol), kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in,
-                                                             n_max, nblk, index, plan.row_len);
+  if (g.kvol <= kCompactAllMaxVol)
+    compact_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in, n_max,
+                                                     nblk, g.kvol, index, plan.row_len);
+  else
+    compact_kernel<<<dim3(nblk, g.kvol), kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg,
+                                                               num_act_in, n_max, nblk, index, plan.row_len);
   fill_padding_kernel<<<stream_grid(3 * plan.row_len, 256), 256, 0, st>>>(plan.seg, g.kvol, index, plan.row_len);
   D3D_CHECK_LAUNCH();
   return D3D_OK;

@@ -36,26 +36,30 @@ __global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* tile_mask,
 __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t row_len,
                                      const int32_t* __restrict__ num_index, int inverse, int kvol, int64_t m_max,
                                      int32_t* __restrict__ table, uint32_t* __restrict__ tile_mask) {
-  int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t n = *num_index;
   n = n > row_len ? row_len : n;
-  bool valid = p < n;
-  int k = -1, g = -1, s = -1;
-  if (valid) {
-    k = __ldg(index + 2 * row_len + p);
-    valid = k >= 0 && k < kvol;  // else a padding entry
+  // grid-stride over the live part of the rulebook only (the rows are sized for the worst case, mostly unused);
+  // whole warps iterate together so that the shuffle below is always fully populated
+  const int64_t n_warp = (n + 31) & ~(int64_t)31;
+  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_warp; p += (int64_t)gridDim.x * blockDim.x) {
+    bool valid = p < n;
+    int k = -1, g = -1, s = -1;
+    if (valid) {
+      k = __ldg(index + 2 * row_len + p);
+      valid = k >= 0 && k < kvol;  // else a padding entry
+    }
+    if (valid) {
+      g = __ldg(index + (inverse ? row_len : 0) + p);
+      s = __ldg(index + (inverse ? 0 : row_len) + p);
+      valid = g >= 0 && s >= 0 && s < m_max;
+    }
+    // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
+    if (valid) table[((int64_t)(s >> 7) * kvol + k) * 128 + (s & 127)] = g;
+    // one atomicOr per run of equal (tile, offset) in the warp: neighbouring entries mostly share both
+    const unsigned key = (valid && k < 32) ? ((unsigned)(s >> 7) << 5) | (unsigned)k : 0xFFFFFFFFu;
+    const unsigned prev = __shfl_up_sync(0xffffffffu, key, 1);
+    if (key != 0xFFFFFFFFu && ((threadIdx.x & 31) == 0 || prev != key)) atomicOr(tile_mask + (s >> 7), 1u << k);
   }
-  if (valid) {
-    g = __ldg(index + (inverse ? row_len : 0) + p);
-    s = __ldg(index + (inverse ? 0 : row_len) + p);
-    valid = g >= 0 && s >= 0 && s < m_max;
-  }
-  // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
-  if (valid) table[((int64_t)(s >> 7) * kvol + k) * 128 + (s & 127)] = g;
-  // one atomicOr per distinct (tile, offset) of the warp: neighbouring entries mostly share both
-  const unsigned key = (valid && k < 32) ? ((unsigned)(s >> 7) << 5) | (unsigned)k : 0xFFFFFFFFu;
-  const unsigned peers = __match_any_sync(0xffffffffu, key);
-  if (key != 0xFFFFFFFFu && (int)(threadIdx.x & 31) == __ffs(peers) - 1) atomicOr(tile_mask + (s >> 7), 1u << k);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -346,7 +350,7 @@ extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_nu
   table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16, tile_mask,
                                                            pitch / 128);
   if (index_row_len > 0)
-    table_scatter_kernel<<<(unsigned)ceil_div(index_row_len, 256), 256, 0, st>>>(
+    table_scatter_kernel<<<stream_grid(index_row_len, 256), 256, 0, st>>>(
         index, index_row_len, num_index, inverse, kernel_vol, pitch, reinterpret_cast<int32_t*>(table), tile_mask);
   D3D_CHECK_LAUNCH();
   return D3D_OK;

@@ -345,6 +345,8 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   const uint32_t n_in_rows = (uint32_t)p.n_in_rows;
   const uint32_t tiles_addr = smem_u32(s.tiles);
   const int ids_per_tile = p.kvol * kTileRows;
+  static_assert(kGroup * kPasses <= 8 && kMaxStages <= 8, "zero_rows keeps 8 bits per stage");
+  uint64_t zero_rows = 0;  // bit 8 * stage + e * kPasses + i: this thread's last copy to that position was a zero fill
   int stage = 0;
   uint32_t phase = 0, idx_phase = 0;  // idx_phase bit b: parity to wait for on idx_full[b]
   int buf = 0;
@@ -372,15 +374,26 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
 #pragma unroll
           for (int i = 0; i < kPasses; ++i)
             id[e][i] = ((take >> e) & 1u) ? idp[e * kTileRows + i * kRowsPerPass] : -1;
+        // Most rows of a block have no neighbour (LiDAR: about 5 of 27 offsets per voxel).  A position this thread
+        // zero-filled the last time it wrote the stage is still zero (nobody else writes it), so a zero row over a
+        // zero row is skipped: it would only spend shared-memory bandwidth the tensor core needs.
+        const uint32_t was_zero = (uint32_t)(zero_rows >> (stage * 8)) & 0xFFu;
+        uint32_t now_zero = was_zero;
 #pragma unroll
         for (int e = 0; e < kGroup; ++e)
 #pragma unroll
           for (int i = 0; i < kPasses; ++i) {
+            constexpr uint32_t kNone = 0u;
+            const uint32_t bit = 1u << (e * kPasses + i);
+            const uint32_t run = (take >> e) & 1u;
             const bool valid = (uint32_t)id[e][i] < n_in_rows;  // negative = no neighbour
             const unsigned char* src = src_part + (uint64_t)(valid ? (uint32_t)id[e][i] : 0u) * row_src_bytes;
-            cp_async_16_if((take >> e) & 1u, dst + (uint32_t)(e * kBlockBytes + i * kRowsPerPass * kRowBytes), src,
-                           valid ? 16u : 0u);
+            const uint32_t redundant = (!valid && (was_zero & bit)) ? 1u : kNone;
+            cp_async_16_if(run & (redundant ^ 1u), dst + (uint32_t)(e * kBlockBytes + i * kRowsPerPass * kRowBytes),
+                           src, valid ? 16u : 0u);
+            if (run) now_zero = valid ? (now_zero & ~bit) : (now_zero | bit);
           }
+        zero_rows = (zero_rows & ~(0xFFull << (stage * 8))) | ((uint64_t)now_zero << (stage * 8));
         cp_async_arrive(&sh->full[stage]);  // one arrival per producer thread once its copies have landed
         if (++stage == p.stages) stage = 0, phase ^= 1;
       }
@@ -707,7 +720,8 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   const size_t blk_bytes = (size_t)p.a_bytes + (p.b_resident ? 0 : p.b_bytes);
   int group = 1;
   if (p.kparts == 1)
-    while (group < kMaxGroup && (size_t)(2 * group) * blk_bytes <= 48 * 1024) group *= 2;
+    while (group < kMaxGroup && (size_t)(2 * group) * blk_bytes <= 48 * 1024 && 2 * group * (kchunk / 16) <= 8)
+      group *= 2;
   p.group = group;
   const size_t stage_bytes = (size_t)group * blk_bytes;
   int stages = (int)(ring_budget / stage_bytes);
@@ -718,13 +732,15 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it owns the SM's tensor memory
   // one kernel instance per (MMAs per block, offsets per stage)
   typedef void (*KernelFn)(const CUtensorMap, const TcParams);
+  // (a stage holds at most 8 K-step blocks: K steps x offsets <= 8)
   static const KernelFn kernels[4][4] = {
       {spconv_mm_tc_kernel<1, 1>, spconv_mm_tc_kernel<1, 2>, spconv_mm_tc_kernel<1, 4>, spconv_mm_tc_kernel<1, 8>},
-      {spconv_mm_tc_kernel<2, 1>, spconv_mm_tc_kernel<2, 2>, spconv_mm_tc_kernel<2, 4>, spconv_mm_tc_kernel<2, 8>},
-      {spconv_mm_tc_kernel<4, 1>, spconv_mm_tc_kernel<4, 2>, spconv_mm_tc_kernel<4, 4>, spconv_mm_tc_kernel<4, 8>},
-      {spconv_mm_tc_kernel<8, 1>, spconv_mm_tc_kernel<8, 2>, spconv_mm_tc_kernel<8, 4>, spconv_mm_tc_kernel<8, 8>}};
+      {spconv_mm_tc_kernel<2, 1>, spconv_mm_tc_kernel<2, 2>, spconv_mm_tc_kernel<2, 4>, nullptr},
+      {spconv_mm_tc_kernel<4, 1>, spconv_mm_tc_kernel<4, 2>, nullptr, nullptr},
+      {spconv_mm_tc_kernel<8, 1>, nullptr, nullptr, nullptr}};
   const int si = kchunk == 16 ? 0 : kchunk == 32 ? 1 : kchunk == 64 ? 2 : 3;
   const int gi = group == 1 ? 0 : group == 2 ? 1 : group == 4 ? 2 : 3;
+  D3D_REQUIRE(kernels[si][gi] != nullptr, D3D_ERR_TOO_LARGE);
   static bool attr_set[64][4][4] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return D3D_ERR_CUDA;
