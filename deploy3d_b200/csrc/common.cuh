@@ -161,6 +161,22 @@ __device__ __forceinline__ int32_t hash_lookup(const unsigned long long* __restr
   return -1;
 }
 
+// Lookup split in two so that a thread can have the first probes of several keys in flight at once: the caller
+// loads `first = table[home_slot(key)]` for all its keys, then resolves each; only a collision walks on.
+__device__ __forceinline__ int32_t hash_lookup_resolve(const unsigned long long* __restrict__ table, uint32_t cap_mask,
+                                                       uint32_t key, unsigned long long first) {
+  if ((uint32_t)(first >> 32) == key) return (int32_t)(uint32_t)first;
+  if (first == kEmptySlot) return -1;
+  uint32_t slot = (home_slot(key, cap_mask) + 4u) & cap_mask;
+  for (uint32_t probes = 1; probes <= (cap_mask >> 2); ++probes) {
+    unsigned long long cur = __ldg(&table[slot]);
+    if ((uint32_t)(cur >> 32) == key) return (int32_t)(uint32_t)cur;
+    if (cur == kEmptySlot) return -1;
+    slot = (slot + 4u) & cap_mask;
+  }
+  return -1;
+}
+
 // Capacity (slots, power of two >= 16) for `keys` insertions at load factor <= 0.5, clamped to `cap_max`.
 __device__ __forceinline__ uint32_t hash_capacity(long long keys, uint32_t cap_max) {
   unsigned long long want = (unsigned long long)(keys > 8 ? keys : 8) * 2ull;

@@ -47,8 +47,17 @@ __device__ __forceinline__ bool out_coord(const Geometry& g, int d, int in, int 
     o = in * g.stride[d] - g.pad[d] + kd * g.dil[d];
   } else {
     int dc = in + g.pad[d] - kd * g.dil[d];
-    if (dc % g.stride[d] != 0) return false;
-    o = dc / g.stride[d];
+    if (dc < 0) return false;  // would map to a negative output coordinate or fail the divisibility test
+    const int st = g.stride[d];
+    if (st == 1) {
+      o = dc;
+    } else if (st == 2) {  // the common strides need no integer division
+      if (dc & 1) return false;
+      o = dc >> 1;
+    } else {
+      if (dc % st != 0) return false;
+      o = dc / st;
+    }
   }
   *out = o;
   return o >= 0 && o < g.shape[d + 1];
@@ -163,11 +172,14 @@ __global__ void subm_probe_kernel(const unsigned long long* __restrict__ table, 
 // 3-D specialisation of the SubM probe, same outputs.  One thread per input voxel walks all kernel offsets with
 // its coordinates in registers; the probes of one kernel row are independent loads in flight together, and the
 // per-(offset, CTA) counts are collected in shared memory with a single barrier at the end.
+// kPlane3x3: the two trailing kernel extents are 3 x 3 (the usual case); the nine probes of a leading tap are
+// then issued together.
+template <bool kPlane3x3>
 __global__ void __launch_bounds__(kIdxThreads)
 subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ coors,
                    const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
                    int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk) {
-  constexpr int kBatch = 4;
+  constexpr int kBatch = 4;  // probes in flight per thread
   __shared__ int cnt[kMaxKernelVol];
   const int n = live_count(num_act_in, n_max);
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
@@ -179,23 +191,58 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
   int4 c = make_int4(-1, 0, 0, 0);
   if (live) c = __ldg(reinterpret_cast<const int4*>(coors) + i);
   const bool batch_ok = live && c.x >= 0 && c.x < g.shape[0];
+  // SubM: stride 1, never transposed, so the neighbour along d is c_d + pad_d - k_d * dil_d (geometry.h:41-49 with
+  // stride 1) and its key differs from the key of (c + pad) by a per-offset constant: no division per probe.
+  const int b0 = c.y + g.pad[0], b1 = c.z + g.pad[1], b2 = c.w + g.pad[2];
+  const uint32_t s1 = (uint32_t)g.shape[1], s2 = (uint32_t)g.shape[2], s3 = (uint32_t)g.shape[3];
+  const uint32_t key_base = (((uint32_t)c.x * s1 + (uint32_t)b0) * s2 + (uint32_t)b1) * s3 + (uint32_t)b2;
   int k = 0;
   for (int k0 = 0; k0 < g.ksize[0]; ++k0) {
-    int o0;
-    const bool ok0 = out_coord(g, 0, c.y, k0, &o0) && batch_ok;
+    const int o0 = b0 - k0 * g.dil[0];
+    const bool ok0 = batch_ok && (uint32_t)o0 < s1;
+    if (kPlane3x3) {
+      int v[9];
+      uint32_t key[9];
+      unsigned long long first[9];
+      bool probe[9];
+      const uint32_t key_k0 = key_base - (uint32_t)(k0 * g.dil[0]) * s2 * s3;
+#pragma unroll
+      for (int b = 0; b < 9; ++b) {  // first probes of the whole plane: independent loads
+        const int k1 = b / 3, k2 = b % 3;
+        const int o1 = b1 - k1 * g.dil[1], o2 = b2 - k2 * g.dil[2];
+        probe[b] = ok0 && (uint32_t)o1 < s2 && (uint32_t)o2 < s3;
+        key[b] = key_k0 - (uint32_t)(k1 * g.dil[1]) * s3 - (uint32_t)(k2 * g.dil[2]);
+        first[b] = probe[b] ? __ldg(&table[home_slot(key[b], mask)]) : kEmptySlot;
+      }
+#pragma unroll
+      for (int b = 0; b < 9; ++b) v[b] = probe[b] ? hash_lookup_resolve(table, mask, key[b], first[b]) : -1;
+#pragma unroll
+      for (int b = 0; b < 9; ++b) {
+        if (live) pair_out[(int64_t)(k + b) * n_max + i] = v[b];
+        const unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
+        if (lane_id() == 0 && hits) atomicAdd(&cnt[k + b], __popc(hits));
+      }
+      k += 9;
+      continue;
+    }
     for (int k1 = 0; k1 < g.ksize[1]; ++k1) {
-      int o1;
-      const bool ok1 = out_coord(g, 1, c.z, k1, &o1) && ok0;
-      const uint32_t prefix = ((uint32_t)c.x * (uint32_t)g.shape[1] + (uint32_t)o0) * (uint32_t)g.shape[2] + (uint32_t)o1;
+      const int o1 = b1 - k1 * g.dil[1];
+      const bool ok1 = ok0 && (uint32_t)o1 < s2;
+      const uint32_t key_row = key_base - ((uint32_t)(k0 * g.dil[0]) * s2 + (uint32_t)(k1 * g.dil[1])) * s3;
       for (int k2 = 0; k2 < g.klast; k2 += kBatch) {
         int v[kBatch];
+        uint32_t key[kBatch];
+        unsigned long long first[kBatch];
+        bool probe[kBatch];
 #pragma unroll
-        for (int b = 0; b < kBatch; ++b) {
-          int o2;
-          v[b] = -1;
-          if (k2 + b < g.klast && out_coord(g, 2, c.w, k2 + b, &o2) && ok1)
-            v[b] = hash_lookup(table, mask, prefix * (uint32_t)g.shape[3] + (uint32_t)o2);
+        for (int b = 0; b < kBatch; ++b) {  // first probes of the batch: independent loads
+          const int o2 = b2 - (k2 + b) * g.dil[2];
+          probe[b] = ok1 && k2 + b < g.klast && (uint32_t)o2 < s3;
+          key[b] = key_row - (uint32_t)((k2 + b) * g.dil[2]);
+          first[b] = probe[b] ? __ldg(&table[home_slot(key[b], mask)]) : kEmptySlot;
         }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) v[b] = probe[b] ? hash_lookup_resolve(table, mask, key[b], first[b]) : -1;
 #pragma unroll
         for (int b = 0; b < kBatch; ++b) {
           if (k2 + b < g.klast) {
@@ -245,6 +292,27 @@ __device__ __forceinline__ bool is_winner(const unsigned long long* table, int s
   return slot >= 0 && (uint32_t)table[slot] == pair_id;
 }
 
+// Bit k of the result: pair (i, k) wins.  Loads are issued nine offsets at a time (two dependent gathers each).
+// Valid for kvol <= 32.
+__device__ __forceinline__ uint32_t winner_bits(const unsigned long long* __restrict__ table,
+                                                const int32_t* __restrict__ pair_out, int64_t n_max, int kvol,
+                                                int i) {
+  constexpr int kBatch = 9;
+  uint32_t bits = 0;
+  for (int k0 = 0; k0 < kvol; k0 += kBatch) {
+    int slot[kBatch];
+    unsigned long long cur[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) slot[j] = k0 + j < kvol ? __ldg(pair_out + (int64_t)(k0 + j) * n_max + i) : -1;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) cur[j] = slot[j] >= 0 ? __ldg(table + slot[j]) : kEmptySlot;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j)
+      if (slot[j] >= 0 && (uint32_t)cur[j] == (uint32_t)(i * kvol + k0 + j)) bits |= 1u << (k0 + j);
+  }
+  return bits;
+}
+
 __global__ void conv_count_winners_kernel(const unsigned long long* __restrict__ table,
                                           const int32_t* __restrict__ pair_out, const int32_t* num_act_in,
                                           int64_t n_max, int kvol, int32_t* __restrict__ winners) {
@@ -252,8 +320,13 @@ __global__ void conv_count_winners_kernel(const unsigned long long* __restrict__
   int n = live_count(num_act_in, n_max);
   int i = blockIdx.x * kIdxThreads + threadIdx.x;
   int cnt = 0;
-  if (i < n)
-    for (int k = 0; k < kvol; ++k) cnt += is_winner(table, pair_out[(int64_t)k * n_max + i], (uint32_t)(i * kvol + k));
+  if (i < n) {
+    if (kvol <= 32)
+      cnt = __popc(winner_bits(table, pair_out, n_max, kvol, i));
+    else
+      for (int k = 0; k < kvol; ++k)
+        cnt += is_winner(table, pair_out[(int64_t)k * n_max + i], (uint32_t)(i * kvol + k));
+  }
   int total;
   block_exclusive_scan(cnt, scratch, &total);
   if (threadIdx.x == 0) winners[blockIdx.x] = total;
@@ -269,15 +342,24 @@ __global__ void conv_assign_kernel(const unsigned long long* __restrict__ table,
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
   int i = blockIdx.x * kIdxThreads + threadIdx.x;
   int cnt = 0;
-  if (i < n)
-    for (int k = 0; k < g.kvol; ++k)
-      cnt += is_winner(table, pair_out[(int64_t)k * n_max + i], (uint32_t)(i * g.kvol + k));
+  uint32_t bits = 0;
+  const bool small = g.kvol <= 32;
+  if (i < n) {
+    if (small) {
+      bits = winner_bits(table, pair_out, n_max, g.kvol, i);
+      cnt = __popc(bits);
+    } else {
+      for (int k = 0; k < g.kvol; ++k)
+        cnt += is_winner(table, pair_out[(int64_t)k * n_max + i], (uint32_t)(i * g.kvol + k));
+    }
+  }
   int total;
   int id = winners_base[blockIdx.x] + block_exclusive_scan(cnt, scratch, &total);
   if (i >= n || cnt == 0) return;
   for (int k = 0; k < g.kvol; ++k) {
+    if (small && !((bits >> k) & 1u)) continue;
     int slot = pair_out[(int64_t)k * n_max + i];
-    if (!is_winner(table, slot, (uint32_t)(i * g.kvol + k))) continue;
+    if (!small && !is_winner(table, slot, (uint32_t)(i * g.kvol + k))) continue;
     if (id < max_out) {
       slot_out[slot] = id;
       int32_t oc[D3D_MAX_NDIM + 1];
@@ -290,29 +372,36 @@ __global__ void conv_assign_kernel(const unsigned long long* __restrict__ table,
   }
 }
 
-// pair_out: slot -> output id; per-(k, input block) hit counts.  CTA (x = input block, y = k).
-__global__ void conv_translate_kernel(int32_t* __restrict__ pair_out, const int32_t* __restrict__ slot_out,
-                                      const int32_t* num_act_in, int64_t n_max, int32_t* __restrict__ block_counts,
-                                      int nblk) {
-  __shared__ int warp_cnt[kIdxThreads / 32];
-  int n = live_count(num_act_in, n_max);
+// pair_out: slot -> output id; per-(k, input block) hit counts.  One CTA per input block walks all offsets
+// (kvol <= kMaxKernelVol) with nine gathers in flight per thread and a single barrier.
+__global__ void __launch_bounds__(kIdxThreads)
+conv_translate_all_kernel(int32_t* __restrict__ pair_out, const int32_t* __restrict__ slot_out,
+                          const int32_t* num_act_in, int64_t n_max, int kvol, int32_t* __restrict__ block_counts,
+                          int nblk) {
+  constexpr int kBatch = 9;
+  __shared__ int cnt[kMaxKernelVol];
+  const int n = live_count(num_act_in, n_max);
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
-  int k = blockIdx.y;
-  int i = blockIdx.x * kIdxThreads + threadIdx.x;
-  int v = -1;
-  if (i < n) {
-    int slot = pair_out[(int64_t)k * n_max + i];
-    if (slot >= 0) v = slot_out[slot];
-    pair_out[(int64_t)k * n_max + i] = v;
-  }
-  unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
-  if (lane_id() == 0) warp_cnt[threadIdx.x >> 5] = __popc(hits);
+  for (int t = threadIdx.x; t < kvol; t += kIdxThreads) cnt[t] = 0;
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int s = 0;
-    for (int w = 0; w < kIdxThreads / 32; ++w) s += warp_cnt[w];
-    block_counts[(int64_t)k * nblk + blockIdx.x] = s;
+  const int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  for (int k0 = 0; k0 < kvol; k0 += kBatch) {
+    int v[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) v[j] = (i < n && k0 + j < kvol) ? pair_out[(int64_t)(k0 + j) * n_max + i] : -1;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) v[j] = v[j] >= 0 ? __ldg(slot_out + v[j]) : -1;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      if (k0 + j < kvol) {
+        if (i < n) pair_out[(int64_t)(k0 + j) * n_max + i] = v[j];
+        const unsigned hits = __ballot_sync(0xffffffffu, v[j] >= 0);
+        if (lane_id() == 0 && hits) atomicAdd(&cnt[k0 + j], __popc(hits));
+      }
+    }
   }
+  __syncthreads();
+  for (int t = threadIdx.x; t < kvol; t += kIdxThreads) block_counts[(int64_t)t * nblk + blockIdx.x] = cnt[t];
 }
 
 // Single CTA of 1024 threads.  Warp w scans the counts of offsets w, w+32, ..; then the segment starts
@@ -393,26 +482,49 @@ compact_all_kernel(const int32_t* __restrict__ pair_out, const int32_t* __restri
   __shared__ int warp_cnt[kCompactAllMaxVol][kWarps];
   const int n = live_count(num_act_in, n_max);
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  constexpr int kBatch = 9;  // loads in flight per thread
   const int i = blockIdx.x * kIdxThreads + threadIdx.x;
   const int warp = threadIdx.x >> 5;
-  for (int k = 0; k < kvol; ++k) {
-    const int v = i < n ? __ldg(pair_out + (int64_t)k * n_max + i) : -1;
-    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
-    if (lane_id() == 0) warp_cnt[k][warp] = __popc(hits);
+  for (int k0 = 0; k0 < kvol; k0 += kBatch) {
+    int v[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) v[j] = (i < n && k0 + j < kvol) ? __ldg(pair_out + (int64_t)(k0 + j) * n_max + i) : -1;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const unsigned hits = __ballot_sync(0xffffffffu, v[j] >= 0);
+      if (lane_id() == 0 && k0 + j < kvol) warp_cnt[k0 + j][warp] = __popc(hits);
+    }
   }
   __syncthreads();
-  for (int k = 0; k < kvol; ++k) {
-    const int v = i < n ? __ldg(pair_out + (int64_t)k * n_max + i) : -1;
-    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
-    if (v < 0) continue;
-    int before = 0;
-    for (int w = 0; w < warp; ++w) before += warp_cnt[k][w];
-    const int64_t pos = (int64_t)seg[k] + block_prefix[(int64_t)k * nblk + blockIdx.x] + before +
-                        __popc(hits & lanemask_lt());
-    if (pos >= row_len) continue;
-    index[pos] = i;
-    index[row_len + pos] = v;
-    index[2 * row_len + pos] = k;
+  // counts -> first output position of every (offset, warp) of this CTA
+  if (threadIdx.x < kvol) {
+    const int k = threadIdx.x;
+    int pos = seg[k] + block_prefix[(int64_t)k * nblk + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = warp_cnt[k][w];
+      warp_cnt[k][w] = pos;
+      pos += c;
+    }
+  }
+  __syncthreads();
+  for (int k0 = 0; k0 < kvol; k0 += kBatch) {
+    int v[kBatch];
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j)
+      v[j] = (i < n && k0 + j < kvol) ? __ldg(pair_out + (int64_t)(k0 + j) * n_max + i) : -1;
+#pragma unroll
+    for (int j = 0; j < kBatch; ++j) {
+      const unsigned hits = __ballot_sync(0xffffffffu, v[j] >= 0);
+      if (v[j] >= 0) {
+        const int64_t pos = (int64_t)warp_cnt[k0 + j][warp] + __popc(hits & lanemask_lt());
+        if (pos < row_len) {
+          index[pos] = i;
+          index[row_len + pos] = v[j];
+          index[2 * row_len + pos] = k0 + j;
+        }
+      }
+    }
   }
 }
 
@@ -617,13 +729,18 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
                                                                          plan.cap_max);
   if (p->subm) {
     subm_insert_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max);
-    if (g.ndim == 3)
-      subm_probe3_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
-                                                       plan.pair_out, plan.block_counts, nblk);
-    else
+    if (g.ndim == 3 && !g.transpose && g.stride[0] == 1 && g.stride[1] == 1 && g.stride[2] == 1) {
+      if (g.ksize[1] == 3 && g.klast == 3)
+        subm_probe3_kernel<true><<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
+                                                               plan.pair_out, plan.block_counts, nblk);
+      else
+        subm_probe3_kernel<false><<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
+                                                                plan.pair_out, plan.block_counts, nblk);
+    } else {
       subm_probe_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
                                                                     plan.cap_max, plan.pair_out, plan.block_counts,
                                                                     nblk);
+    }
   } else {
     int32_t* out_coors = reinterpret_cast<int32_t*>(outputs[2]);
     int32_t* num_act_out = reinterpret_cast<int32_t*>(outputs[3]);
@@ -636,8 +753,8 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
     scan_totals_kernel<<<1, 1024, 0, st>>>(plan.winners, nblk, p->max_num_act_out, num_act_out);
     conv_assign_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g, plan.winners,
                                                      p->max_num_act_out, plan.slot_out, out_coors);
-    conv_translate_kernel<<<dim3(nblk, g.kvol), kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max,
-                                                                      plan.block_counts, nblk);
+    conv_translate_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max, g.kvol,
+                                                            plan.block_counts, nblk);
   }
   segment_scan_kernel<<<1, 1024, 0, st>>>(plan.block_counts, nblk, g.kvol, num_act_in, n_max, plan.seg, num_index);
   if (g.kvol <= kCompactAllMaxVol)

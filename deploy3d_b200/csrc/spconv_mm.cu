@@ -22,11 +22,23 @@ namespace {
 // ---------------------------------------------------------------------------------------------
 // Neighbour table
 // ---------------------------------------------------------------------------------------------
-__global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* tile_mask, int64_t tiles) {
+// `flags` holds one byte per (tile, offset < 32), cleared here, set by the scatter kernel with plain stores (many
+// writers, one value) and packed into the per-tile bit masks afterwards: atomics on the masks themselves serialise
+// on the few words all offsets of a tile share.
+__global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* flags32, int64_t flag_words) {
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
     table[i] = make_int4(-1, -1, -1, -1);
-    if (i < tiles) tile_mask[i] = 0u;
+    if (i < flag_words) flags32[i] = 0u;
   }
+}
+
+// One warp per tile: lane k reads the flag of offset k.
+__global__ void pack_mask_kernel(const unsigned char* __restrict__ flags, int64_t tiles,
+                                 uint32_t* __restrict__ tile_mask) {
+  const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  if (tile >= tiles) return;
+  const unsigned m = __ballot_sync(0xffffffffu, flags[tile * 32 + (threadIdx.x & 31)] != 0);
+  if ((threadIdx.x & 31) == 0) tile_mask[tile] = m;
 }
 
 // index rows: gatherIn | scatterOut | kernelOffset (trt/spconv/index_trt.cu:211-213); `inverse` swaps the
@@ -35,30 +47,39 @@ __global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* tile_mask,
 // convolution kernel can skip the others without scanning the ids.
 __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t row_len,
                                      const int32_t* __restrict__ num_index, int inverse, int kvol, int64_t m_max,
-                                     int32_t* __restrict__ table, uint32_t* __restrict__ tile_mask) {
+                                     int32_t* __restrict__ table, unsigned char* __restrict__ flags) {
   int64_t n = *num_index;
   n = n > row_len ? row_len : n;
   // grid-stride over the live part of the rulebook only (the rows are sized for the worst case, mostly unused);
   // whole warps iterate together so that the shuffle below is always fully populated
   const int64_t n_warp = (n + 31) & ~(int64_t)31;
-  for (int64_t p = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p < n_warp; p += (int64_t)gridDim.x * blockDim.x) {
-    bool valid = p < n;
-    int k = -1, g = -1, s = -1;
-    if (valid) {
-      k = __ldg(index + 2 * row_len + p);
-      valid = k >= 0 && k < kvol;  // else a padding entry
+  constexpr int kUnroll = 4;  // entries in flight per thread
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const int32_t* gather_row = index + (inverse ? row_len : 0);
+  const int32_t* scatter_row = index + (inverse ? 0 : row_len);
+  for (int64_t p0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; p0 < n_warp; p0 += kUnroll * stride) {
+    int k[kUnroll], g[kUnroll], s[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const int64_t p = p0 + u * stride;
+      const bool in = p < n;
+      k[u] = in ? __ldg(index + 2 * row_len + p) : -1;
+      g[u] = in ? __ldg(gather_row + p) : -1;
+      s[u] = in ? __ldg(scatter_row + p) : -1;
     }
-    if (valid) {
-      g = __ldg(index + (inverse ? row_len : 0) + p);
-      s = __ldg(index + (inverse ? 0 : row_len) + p);
-      valid = g >= 0 && s >= 0 && s < m_max;
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      if (p0 + u * stride >= n_warp) break;  // warp-uniform
+      // k outside [0, kvol) marks a padding entry
+      const bool valid = k[u] >= 0 && k[u] < kvol && g[u] >= 0 && s[u] >= 0 && s[u] < m_max;
+      // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
+      if (valid) table[((int64_t)(s[u] >> 7) * kvol + k[u]) * 128 + (s[u] & 127)] = g[u];
+      // one flag store per run of equal (tile, offset) in the warp: neighbouring entries mostly share both
+      const unsigned key = (valid && k[u] < 32) ? ((unsigned)(s[u] >> 7) << 5) | (unsigned)k[u] : 0xFFFFFFFFu;
+      const unsigned prev = __shfl_up_sync(0xffffffffu, key, 1);
+      if (key != 0xFFFFFFFFu && ((threadIdx.x & 31) == 0 || prev != key))
+        flags[(int64_t)(s[u] >> 7) * 32 + k[u]] = 1;
     }
-    // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
-    if (valid) table[((int64_t)(s >> 7) * kvol + k) * 128 + (s & 127)] = g;
-    // one atomicOr per run of equal (tile, offset) in the warp: neighbouring entries mostly share both
-    const unsigned key = (valid && k < 32) ? ((unsigned)(s >> 7) << 5) | (unsigned)k : 0xFFFFFFFFu;
-    const unsigned prev = __shfl_up_sync(0xffffffffu, key, 1);
-    if (key != 0xFFFFFFFFu && ((threadIdx.x & 31) == 0 || prev != key)) atomicOr(tile_mask + (s >> 7), 1u << k);
   }
 }
 
@@ -327,7 +348,8 @@ extern "C" size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_
   // rows are padded to a multiple of 128 entries so every 128-output tile can be read as a whole
   // followed by one 32-bit offset mask per tile (zero-filled together with the -1 ids: see prepare)
   int64_t pitch = (max_num_act_out + 127) / 128 * 128;
-  return table_ids_bytes(kernel_vol, max_num_act_out) + align_up((size_t)(pitch / 128) * sizeof(uint32_t), 256);
+  return table_ids_bytes(kernel_vol, max_num_act_out) + align_up((size_t)(pitch / 128) * sizeof(uint32_t), 256) +
+         align_up((size_t)(pitch / 128) * 32, 256);
 }
 
 extern "C" int d3d_spconv_mm_workspace(d3d_spconv_mm_t h, const d3d_tensor_desc* in, int n_in, size_t* bytes) {
@@ -347,11 +369,14 @@ extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_nu
   int64_t n16 = (int64_t)kernel_vol * pitch / 4;
   uint32_t* tile_mask = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(table) +
                                                     table_ids_bytes(kernel_vol, max_num_act_out));
-  table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16, tile_mask,
-                                                           pitch / 128);
+  const int64_t tiles = pitch / 128;
+  unsigned char* flags = reinterpret_cast<unsigned char*>(tile_mask) + align_up((size_t)tiles * sizeof(uint32_t), 256);
+  table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16,
+                                                           reinterpret_cast<uint32_t*>(flags), tiles * 8);
   if (index_row_len > 0)
     table_scatter_kernel<<<stream_grid(index_row_len, 256), 256, 0, st>>>(
-        index, index_row_len, num_index, inverse, kernel_vol, pitch, reinterpret_cast<int32_t*>(table), tile_mask);
+        index, index_row_len, num_index, inverse, kernel_vol, pitch, reinterpret_cast<int32_t*>(table), flags);
+  pack_mask_kernel<<<(unsigned)ceil_div(tiles * 32, 256), 256, 0, st>>>(flags, tiles, tile_mask);
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }
