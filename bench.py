@@ -161,6 +161,11 @@ def run_reference(args):
 # ------------------------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------------------------
+# dram__bytes_read.sum + dram__bytes_write.sum over the 21 SPConvMM launches of one config-4 frame, from the ncu capture
+# summarised in profiles/spconv_mm_tc_bench_layers_dram.md (cold L2 per launch: an upper bound for the stream)
+CONV_DRAM_BYTES_PER_FRAME = 5.12e9
+
+
 def conv_launch_times(pipe, frames, reps):
     """CUDA-event duration of every SPConvMM launch of a frame (eager replay of the layer list), averaged over
     `reps` frames.  Returns per-layer dicts with dense-equivalent and pair FLOPs."""
@@ -197,7 +202,8 @@ def conv_launch_times(pipe, frames, reps):
         esz = 2
         out.append(dict(layer=li, cin=cin, cout=cout, kvol=kvol, m=m, pairs=pairs, seconds=t,
                         flops_dense=2.0 * m * kvol * cin * cout, flops_pair=2.0 * pairs * cin * cout,
-                        bytes=m * cin * esz + m * cout * esz + kvol * cin * cout * esz + 4.0 * kvol * m))
+                        bytes=m * cin * esz + m * cout * esz + kvol * cin * cout * esz + 4.0 * kvol * m +
+                        (m * cout * esz if net.layers[li].residual else 0)))
     return out
 
 
@@ -325,7 +331,11 @@ def run_ours(args):
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_elapsed / args.steps * 1e3},
             "gpu_launches": launches_per_frame * args.steps,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                         "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                         "frac": achieved / peaks["bf16_tflops"],
+                         "traffic": CONV_DRAM_BYTES_PER_FRAME / len(tc),
+                         "traffic_unit": "bytes per launch (mean of the %d launches of a frame; ncu, L2 flushed before "
+                                         "every launch)" % len(tc),
+                         "algorithmic_bytes": sum(l["bytes"] for l in tc) / len(tc),
                          "kernel": "SPConvMM (tcgen05) over all %d layers of the backbone, dense-equivalent FLOPs "
                                    "2*M*kVol*Cin*Cout per launch, time = sum of per-launch CUDA-event durations"
                                    % len(tc),
