@@ -62,6 +62,10 @@ class Nms3dParams(ctypes.Structure):
     _fields_ = [("iou_threshold", ctypes.c_float)]
 
 
+class YoloX3dDecodeParams(ctypes.Structure):
+    _fields_ = [("stride", ctypes.c_int32), ("topk", ctypes.c_int32), ("class_ids", ctypes.c_int32 * 8)]
+
+
 _vp = ctypes.c_void_p
 _sz = ctypes.c_size_t
 _descp = ctypes.POINTER(TensorDesc)
@@ -117,6 +121,12 @@ SIGNATURES = {
     "d3d_nms3d_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(Nms3dParams)]),
     "d3d_nms3d_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(Nms3dParams))),
     "d3d_nms3d_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(Nms3dParams))),
+    "d3d_yolox3d_decode_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(YoloX3dDecodeParams)]),
+    "d3d_yolox3d_decode_num_outputs": (ctypes.c_int, [ctypes.POINTER(YoloX3dDecodeParams)]),
+    "d3d_yolox3d_decode_output_desc": (ctypes.c_int, [ctypes.POINTER(YoloX3dDecodeParams), _descp, ctypes.c_int,
+                                                      ctypes.c_int, _descp]),
+    "d3d_yolox3d_decode_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(YoloX3dDecodeParams))),
+    "d3d_yolox3d_decode_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(YoloX3dDecodeParams))),
     "d3d_nms3d_enqueue_static": (ctypes.c_int, [ctypes.POINTER(Nms3dParams), _descp, ctypes.c_int, _descp,
                                                  ctypes.c_int, _vpp, _vpp, _vp]),
 }

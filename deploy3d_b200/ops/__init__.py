@@ -11,8 +11,8 @@ from .spconv import (bev_densify, data_s_bev_densify, data_s_spconv_index, data_
                      spconv_mm)
 from .voxel_encoder import (cylinder_encoder, data_s_voxel_encoder, simple_mean_encoder)
 from .point_voxel_mapping import (data_s_gather_back, data_s_scatter_to, gather_back, scatter_to)
-from .decoder import nms3d
+from .decoder import data_s_yolox3d_decode, nms3d, yolox3d_decode
 
 __all__ = ["spconv_index", "spconv_mm", "bev_densify", "simple_mean_encoder", "cylinder_encoder", "scatter_to",
-           "gather_back", "nms3d", "data_s_spconv_index", "data_s_spconv_mm", "data_s_bev_densify",
+           "gather_back", "nms3d", "yolox3d_decode", "data_s_yolox3d_decode", "data_s_spconv_index", "data_s_spconv_mm", "data_s_bev_densify",
            "data_s_voxel_encoder", "data_s_scatter_to", "data_s_gather_back"]

@@ -271,16 +271,35 @@ class NMS3dPlugin(_PodPlugin):
         return [make_desc(D3D_FLOAT, tuple(d[0].dims[:d[0].nb_dims]))]
 
 
+class YoloX3dDecodePlugin(_PodPlugin):
+    """``YoloX3dDecode`` (trt/decoder/yolox3d_decode.cu:147-412): three outputs per class id of the blob."""
+    name = "YoloX3dDecode"
+    _prefix = "d3d_yolox3d_decode"
+    _params_t = _lib.YoloX3dDecodeParams
+
+    def output_descs(self, d):
+        n = lib().d3d_yolox3d_decode_num_outputs(ctypes.byref(self.p))
+        out = []
+        for i in range(n):
+            desc = _lib.TensorDesc()
+            check("d3d_yolox3d_decode_output_desc",
+                  lib().d3d_yolox3d_decode_output_desc(ctypes.byref(self.p), desc_array(d), len(d), i,
+                                                       ctypes.byref(desc)))
+            out.append(desc)
+        return out
+
+
 _REGISTRY = {
     "SPConvIdx1d": SPConvIdxPlugin, "SPConvIdx2d": SPConvIdxPlugin, "SPConvIdx3d": SPConvIdxPlugin,
     "SPConvIdx4d": SPConvIdxPlugin, "SPConvMM": SPConvMMPlugin, "BEVDensify": BEVDensifyPlugin,
     "SimpleMeanEncoder": SimpleMeanEncoderPlugin, "CylinderEncoder": CylinderEncoderPlugin,
     "ScatterTo": ScatterToPlugin, "GatherBack": GatherBackPlugin, "NMS3d": NMS3dPlugin,
+    "YoloX3dDecode": YoloX3dDecodePlugin,
 }
 
 
 def registered_plugins():
-    """Names under which the reference registers its creators (REGISTER_TENSORRT_PLUGIN), minus YoloX3dDecode."""
+    """Names under which the reference registers its creators (REGISTER_TENSORRT_PLUGIN)."""
     return sorted(_REGISTRY)
 
 

@@ -274,6 +274,34 @@ int d3d_nms3d_enqueue_static(const d3d_nms3d_params* p, const d3d_tensor_desc* i
                              const d3d_tensor_desc* out, int n_out, const void* const* inputs, void* const* outputs,
                              void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * YoloX3dDecode -- per class, the topK BEV cells by class score, decoded into boxes; the step before NMS3d.
+ * Replaces decoder::YoloX3dDecodePlugin (trt/decoder/yolox3d_decode.cu:139-412).
+ * data_s (pack(1), :139-145): int32 stride, int32 topk, int32 classIds[8] (unused entries -1).
+ * Inputs : 0 cls_scores float/half [B, C, Y, X], 1 bbox_preds same dtype [B, 9+a, Y, X]
+ *          (dx, dy, z, log w, log l, log h, yaw, sin, cos, extras), 2 voxel_config float [6] (x_min, y_min, z_min,
+ *          voxel size, ..).
+ * Outputs: for class i < C: 3i topk_class_ids int32 [B, K], 3i+1 topk_scores float [B, K] (descending; equal scores
+ *          in ascending cell order, as the reference's stable sort leaves them; -1 for an invalid box),
+ *          3i+2 topk_boxes float [B, K, 7+a]; K = min(topk, Y*X) (:192-206).
+ * Workspace: none (the reference sorts all B*C*Y*X scores and needs the cub scratch, :255-298).
+ * K above 4096 is refused with D3D_ERR_TOO_LARGE.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct {
+  int32_t stride;
+  int32_t topk;
+  int32_t class_ids[8];
+} d3d_yolox3d_decode_params;
+int d3d_yolox3d_decode_parse(const void* data_s, size_t len, d3d_yolox3d_decode_params* p);
+int d3d_yolox3d_decode_num_outputs(const d3d_yolox3d_decode_params* p);
+int d3d_yolox3d_decode_output_desc(const d3d_yolox3d_decode_params* p, const d3d_tensor_desc* in, int n_in, int index,
+                                   d3d_tensor_desc* out);
+int d3d_yolox3d_decode_workspace(const d3d_yolox3d_decode_params* p, const d3d_tensor_desc* in, int n_in,
+                                 size_t* bytes);
+int d3d_yolox3d_decode_enqueue(const d3d_yolox3d_decode_params* p, const d3d_tensor_desc* in, int n_in,
+                               const d3d_tensor_desc* out, int n_out, const void* const* inputs, void* const* outputs,
+                               void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

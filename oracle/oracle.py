@@ -215,6 +215,75 @@ def nms3d(scores, boxes, thr=0.1):
     return out
 
 
+def yolox3d_decode(cls_scores, bbox_preds, voxel_config, stride, class_ids, topk):
+    """Restatement of the reference's YoloX3dDecode in numpy (trt/decoder/yolox3d_decode.cu): per (batch, class) a
+    stable descending sort of the Y*X scores (:341-355; equal scores keep ascending cell order), the first
+    K = min(topk, Y*X) entries (:192-206) decoded by `kernel::decode` (:25-126) with its float / double mix:
+    float arithmetic, M_PI terms in double, floorf on the value rounded to float.  Parity unpinned beyond the
+    reference's source: its tests hold no vectors for this operator.
+    Returns [(class_ids int32 [B,K], scores float32 [B,K], boxes float32 [B,K,7+a])] per class."""
+    f32, f64 = np.float32, np.float64
+    s = np.asarray(cls_scores).astype(f32)
+    p = np.asarray(bbox_preds).astype(f32)
+    cfg = _f32(voxel_config)
+    b, c, ny, nx = s.shape
+    n = ny * nx
+    k = min(int(topk), n)
+    extra = p.shape[1] - 9
+    feat_stride = f32(f32(stride) * cfg[3])
+    out = []
+    with np.errstate(all="ignore"):
+        for ci in range(c):
+            ids = np.full((b, k), class_ids[ci], dtype=np.int32)
+            sc = np.empty((b, k), dtype=f32)
+            bx = np.empty((b, k, 7 + extra), dtype=f32)
+            for bi in range(b):
+                flat = s[bi, ci].reshape(-1)
+                key = np.where(flat == 0, f32(0), flat)  # the sort treats -0 and +0 alike
+                order = np.argsort(-key.astype(f64), kind="stable")[:k]
+                pr = p[bi].reshape(9 + extra, n)[:, order]
+                score = flat[order].copy()
+                cx = (pr[0] + (order % nx).astype(f32)).astype(f32)
+                cx_valid = (cx <= f32(nx)) & (cx >= 0)
+                cx = (cfg[0] + feat_stride * cx).astype(f32)
+                cy = (pr[1] + (order // nx).astype(f32)).astype(f32)
+                cy_valid = (cy <= f32(ny)) & (cy >= 0)
+                cy = (cfg[1] + feat_stride * cy).astype(f32)
+                cz = pr[2].copy()
+                dx = (feat_stride * np.exp(pr[3])).astype(f32)
+                dy = (feat_stride * np.exp(pr[4])).astype(f32)
+                dz = np.exp(pr[5]).astype(f32)
+                yaw = pr[6].copy()
+                ds, dc = pr[7], pr[8]
+                direction = np.arctan2(ds, dc).astype(f32)
+                ok = (np.isfinite(cx) & np.isfinite(cy) & np.isfinite(cz) & np.isfinite(dx) & np.isfinite(dy) &
+                      np.isfinite(dz) & np.isfinite(yaw) & (dx > 0) & (dy > 0) & (dz > 0) & ((ds != 0) | (dc != 0)) &
+                      cx_valid & cy_valid)
+                square = ok & (f32(0.9) * dx < dy) & (dy < f32(1.11) * dx)
+                longish = ok & ~square
+                # elongated boxes: make dx the long side, then move yaw into the half-plane of the direction head
+                swap = longish & (dy > dx)
+                yaw_l = np.where(swap, (yaw.astype(f64) + np.pi / 2).astype(f32), yaw)
+                dx_l, dy_l = np.where(swap, dy, dx), np.where(swap, dx, dy)
+                q = ((direction - yaw_l).astype(f32).astype(f64) / np.pi + 0.5).astype(f32)
+                yaw_l = (yaw_l.astype(f64) + np.floor(q).astype(f64) * np.pi).astype(f32)
+                q = (yaw_l.astype(f64) / (2 * np.pi) + 0.5).astype(f32)
+                yaw_l = (yaw_l.astype(f64) - np.floor(q).astype(f64) * (2 * np.pi)).astype(f32)
+                big = np.maximum(dx, dy)
+                sc[bi] = np.where(ok, score, f32(-1))
+                bx[bi, :, 0] = np.where(ok, cx, f32(10000))
+                bx[bi, :, 1] = np.where(ok, cy, f32(10000))
+                bx[bi, :, 2] = np.where(ok, cz, f32(10000))
+                bx[bi, :, 3] = np.where(square, big, np.where(longish, dx_l, f32(1)))
+                bx[bi, :, 4] = np.where(square, big, np.where(longish, dy_l, f32(1)))
+                bx[bi, :, 5] = np.where(ok, dz, f32(1))
+                bx[bi, :, 6] = np.where(square, direction, np.where(longish, yaw_l, f32(0)))
+                for e in range(extra):
+                    bx[bi, :, 7 + e] = pr[9 + e]
+            out.append((ids, sc, bx))
+    return out
+
+
 def bev_iou(a, b):
     a, b = _f32(a), _f32(b)
     return float(lib().orc_bev_iou(_p(a, _f32p), _p(b, _f32p)))

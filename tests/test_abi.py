@@ -26,11 +26,24 @@ def test_registry_matches_reference_names(d3d):
     from deploy3d_b200.plugins import deserialize_plugin, registered_plugins
     assert registered_plugins() == sorted(["SPConvIdx1d", "SPConvIdx2d", "SPConvIdx3d", "SPConvIdx4d", "SPConvMM",
                                            "BEVDensify", "SimpleMeanEncoder", "CylinderEncoder", "ScatterTo",
-                                           "GatherBack", "NMS3d"])
+                                           "GatherBack", "NMS3d", "YoloX3dDecode"])
     with pytest.raises(KeyError):
         deserialize_plugin("NoSuchPlugin", b"")
     with pytest.raises(KeyError):
         deserialize_plugin("NMS3d", b"", version="1.0")
+
+
+def test_yolox3d_decode_blob_round_trip(d3d):
+    """The exporter's blob (deploy3d/symfun/ops/decoder/yolox3d_decode.py:43-50): stride, topk, 8 class ids."""
+    from deploy3d_b200 import _lib
+    from deploy3d_b200.plugins import deserialize_plugin
+    blob = d3d.data_s_yolox3d_decode(8, (0, 3, 7), 500)
+    assert len(blob) == 40
+    plug = deserialize_plugin("YoloX3dDecode", blob)
+    assert (plug.p.stride, plug.p.topk, list(plug.p.class_ids)) == (8, 500, [0, 3, 7, -1, -1, -1, -1, -1])
+    assert _lib.lib().d3d_yolox3d_decode_num_outputs(plug._params_ref()) == 9
+    with pytest.raises(_lib.D3DError):
+        deserialize_plugin("YoloX3dDecode", blob[:39])
 
 
 def test_spconv_index_blob_round_trip(d3d):

@@ -250,3 +250,31 @@ def test_cylinder_against_numpy(orc):
                            pts[:, :2], pts[:, 3:]], 1)
     assert np.allclose(aug[valid], want[valid], atol=1e-3, rtol=1e-3)
     assert (aug[~valid] == 0).all()
+
+
+def test_yolox3d_decode_oracle_properties(orc):
+    """The numpy restatement of YoloX3dDecode: K = min(topk, Y*X), scores non-increasing per row apart from the
+    -1 of invalid boxes, equal scores in ascending cell order, nearly square boxes get dx == dy and the heading of
+    the direction head, headings of elongated boxes end up in (-pi, pi] on the side of the direction head."""
+    r = rng(5)
+    b, c, ny, nx = 2, 2, 9, 11
+    scores = (np.round(r.uniform(0, 1, (b, c, ny, nx)) * 10) / 10).astype(np.float32)
+    preds = r.uniform(-1, 1, (b, 9, ny, nx)).astype(np.float32)
+    preds[:, 0:2] = r.uniform(0, 1, (b, 2, ny, nx))
+    cfg = np.array([-10, -20, -3, 0.25, 0.25, 4], dtype=np.float32)
+    out = orc.yolox3d_decode(scores, preds, cfg, 4, (2, 5), 1000)
+    assert len(out) == 2
+    for ci, (ids, sc, bx) in enumerate(out):
+        assert ids.shape == (b, ny * nx) and (ids == (2, 5)[ci]).all() and bx.shape == (b, ny * nx, 7)
+        for bi in range(b):
+            flat = scores[bi, ci].reshape(-1)
+            order = np.lexsort((np.arange(flat.size), -flat))
+            assert (np.where(sc[bi] >= 0, sc[bi], flat[order]) == flat[order]).all()
+            x0 = -10 + 4 * 0.25 * (preds[bi, 0].reshape(-1)[order] + order % nx)
+            ok = sc[bi] >= 0
+            np.testing.assert_allclose(bx[bi, ok, 0], x0[ok], rtol=1e-5, atol=1e-5)
+            assert (np.abs(bx[bi, ok, 6]) <= np.pi + 1e-5).all()
+            square = ok & (bx[bi, :, 3] == bx[bi, :, 4])
+            want_dir = np.arctan2(preds[bi, 7].reshape(-1)[order], preds[bi, 8].reshape(-1)[order])
+            np.testing.assert_allclose(bx[bi, square, 6], want_dir[square], rtol=1e-5, atol=1e-6)
+            assert (bx[bi, ok & ~square, 3] >= bx[bi, ok & ~square, 4]).all()
