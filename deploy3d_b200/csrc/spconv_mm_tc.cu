@@ -158,9 +158,13 @@ __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-               : "memory");
+__device__ __forceinline__ void umma_commit_if(uint32_t run, uint64_t* bar) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %1, 0;\n\t"
+      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)),
+      "r"(run)
+      : "memory");
 }
 // D (+)= A * B, issued only when `run` != 0 (predicated, not branched around).
 __device__ __forceinline__ void umma_f16_if(uint32_t run, uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
@@ -493,6 +497,8 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
   if (resident && !mbar_wait(&sh->b_ready, 0, abort_flag, 23)) return;
   int stage = 0, acc = 0;
   uint32_t phase = 0, acc_phase = 0;
+  const int num_stages = p.stages, kvol = p.kvol, kparts = p.kparts;
+  const uint32_t lane0 = (threadIdx.x & 31) == 0 ? 1u : 0u;  // the lane that issues; the others keep it company
   uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
     const int next = tile + gridDim.x;
@@ -502,32 +508,40 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
       tc_fence_after();
       const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.cout);
       uint32_t accumulate = 0;
-      for (int base = 0; base < p.kvol; base += kGroup) {
+      int part = 0;
+      for (int base = 0; base < kvol;) {
         const uint32_t take = (mask >> base) & gmask;
-        if (!take) continue;
-        for (int part = 0; part < p.kparts; ++part) {
+        if (take) {
+          // the full barrier guards shared memory only: no tcgen05 fence is needed, but the rows written by
+          // cp.async (generic proxy) must be made visible to the tensor core's reads (async proxy)
           if (!mbar_wait(&sh->full[stage], phase, abort_flag, 21)) return;
-          tc_fence_after();
-          fence_proxy_async();  // rows written by cp.async (generic proxy) -> tensor-core reads (async proxy)
+          fence_proxy_async();
           const uint32_t a_lo = tiles_lo + (uint32_t)stage * stage_step;
           uint32_t b_lo = resident ? bres_lo + (uint32_t)base * b_step : a_lo + b_in_stage;
 #pragma unroll
           for (int e = 0; e < kGroup; ++e, b_lo += b_step) {
-            const uint32_t run = (take >> e) & 1u;
+            const uint32_t present = (take >> e) & 1u, run = present & lane0;
 #pragma unroll
             for (int ks = 0; ks < kSteps; ++ks) {
               // 32 bytes per K step inside the swizzle span, the next 64-column block every 4 steps
               const uint32_t adv_a = (uint32_t)e * a_step + (uint32_t)(ks >> 2) * cs_a + (uint32_t)(ks & 3) * 2u;
               const uint32_t adv_b = (uint32_t)(ks >> 2) * cs_b + (uint32_t)(ks & 3) * 2u;
               umma_f16_if(run, d_addr, desc_hi | (a_lo + adv_a), desc_hi | (b_lo + adv_b), idesc, accumulate);
-              accumulate |= run;
+              accumulate |= present;
             }
           }
-          umma_commit(&sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
-          if (++stage == p.stages) stage = 0, phase ^= 1;
+          umma_commit_if(lane0, &sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
+          const bool wrap = stage + 1 == num_stages;
+          stage = wrap ? 0 : stage + 1;
+          phase ^= wrap ? 1u : 0u;
+          ++part;
         }
+        // next K part of the same window, or the next window (one loop, one back edge: branches are what costs)
+        const bool window_done = !take || part == kparts;
+        base += window_done ? kGroup : 0;
+        part = window_done ? 0 : part;
       }
-      umma_commit(&sh->acc_full[acc]);
+      umma_commit_if(lane0, &sh->acc_full[acc]);
       if (++acc == kNumAcc) acc = 0, acc_phase ^= 1;
     }
     mask = next_mask;
@@ -594,7 +608,7 @@ spconv_mm_tc_kernel(const __grid_constant__ CUtensorMap map_b, const TcParams p)
   if (warp < kProducerThreads / 32) {
     producer_role<2 * kSteps, kGroup>(p, s, threadIdx.x);
   } else if (warp == kMmaWarp) {
-    if (lane == 0) mma_role<kSteps, kGroup>(p, s, tmem_base);
+    mma_role<kSteps, kGroup>(p, s, tmem_base);
     __syncwarp();
   } else if (warp == kControlWarp) {
     if (lane == 0) control_role(p, s, &map_b);
