@@ -233,22 +233,26 @@ suppress_kernel(const unsigned long long* __restrict__ mask, const float* __rest
 // only, instead of waiting for one global load per kept box.
 constexpr int kStagedMaxWords = 32;
 
-__global__ void __launch_bounds__(32)
+constexpr int kStagedThreads = 128;  // four warps load the rows of a block, the first one sweeps them
+
+__global__ void __launch_bounds__(kStagedThreads)
 suppress_staged_kernel(const unsigned long long* __restrict__ mask, const float* __restrict__ in_scores, int k, int nw,
                        float* __restrict__ out_scores) {
   __shared__ unsigned long long rows[kNmsBlock * kStagedMaxWords];
-  const int b = blockIdx.x, lane = threadIdx.x;
+  const int b = blockIdx.x, tid = threadIdx.x, lane = tid & 31;
+  const bool sweeper = tid < 32;
   const unsigned long long* mk = mask + (int64_t)b * k * nw;
-  unsigned long long remv = 0ull;  // word `lane` of the removed set
+  unsigned long long remv = 0ull;  // word `lane` of the removed set (first warp)
   for (int blk = 0; blk < nw; ++blk) {
     const int base = blk * kNmsBlock;
     const int nbox = min(k - base, kNmsBlock);
     const unsigned long long* src = mk + (int64_t)base * nw;  // nbox consecutive rows of nw words
     const int words = nbox * nw;
-    __syncwarp();
-#pragma unroll 8
-    for (int f = lane; f < words; f += 32) rows[f] = __ldg(src + f);
-    __syncwarp();
+    __syncthreads();  // the previous block's rows are no longer needed
+#pragma unroll 4
+    for (int f = tid; f < words; f += kStagedThreads) rows[f] = __ldg(src + f);
+    __syncthreads();
+    if (!sweeper) continue;
     const unsigned long long d0 = lane < nbox ? rows[lane * nw + blk] : 0ull;
     const unsigned long long d1 = lane + 32 < nbox ? rows[(lane + 32) * nw + blk] : 0ull;
     unsigned long long cur = __shfl_sync(0xffffffffu, remv, blk);
@@ -319,7 +323,7 @@ extern "C" int d3d_nms3d_enqueue(const d3d_nms3d_params* p, const d3d_tensor_des
   overlap_mask_kernel<<<dim3(nw, nw, b), 256, 0, st>>>(reinterpret_cast<const float*>(inputs[1]), k, bd,
                                                        p->iou_threshold, nw, mask);
   if (nw <= kStagedMaxWords)
-    suppress_staged_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
+    suppress_staged_kernel<<<b, kStagedThreads, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
                                              reinterpret_cast<float*>(outputs[0]));
   else
     suppress_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,

@@ -287,6 +287,49 @@ __global__ void conv_insert_kernel(unsigned long long* table, const int32_t* __r
   }
 }
 
+// 3-D specialisation for kernels of at most 3 taps per axis, same outputs.  One thread per input voxel: the output
+// coordinate of every tap is resolved once per axis (3 + 3 + 3 small computations, the only divisions), then the
+// offsets are walked with those in registers; only the combinations valid on all three axes touch the hash table.
+__global__ void __launch_bounds__(kIdxThreads)
+conv_insert3_kernel(unsigned long long* table, const int32_t* __restrict__ coors, const int32_t* num_act_in,
+                    int64_t n_max, Geometry g, int fan, uint32_t cap_max, int32_t* __restrict__ pair_out) {
+  const int n = live_count(num_act_in, n_max);
+  const int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  if (i >= n) return;
+  const uint32_t mask = hash_capacity((long long)n * fan, cap_max) - 1;
+  const int4 c = __ldg(reinterpret_cast<const int4*>(coors) + i);
+  const bool batch_ok = c.x >= 0 && c.x < g.shape[0];
+  int o0[3], o1[3], o2[3];  // output coordinate per tap, -1 = this tap reaches no output
+#pragma unroll
+  for (int t = 0; t < 3; ++t) {
+    int o;
+    o0[t] = (t < g.ksize[0] && out_coord(g, 0, c.y, t, &o)) ? o : -1;
+    o1[t] = (t < g.ksize[1] && out_coord(g, 1, c.z, t, &o)) ? o : -1;
+    o2[t] = (t < g.ksize[2] && out_coord(g, 2, c.w, t, &o)) ? o : -1;
+  }
+  const uint32_t s1 = (uint32_t)g.shape[1], s2 = (uint32_t)g.shape[2], s3 = (uint32_t)g.shape[3];
+  const uint32_t pair_base = (uint32_t)(i * g.kvol);
+#pragma unroll
+  for (int k0 = 0; k0 < 3; ++k0) {
+#pragma unroll
+    for (int k1 = 0; k1 < 3; ++k1) {
+#pragma unroll
+      for (int k2 = 0; k2 < 3; ++k2) {
+        if (k0 < g.ksize[0] && k1 < g.ksize[1] && k2 < g.ksize[2]) {
+          const int k = (k0 * g.ksize[1] + k1) * g.ksize[2] + k2;
+          int v = -1;
+          if (batch_ok && o0[k0] >= 0 && o1[k1] >= 0 && o2[k2] >= 0) {
+            const uint32_t key = (((uint32_t)c.x * s1 + (uint32_t)o0[k0]) * s2 + (uint32_t)o1[k1]) * s3 + (uint32_t)o2[k2];
+            const uint32_t slot = hash_insert_min(table, mask, key, pair_base + (uint32_t)k);
+            v = slot == 0xFFFFFFFFu ? -1 : (int)slot;
+          }
+          pair_out[(int64_t)k * n_max + i] = v;
+        }
+      }
+    }
+  }
+}
+
 // A pair "wins" its output voxel when its id is the one left in the slot.
 __device__ __forceinline__ bool is_winner(const unsigned long long* table, int slot, uint32_t pair_id) {
   return slot >= 0 && (uint32_t)table[slot] == pair_id;
@@ -746,8 +789,12 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
     int32_t* num_act_out = reinterpret_cast<int32_t*>(outputs[3]);
     D3D_REQUIRE(out_coors && num_act_out, D3D_ERR_INVALID_ARGUMENT);
     D3D_REQUIRE(out[2].dims[0] >= p->max_num_act_out, D3D_ERR_INVALID_ARGUMENT);
-    conv_insert_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.fan,
-                                                                   plan.cap_max, plan.pair_out);
+    if (g.ndim == 3 && g.ksize[0] <= 3 && g.ksize[1] <= 3 && g.ksize[2] <= 3)
+      conv_insert3_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.fan,
+                                                        plan.cap_max, plan.pair_out);
+    else
+      conv_insert_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
+                                                                     plan.fan, plan.cap_max, plan.pair_out);
     conv_count_winners_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g.kvol,
                                                             plan.winners);
     scan_totals_kernel<<<1, 1024, 0, st>>>(plan.winners, nblk, p->max_num_act_out, num_act_out);
