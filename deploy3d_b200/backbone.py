@@ -117,6 +117,9 @@ class SparseNet:
                     assert L.kind != "inverse", "an inverse layer needs the rulebook of its conv"
                     rb = _Rulebook()
                     rb.kind, rb.in_set, rb.ksize = L.kind, cur, L.ksize
+                    # SubM with an odd kernel and 'same' padding: offsets k and kVol-1-k mirror each other
+                    rb.mirror = (L.kind == "subm" and all(k % 2 == 1 for k in L.ksize) and
+                                 tuple(L.padding) == tuple(k // 2 for k in L.ksize))
                     rb.kvol = int(np.prod(L.ksize))
                     subm = L.kind == "subm"
                     if subm:
@@ -198,7 +201,8 @@ class SparseNet:
                     rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor,
                                       outputs=[rb.index, rb.num_index, dst["coors"], dst["num"],
                                                rb.out_shape_tensor])
-                SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd)
+                SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd,
+                                       mirror=rb.mirror)
                 if rb.table_inv is not None:
                     SPConvMMPlugin.prepare(rb.kvol, True, src["cap"], rb.index, rb.num_index, table=rb.table_inv)
                 built.add(L.key)

@@ -46,8 +46,8 @@ __global__ void pack_mask_kernel(const unsigned char* __restrict__ flags, int64_
 // Besides the ids, every tile of 128 outputs gets a bit mask of the kernel offsets (< 32) that feed it, so that the
 // convolution kernel can skip the others without scanning the ids.
 __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t row_len,
-                                     const int32_t* __restrict__ num_index, int inverse, int kvol, int64_t m_max,
-                                     int32_t* __restrict__ table, unsigned char* __restrict__ flags) {
+                                     const int32_t* __restrict__ num_index, int inverse, int mirror, int kvol,
+                                     int64_t m_max, int32_t* __restrict__ table, unsigned char* __restrict__ flags) {
   int64_t n = *num_index;
   n = n > row_len ? row_len : n;
   // grid-stride over the live part of the rulebook only (the rows are sized for the worst case, mostly unused);
@@ -66,6 +66,13 @@ __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t 
       k[u] = in ? __ldg(index + 2 * row_len + p) : -1;
       g[u] = in ? __ldg(gather_row + p) : -1;
       s[u] = in ? __ldg(scatter_row + p) : -1;
+      // A mirror-symmetric SubM rulebook holds (g, s) under offset k exactly when it holds (s, g) under
+      // kvol - 1 - k.  Reading every entry as its mirror image makes the table writes follow the ascending gather
+      // index of the segment: neighbouring lanes then hit the same few table rows instead of scattered ones.
+      if (mirror && k[u] >= 0 && k[u] < kvol) {
+        const int t = g[u];
+        g[u] = s[u], s[u] = t, k[u] = kvol - 1 - k[u];
+      }
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
@@ -359,11 +366,14 @@ extern "C" int d3d_spconv_mm_workspace(d3d_spconv_mm_t h, const d3d_tensor_desc*
   return D3D_OK;
 }
 
-extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_num_act_out, const int32_t* index,
+extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int mode, int64_t max_num_act_out, const int32_t* index,
                                      int64_t index_row_len, const int32_t* num_index, void* table, void* stream) {
-  D3D_REQUIRE(kernel_vol >= 1 && max_num_act_out >= 0 && index_row_len >= 0, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(kernel_vol >= 1 && max_num_act_out >= 0 && index_row_len >= 0 && mode >= 0 && mode <= 3,
+              D3D_ERR_INVALID_ARGUMENT);
   if (max_num_act_out == 0) return D3D_OK;
   D3D_REQUIRE(index && num_index && table, D3D_ERR_INVALID_ARGUMENT);
+  const int inverse = mode & 1;
+  const int mirror = (mode & 2) && !inverse;  // a symmetric rulebook is its own inverse
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int64_t pitch = (max_num_act_out + 127) / 128 * 128;
   int64_t n16 = (int64_t)kernel_vol * pitch / 4;
@@ -375,7 +385,7 @@ extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_nu
                                                            reinterpret_cast<uint32_t*>(flags), tiles * 8);
   if (index_row_len > 0)
     table_scatter_kernel<<<stream_grid(index_row_len, 256), 256, 0, st>>>(
-        index, index_row_len, num_index, inverse, kernel_vol, pitch, reinterpret_cast<int32_t*>(table), flags);
+        index, index_row_len, num_index, inverse, mirror, kernel_vol, pitch, reinterpret_cast<int32_t*>(table), flags);
   pack_mask_kernel<<<(unsigned)ceil_div(tiles * 32, 256), 256, 0, st>>>(flags, tiles, tile_mask);
   D3D_CHECK_LAUNCH();
   return D3D_OK;

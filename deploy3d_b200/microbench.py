@@ -46,7 +46,7 @@ def main():
     outs = idx_plug.enqueue(coors, num_in, shape)
     num_out = num_in if subm else outs[3]
     m = int(num_out.item())
-    table = SPConvMMPlugin.prepare(27, False, max_out, outs[0], outs[1])
+    table = SPConvMMPlugin.prepare(27, False, max_out, outs[0], outs[1], mirror=subm)
     pairs = int((outs[0][2, :int(outs[1].item())] >= 0).sum().item())
     tdt = torch.float16 if args.dtype == "fp16" else torch.bfloat16
     w = synth.kaiming_weight(rng, 27, args.cin, args.cout)
@@ -75,7 +75,7 @@ def main():
         e0.record()
         for _ in range(args.index_reps):
             outs = idx_plug.enqueue(coors, num_in, shape, outputs=list(outs))
-            SPConvMMPlugin.prepare(27, False, max_out, outs[0], outs[1], table=table)
+            SPConvMMPlugin.prepare(27, False, max_out, outs[0], outs[1], table=table, mirror=subm)
         e1.record()
         torch.cuda.synchronize()
         res["us_rulebook_and_table"] = e0.elapsed_time(e1) * 1e3 / args.index_reps

@@ -166,14 +166,16 @@ class SPConvMMPlugin(_Plugin):
         return int(lib().d3d_spconv_mm_table_bytes(int(kernel_vol), int(max_num_act_out)))
 
     @staticmethod
-    def prepare(kernel_vol, inverse, max_num_act_out, index, num_index, table=None, stream=None):
+    def prepare(kernel_vol, inverse, max_num_act_out, index, num_index, table=None, stream=None, mirror=False):
+        """`mirror`: the rulebook is a mirror-symmetric SubM rulebook (same table, faster build)."""
         nbytes = SPConvMMPlugin.table_bytes(kernel_vol, max_num_act_out)
         if table is None:
             table = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=index.device)
         assert table.numel() >= nbytes
         with torch.cuda.device(index.device):
             check("d3d_spconv_mm_prepare",
-                  lib().d3d_spconv_mm_prepare(int(kernel_vol), int(bool(inverse)), int(max_num_act_out),
+                  lib().d3d_spconv_mm_prepare(int(kernel_vol), int(bool(inverse)) | (2 if mirror else 0),
+                                              int(max_num_act_out),
                                               ctypes.c_void_p(index.data_ptr()), int(index.shape[1]),
                                               ctypes.c_void_p(num_index.data_ptr()),
                                               ctypes.c_void_p(table.data_ptr()), _stream_ptr(stream)))

@@ -157,9 +157,14 @@ int d3d_spconv_mm_enqueue(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int
 /* Two-step form for callers that run several SPConvMM layers over one rulebook (the reference
  * shares rulebooks through an indice_key dictionary, tests/cylinder/test_cylinder3d.py:52-75):
  * prepare builds the neighbour table once, run consumes it.  `table` must hold
- * d3d_spconv_mm_table_bytes(kVol, maxNumActOut) bytes. */
+ * d3d_spconv_mm_table_bytes(kVol, maxNumActOut) bytes.
+ * `mode`: bit 0 = inverse (swap the gather and scatter rows, trt/spconv/mm_trt.cu:174-177); bit 1 = the caller
+ * asserts that the rulebook is a mirror-symmetric SubM rulebook (odd kernel, padding = dilation * (k - 1) / 2 on
+ * every axis, so that offset k and kVol-1-k hold each other's pairs with the roles swapped -- the property the
+ * reference's test checks, tests/spconv/test_spconv.py:101-108); the table is then written in gather order, which
+ * is faster.  The result is the same table.  The plugin-level d3d_spconv_mm_enqueue never sets bit 1. */
 size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out);
-int d3d_spconv_mm_prepare(int kernel_vol, int inverse, int64_t max_num_act_out, const int32_t* index,
+int d3d_spconv_mm_prepare(int kernel_vol, int mode, int64_t max_num_act_out, const int32_t* index,
                           int64_t index_row_len, const int32_t* num_index, void* table, void* stream);
 int d3d_spconv_mm_run(d3d_spconv_mm_t handle, int dtype, const void* in_feats, int64_t max_num_act_in,
                       const int32_t* num_act_out, const void* table, void* out_feats,

@@ -25,12 +25,12 @@ def _kernel_error():
     return code.value
 
 
-def _rulebook(d3d, coors, shape_b, ks, st, pd, subm, max_out):
+def _rulebook(d3d, coors, shape_b, ks, st, pd, subm, max_out, dilation=(1, 1, 1)):
     n = coors.shape[0]
     num_in = torch.tensor([n], dtype=torch.int32, device=DEV)
     outs = d3d.spconv_index(_t(coors), num_in, torch.empty([shape_b[0], 0] + shape_b[1:], dtype=torch.int32,
                                                            device=DEV),
-                            ks, st, pd, (1, 1, 1), (0, 0, 0), max_out, subm, False)
+                            ks, st, pd, tuple(dilation), (0, 0, 0), max_out, subm, False)
     return outs, num_in
 
 
@@ -116,3 +116,25 @@ def test_ragged_and_empty_tiles(d3d, orc):
         coors = unique_coors(rng(20 + n), n, [1, 40, 40, 40])
         outs, num_in = _rulebook(d3d, coors, [1, 40, 40, 40], (3, 3, 3), (1, 1, 1), (1, 1, 1), True, n + 300)
         _run(d3d, orc, outs, num_in, num_in, n, n + 300, 16, 32, (3, 3, 3), False, "fp16", 30 + n)
+
+
+@pytest.mark.parametrize("ks,dil", [((3, 3, 3), (1, 1, 1)), ((3, 1, 3), (1, 1, 2)), ((5, 3, 3), (1, 1, 1))])
+def test_mirror_table_build_gives_the_same_table(d3d, ks, dil):
+    """A SubM rulebook with 'same' padding is mirror-symmetric; building the neighbour table in gather order from
+    the mirrored entries must give exactly the table (ids and per-tile offset masks) of the generic scatter."""
+    pad = tuple(d * (k // 2) for k, d in zip(ks, dil))
+    shape = [2, 12, 30, 28]
+    coors = unique_coors(rng(21), 3000, shape)
+    outs, num_in = _rulebook(d3d, coors, shape, ks, (1, 1, 1), pad, True, 3000, dilation=dil)
+    from deploy3d_b200.plugins import SPConvMMPlugin
+    kvol = int(np.prod(ks))
+    plain = SPConvMMPlugin.prepare(kvol, False, 3000, outs[0], outs[1])
+    mirrored = SPConvMMPlugin.prepare(kvol, False, 3000, outs[0], outs[1], mirror=True)
+    tiles, ids_bytes = 3072 // 128, kvol * 3072 * 4  # 3000 outputs -> 24 tiles; the masks follow the ids, 256-aligned
+    ids_bytes_aligned = (ids_bytes + 255) // 256 * 256
+    ids_a, ids_b = plain[:ids_bytes].view(torch.int32), mirrored[:ids_bytes].view(torch.int32)
+    assert (ids_a == ids_b).all()
+    assert (ids_a >= 0).sum() == (outs[0][2, :int(outs[1].item())] >= 0).sum()
+    mask_a = plain[ids_bytes_aligned:ids_bytes_aligned + 4 * tiles].view(torch.int32)
+    mask_b = mirrored[ids_bytes_aligned:ids_bytes_aligned + 4 * tiles].view(torch.int32)
+    assert (mask_a == mask_b).all() and (mask_a != 0).any()
