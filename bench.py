@@ -4,7 +4,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W]            this implementation (one process per GPU)
     python bench.py --impl reference [--steps K] [--warmup W]      the CPU restatement of the reference on host cores
 
-One step = one frame of BASELINE config 4 (300 000 points x 5 channels -> mean voxel encoder -> VoxelResBackBone8x
+One step = one frame of benchmark config 4 (300 000 points x 5 channels -> mean voxel encoder -> VoxelResBackBone8x
 16/32/64/128 in fp16 -> BEV densify, plus rotated-BEV NMS over 10 x 1000 boxes at IoU 0.2) on synthetic, seeded
 data.  Prints ONE JSON line (rank 0).  `value` is measured with the inputs resident in HBM (CUDA-graph replay,
 CUDA events); `e2e` drives the same frames from pinned host memory through the public pipeline object, with the
@@ -406,7 +406,7 @@ def count_launches(pipe):
     for L in pipe.net.layers:
         if L.key not in built:
             built.add(L.key)
-            n += (6 if L.kind == "subm" else 9) + 2  # rulebook passes + neighbour-table fill/scatter
+            n += (6 if L.kind == "subm" else 9) + 3  # rulebook passes + neighbour-table fill / scatter / mask pack
         n += 1  # SPConvMM
     n += 3  # BEVDensify: map fill, map scatter, densify
     n += 2  # NMS3d: overlap mask, suppression

@@ -72,6 +72,23 @@ def voxel_backbone_8x(cin):
     return L
 
 
+def seg_unet(cin, n_class=16):
+    """Cylinder3D-shaped encoder-decoder for per-point segmentation (the composition of the reference's
+    tests/cylinder/test_cylinder3d.py:11-99: SubM blocks, strided downsampling, and upsampling by the INVERSE of
+    the same rulebook with a skip connection added before the ReLU).  Output is on the input voxel set."""
+    return [
+        Layer("subm", "s0", cin, 32, save="e0"),
+        Layer("conv", "d1", 32, 64, stride=(2, 2, 2), padding=(1, 1, 1)),
+        Layer("subm", "s1", 64, 64, save="e1"),
+        Layer("conv", "d2", 64, 128, stride=(2, 2, 2), padding=(1, 1, 1)),
+        Layer("subm", "s2", 128, 128),
+        Layer("inverse", "d2", 128, 64, residual="e1"),
+        Layer("subm", "s1", 64, 64),
+        Layer("inverse", "d1", 64, 32, residual="e0"),
+        Layer("subm", "s0", 32, n_class, relu=False),
+    ]
+
+
 def make_weights(layers, seed=0):
     """Seeded Kaiming weights [kVol, Cin, Cout] and small biases (batch-norm folded) for every layer, in order."""
     rng = np.random.Generator(np.random.PCG64(4242 + seed))

@@ -146,3 +146,53 @@ class DetectionPipeline:
         for s in self.net.sets.values():
             add(s["coors"])
         return total
+
+
+class SegmentationPipeline:
+    """Cylinder3D-shaped frame pipeline: CylinderEncoder -> ScatterTo (max) -> encoder-decoder sparse network with
+    inverse convolutions -> GatherBack to per-point logits (the op chain of tests/cylinder/test_cylinder3d.py)."""
+
+    def __init__(self, device="cuda:0", n_pts=120000, caps=None, n_class=16, dtype=torch.float16, kernel=0):
+        from .ops import data_s_gather_back, data_s_scatter_to
+        frame = synth.config5_points()
+        self.device, self.dtype, self.n_pts = torch.device(device), dtype, int(n_pts)
+        self.c_pts = frame["points"].shape[1]
+        self.spatial = frame["spatial_shape"]
+        self.cylinder_config = frame["cylinder_config"]
+        self.layers = backbone.seg_unet(self.c_pts + 5, n_class)
+        self.caps = caps or {"in": self.n_pts, "d1": self.n_pts, "d2": self.n_pts}
+        dev = self.device
+        with torch.cuda.device(dev):
+            cap = self.caps["in"]
+            self.points = torch.zeros((self.n_pts, self.c_pts), dtype=torch.float32, device=dev)
+            self.batch = torch.zeros(self.n_pts, dtype=torch.int32, device=dev)
+            self.cfg = torch.from_numpy(self.cylinder_config).to(dev)
+            self.shape_tensor = torch.empty(self.spatial, dtype=torch.int32, device=dev)
+            self.encoder = deserialize_plugin("CylinderEncoder", data_s_voxel_encoder(cap))
+            self.pts_feats = torch.zeros((self.n_pts, self.c_pts + 5), dtype=torch.float32, device=dev)
+            self.scatter_index = torch.zeros(self.n_pts, dtype=torch.int32, device=dev)
+            self.scatter_count = torch.zeros(cap, dtype=torch.int32, device=dev)
+            self.vox_coors = torch.zeros((cap, 4), dtype=torch.int32, device=dev)
+            self.vox_num = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.scatter = deserialize_plugin("ScatterTo", data_s_scatter_to(0))
+            self.vox_feats = torch.zeros((cap, self.c_pts + 5), dtype=torch.float32, device=dev)
+            spatial_b = [self.spatial[0]] + list(self.spatial[2:])
+            self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel)
+            self.vox_feats_lp = torch.zeros((cap, self.net.in_channels), dtype=dtype, device=dev)
+            self.net.set_input(self.vox_coors, self.vox_num)
+            self.gather = deserialize_plugin("GatherBack", data_s_gather_back(0.0))
+            self.logits = torch.zeros((self.n_pts, n_class), dtype=dtype, device=dev)
+
+    def load_frame(self, frame):
+        self.points.copy_(torch.from_numpy(frame["points"]))
+        self.batch.copy_(torch.from_numpy(frame["batch"]))
+
+    def enqueue(self):
+        self.encoder.enqueue(self.points, self.batch, self.cfg, self.shape_tensor,
+                             outputs=[self.pts_feats, self.scatter_index, self.scatter_count, self.vox_coors,
+                                      self.vox_num])
+        self.scatter.enqueue(self.pts_feats, self.scatter_index, self.scatter_count, outputs=[self.vox_feats])
+        self.vox_feats_lp[:, :self.c_pts + 5].copy_(self.vox_feats)
+        feats, _, _ = self.net.forward(self.vox_feats_lp)
+        self.gather.enqueue(feats, self.scatter_index, outputs=[self.logits])
+        return self.logits

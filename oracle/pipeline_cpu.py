@@ -72,3 +72,17 @@ def run_frame(kind, points, batch, voxel_config, spatial, boxes=None, iou_thresh
     if boxes is not None:
         out["nms_scores"] = oracle.nms3d(boxes["scores"], boxes["boxes"], iou_threshold)
     return out
+
+
+def run_segmentation_frame(points, batch, cylinder_config, spatial, n_class=16, dtype="fp16", seed=0):
+    """The Cylinder3D-shaped frame on the CPU: cylinder encoder -> scatter (max) -> seg_unet -> gather back.
+    Returns dict(logits [N_pts, n_class], num_voxels)."""
+    layers = backbone.seg_unet(points.shape[1] + 5, n_class)
+    weights = backbone.make_weights(layers, seed)
+    n = len(points)
+    aug, scatter_index, scatter_count, coors, nv = oracle.cylinder(points, batch, cylinder_config, spatial, n)
+    vox = oracle.scatter_to(aug, scatter_index, scatter_count[:nv].copy(), 0)
+    spatial_b = [spatial[0]] + list(spatial[2:])
+    x, _, _, _ = run_net(layers, weights, _round_lp(vox[:nv], dtype), coors[:nv], spatial_b, dtype)
+    logits = oracle.gather_back(x, scatter_index, fill_val=0.0)
+    return dict(logits=logits, num_voxels=nv, scatter_index=scatter_index)

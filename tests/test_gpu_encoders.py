@@ -55,7 +55,7 @@ def test_simple_mean(d3d, orc, max_out):
 
 
 def test_simple_mean_config_shapes(d3d, orc):
-    """BASELINE configs 3 and 4 (120 000 x 4 and 300 000 x 5 points)."""
+    """benchmark configs 3 and 4 (120 000 x 4 and 300 000 x 5 points)."""
     from deploy3d_b200 import synth
     for c in (synth.config3_points(), synth.config4_points()):
         pts, cfg = c["points"], c["voxel_config"]
@@ -177,7 +177,7 @@ def test_bev_densify(d3d, orc, dtype, num_act):
 
 
 def test_bev_densify_config3_shape(d3d, orc):
-    """[1, 256, 200, 176] map of BASELINE config 3 (C = 128, Z = 2), ragged X (176 is not a multiple of 32... it is;
+    """[1, 256, 200, 176] map of benchmark config 3 (C = 128, Z = 2), ragged X (176 is not a multiple of 32... it is;
     use 200 x 171 as well to cover a ragged strip)."""
     from tests._util import unique_coors
     r = rng(77)

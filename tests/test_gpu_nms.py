@@ -42,7 +42,7 @@ def test_reference_cases(d3d, orc, batch, topk):
 
 
 def test_config4_boxes(d3d, orc):
-    """BASELINE config 4: 10 classes x 1000 boxes, IoU 0.2, 9-wide boxes (extra columns are ignored)."""
+    """benchmark config 4: 10 classes x 1000 boxes, IoU 0.2, 9-wide boxes (extra columns are ignored)."""
     from deploy3d_b200 import synth
     c = synth.config4_boxes()
     boxes = np.concatenate([c["boxes"], np.ones((10, 1000, 2), np.float32)], -1)

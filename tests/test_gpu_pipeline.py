@@ -56,3 +56,38 @@ def test_frame_matches_cpu_pipeline(d3d, kind, denom, graph):
     bad = err > 2e-2 * (np.abs(ref) + scale)
     assert not bad.any(), "%d cells off, worst %.3e at scale %.3e" % (bad.sum(), err[bad].max(), scale)
     assert (pipe.nms_scores.cpu().numpy() == want["nms_scores"]).all()
+
+
+def test_segmentation_frame_matches_cpu_pipeline(d3d):
+    """Cylinder3D-shaped chain on an azimuth sector of a config-5 frame: CylinderEncoder -> ScatterTo(max) ->
+    encoder-decoder with inverse convolutions and skip connections -> GatherBack.  Per-point logits do not depend on
+    the (implementation-defined) voxel numbering, so they are compared directly."""
+    from deploy3d_b200 import synth
+    from deploy3d_b200.pipeline import SegmentationPipeline
+    from oracle import pipeline_cpu
+    frame = synth.config5_points()
+    pts = _sector(frame, 16)
+    rho = np.sqrt(pts[:, 0] ** 2 + pts[:, 1] ** 2)
+    phi = np.arctan2(pts[:, 1], pts[:, 0])
+    cyl = np.stack([rho, phi, pts[:, 2]], 1)
+    cfg = frame["cylinder_config"]
+    shape = frame["spatial_shape"]
+    mins = np.array([cfg[2], cfg[1], cfg[0]], np.float32)  # (rho, phi, z) lower bounds
+    steps = (np.array([cfg[5], cfg[4], cfg[3]], np.float32) - mins) / np.array(shape[2:], np.float32)
+    pts = pts[synth.drop_edge_points(cyl, mins, steps)]
+    n = len(pts)
+    batch = np.zeros(n, np.int32)
+    pipe = SegmentationPipeline("cuda:0", n_pts=n, caps={"in": n, "d1": 4 * n, "d2": 4 * n})
+    pipe.load_frame(dict(points=pts, batch=batch))
+    got = pipe.enqueue().float().cpu().numpy()
+    torch.cuda.synchronize()
+    want = pipeline_cpu.run_segmentation_frame(pts, batch, cfg, shape)
+    assert int(pipe.vox_num.item()) == want["num_voxels"]
+    ref = want["logits"]
+    assert got.shape == ref.shape
+    scale = np.sqrt((ref ** 2).mean()) + 1e-12
+    err = np.abs(got - ref)
+    rel_l2 = np.sqrt((err ** 2).sum() / ((ref ** 2).sum() + 1e-30))
+    assert rel_l2 < 1e-2, "relative L2 error %.3e" % rel_l2
+    bad = err > 2e-2 * (np.abs(ref) + scale)
+    assert not bad.any(), "%d logits off, worst %.3e at scale %.3e" % (bad.sum(), err[bad].max(), scale)

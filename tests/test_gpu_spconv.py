@@ -2,7 +2,7 @@
 
 Mirrors the reference's tests/spconv/test_spconv.py (same 16-case grid: strided (2,2,1) / SubM x padded input
 buffer x truncating maxNumActOut x inverse) and adds transposed, asymmetric, dilated, 2-D and empty cases plus
-BASELINE configs 1 and 2.  Rulebooks are compared bit-exactly (SubM raw, strided after canonicalisation);
+benchmark configs 1 and 2.  Rulebooks are compared bit-exactly (SubM raw, strided after canonicalisation);
 features within 1e-4 (fp32) / 1e-2 (fp16, bf16) of the fp32-accumulating oracle."""
 import numpy as np
 import pytest
@@ -179,7 +179,7 @@ def test_index_is_deterministic(d3d):
 
 
 def test_config1_subm_fp32(d3d, orc):
-    """BASELINE config 1: SubM 3x3x3, 16->16, fp32, 20 000 uniform voxels in 41x1600x1408."""
+    """benchmark config 1: SubM 3x3x3, 16->16, fp32, 20 000 uniform voxels in 41x1600x1408."""
     from deploy3d_b200 import synth
     c = synth.config1()
     outs, num_in = run_index(d3d, c["coors"], 20000, c["spatial_shape"], c["ksize"], c["stride"], c["padding"],
@@ -194,7 +194,7 @@ def test_config1_subm_fp32(d3d, orc):
 
 @pytest.mark.parametrize("dtype", ["fp16", "bf16"])
 def test_config2_strided_and_inverse(d3d, orc, dtype):
-    """BASELINE config 2: conv k3 s2 p1 32->64 then its inverse 64->32 over the same rulebook, batch 2 x 60 000."""
+    """benchmark config 2: conv k3 s2 p1 32->64 then its inverse 64->32 over the same rulebook, batch 2 x 60 000."""
     from deploy3d_b200 import synth
     c = synth.config2()
     n = c["coors"].shape[0]

@@ -101,7 +101,7 @@ def test_strided_inverse_padded_and_epilogue(d3d, orc):
 
 
 def test_config2_through_tensor_cores(d3d, orc):
-    """BASELINE config 2 at full size: 2 x 60 000 LiDAR-like voxels, 32 -> 64 strided then 64 -> 32 inverse."""
+    """benchmark config 2 at full size: 2 x 60 000 LiDAR-like voxels, 32 -> 64 strided then 64 -> 32 inverse."""
     from deploy3d_b200 import synth
     c = synth.config2()
     n = c["coors"].shape[0]

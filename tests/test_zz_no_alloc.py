@@ -45,7 +45,7 @@ def _call_both(lib, _lib, scores, boxes, thr):
 def test_static_scratch_matches_workspace_variant_twice(d3d):
     from deploy3d_b200 import _lib, synth
     lib = _lib.lib()
-    big = synth.config4_boxes(10, 1000)         # 160 000 mask words: the largest BASELINE case
+    big = synth.config4_boxes(10, 1000)         # 160 000 mask words: the largest benchmark case
     small = synth.config4_boxes(3, 200)         # a smaller second call must not see the first one's leftovers
     small["boxes"][..., :2] *= 0.1               # crowded: most boxes are suppressed
     for case, thr in ((big, 0.2), (small, 0.1), (big, 0.1)):
