@@ -181,7 +181,9 @@ class SegmentationPipeline:
             self.vox_feats_lp = torch.zeros((cap, self.net.in_channels), dtype=dtype, device=dev)
             self.net.set_input(self.vox_coors, self.vox_num)
             self.gather = deserialize_plugin("GatherBack", data_s_gather_back(0.0))
-            self.logits = torch.zeros((self.n_pts, n_class), dtype=dtype, device=dev)
+            # GatherBack is an fp32 operator (as in the reference): the network output is widened first
+            self.net_out_f32 = torch.zeros((cap, n_class), dtype=torch.float32, device=dev)
+            self.logits = torch.zeros((self.n_pts, n_class), dtype=torch.float32, device=dev)
 
     def load_frame(self, frame):
         self.points.copy_(torch.from_numpy(frame["points"]))
@@ -194,5 +196,6 @@ class SegmentationPipeline:
         self.scatter.enqueue(self.pts_feats, self.scatter_index, self.scatter_count, outputs=[self.vox_feats])
         self.vox_feats_lp[:, :self.c_pts + 5].copy_(self.vox_feats)
         feats, _, _ = self.net.forward(self.vox_feats_lp)
-        self.gather.enqueue(feats, self.scatter_index, outputs=[self.logits])
+        self.net_out_f32.copy_(feats)
+        self.gather.enqueue(self.net_out_f32, self.scatter_index, outputs=[self.logits])
         return self.logits
