@@ -346,7 +346,7 @@ extern "C" int d3d_spconv_mm_destroy(d3d_spconv_mm_t h) {
 }
 
 extern "C" int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t h, int which) {
-  D3D_REQUIRE(h && which >= 0 && which <= 2, D3D_ERR_INVALID_ARGUMENT);
+  D3D_REQUIRE(h && which >= 0 && which <= 3, D3D_ERR_INVALID_ARGUMENT);
   h->kernel_choice = which;
   return D3D_OK;
 }
@@ -406,7 +406,7 @@ extern "C" int d3d_spconv_mm_run(d3d_spconv_mm_t h, int dtype, const void* in_fe
   a.residual = epilogue ? epilogue->residual : nullptr;
   a.stream = stream;
   bool tc_ok = spconv_mm_tc_eligible(h, dtype);
-  if (h->kernel_choice == 2) {
+  if (h->kernel_choice == 2 || h->kernel_choice == 3) {
     D3D_REQUIRE(tc_ok, D3D_ERR_INVALID_ARGUMENT);
     return launch_spconv_mm_tc(a);
   }

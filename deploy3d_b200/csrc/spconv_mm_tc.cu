@@ -17,11 +17,14 @@
 // What bounds the kernel is shared-memory bandwidth (every A block is written once and read once by the tensor
 // core, 128 B/clk per SM) and, for a single issuing thread, the scalar instructions between two tcgen05.mma; the
 // roles below therefore keep their inner loops to a handful of instructions per copy / per MMA:
-//   8 producer warps   thread t owns piece t % P of rows t / P + i * (256 / P) of every block (P = 16-byte pieces
-//                      per row), so its shared-memory offsets are constants; ids come from the tile's id buffer
+//   8 (4) producer warps  thread t owns piece t % P of rows t / P + i * (threads / P) of every block (P = 16-byte
+//                      pieces per row), so its shared-memory offsets are constants; ids come from the tile's id buffer
 //   1 MMA warp         one lane issues tcgen05.mma from precomputed descriptor words; owns the TMEM allocation
 //   1 control warp     prefetches the neighbour ids of the next tile (one bulk copy) and loads B by TMA
 //   4 epilogue warps   TMEM -> registers -> global
+// Layers of at most 64 input channels run TWO such CTAs per SM (4 producer warps and half the shared memory each):
+// their bound is the serial fill -> issue -> commit chain of a tile, not a hardware unit, and two independent
+// chains per SM overlap each other's hand-over time (measured: 18-24 % faster at 16 / 32 / 64 channels).
 // Every role derives the stage sequence of a tile from the tile's offset mask (built with the neighbour table), so
 // no per-stage metadata is exchanged.  Stages and accumulators are handed over through mbarriers; every wait is
 // bounded (about one second) and on expiry raises an error word, lets the CTA drain and return instead of spinning.
@@ -37,9 +40,11 @@ constexpr int kTileRows = 128;
 constexpr int kMaxStages = 8;
 constexpr int kNumAcc = 2;
 constexpr int kMaxGroup = 8;  // kernel offsets that may share one pipeline stage
-constexpr int kProducerThreads = 256;
-constexpr int kMmaWarp = 8, kControlWarp = 9, kFirstEpilogueWarp = 10;
-constexpr int kThreads = 14 * 32;
+// Warp roles, for kProd producer threads (256: one CTA per SM; 128: two CTAs per SM, each with half the shared
+// memory, which gives small layers two independent producer -> MMA -> epilogue chains per SM): producers first, then
+// the MMA warp, the control warp and four epilogue warps (whose index mod 4 covers the four TMEM lane quarters).
+__host__ __device__ constexpr int mma_warp_of(int prod) { return prod / 32; }
+__host__ __device__ constexpr int threads_of(int prod) { return prod + 6 * 32; }
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
 __device__ int g_tc_error;  // 0 ok; otherwise the code of the first wait that gave up
@@ -290,21 +295,22 @@ __device__ __forceinline__ void store_chunk(const uint32_t* acc, int n, const fl
 }
 
 // Barrier initialisation, bias staging and the TMEM allocation (by the MMA warp); returns the TMEM base address.
+template <int kProd>
 __device__ __forceinline__ uint32_t cta_setup(const TcParams& p, const Smem& s) {
   Shared* sh = s.sh;
   if (threadIdx.x == 0) {
     // a stage is full once every producer thread's copies have landed and, when B travels with the stage, its
     // TMA bytes too (the control warp's expect_tx arrival)
-    const int full_count = kProducerThreads + (p.b_resident ? 0 : 1);
+    const int full_count = kProd + (p.b_resident ? 0 : 1);
     for (int i = 0; i < p.stages; ++i) mbar_init(&sh->full[i], full_count), mbar_init(&sh->empty[i], 1);
     for (int a = 0; a < kNumAcc; ++a) mbar_init(&sh->acc_full[a], 1), mbar_init(&sh->acc_empty[a], 4);
-    for (int b = 0; b < 2; ++b) mbar_init(&sh->idx_full[b], 1), mbar_init(&sh->idx_free[b], kProducerThreads / 32);
+    for (int b = 0; b < 2; ++b) mbar_init(&sh->idx_full[b], 1), mbar_init(&sh->idx_free[b], kProd / 32);
     mbar_init(&sh->b_ready, 1);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   for (int c = threadIdx.x; c < p.cout; c += blockDim.x) s.bias[c] = p.bias[c];
-  if ((int)(threadIdx.x >> 5) == kMmaWarp) tmem_alloc(&sh->tmem_base, p.tmem_cols);
+  if ((int)(threadIdx.x >> 5) == mma_warp_of(kProd)) tmem_alloc(&sh->tmem_base, p.tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -312,29 +318,32 @@ __device__ __forceinline__ uint32_t cta_setup(const TcParams& p, const Smem& s) 
 }
 
 // All roles meet, then the allocating warp returns the tensor memory.
+template <int kProd>
 __device__ __forceinline__ void cta_teardown(const TcParams& p, uint32_t tmem_base) {
   tc_fence_before();
   __syncthreads();
-  if ((int)(threadIdx.x >> 5) == kMmaWarp) {
+  if ((int)(threadIdx.x >> 5) == mma_warp_of(kProd)) {
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
 }
 
 // ---- producers ---------------------------------------------------------------------------------------------------
-// kPieces = 16-byte pieces per block row (kchunk / 8).  The 256 producer threads cover a [128 x kPieces] block in
-// kPieces / 2 passes; thread t copies piece t % kPieces of row t / kPieces + pass * (256 / kPieces).  Consecutive
+// kPieces = 16-byte pieces per block row (kchunk / 8).  The kProd producer threads cover a [128 x kPieces] block in
+// 128 * kPieces / kProd passes; thread t copies piece t % kPieces of row t / kPieces + pass * (kProd / kPieces).  Consecutive
 // lanes take consecutive pieces of a row (whole rows per warp instruction on the global side, whole 128-byte lines
 // on the shared side), and because a pass advances by a multiple of 8 rows the XOR swizzle term of the destination
 // is the same in every pass: one per-thread offset, the rest are immediates.
 // The body of a stage is branch-free and fully unrolled over the kGroup block slots (absent offsets are predicated
 // off): a taken branch costs a lone warp tens of cycles, more than the copies it would skip.
-template <int kPieces, int kGroup>
+template <int kPieces, int kGroup, int kProd>
 __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, int t) {
-  constexpr int kPasses = kPieces / 2;
+  constexpr int kPasses = kTileRows * kPieces / kProd;
   constexpr uint32_t kBlockBytes = kTileRows * kPieces * 16;  // = p.a_bytes
   constexpr uint32_t gmask = (1u << kGroup) - 1u;
-  constexpr int kRowsPerPass = kProducerThreads / kPieces;
+  constexpr int kRowsPerPass = kProd / kPieces;
+  static_assert(kRowsPerPass % 8 == 0, "a pass must advance by whole swizzle periods");
+  constexpr int kBits = kGroup * kPasses <= 8 ? 8 : 16;  // zero-row flags per stage
   constexpr int kRowBytes = kPieces >= 8 ? 128 : kPieces * 16;
   constexpr int kSwzShift = kRowBytes == 128 ? 0 : kRowBytes == 64 ? 1 : 2;
   constexpr int kSwzMask = kRowBytes == 128 ? 7 : kRowBytes == 64 ? 3 : 1;
@@ -349,8 +358,8 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   const uint32_t n_in_rows = (uint32_t)p.n_in_rows;
   const uint32_t tiles_addr = smem_u32(s.tiles);
   const int ids_per_tile = p.kvol * kTileRows;
-  static_assert(kGroup * kPasses <= 8 && kMaxStages <= 8, "zero_rows keeps 8 bits per stage");
-  uint64_t zero_rows = 0;  // bit 8 * stage + e * kPasses + i: this thread's last copy to that position was a zero fill
+  static_assert(kGroup * kPasses <= 16 && kMaxStages <= 8, "zero_rows keeps 8 or 16 bits per stage (then <= 4 stages)");
+  uint64_t zero_rows = 0;  // bit kBits * stage + e * kPasses + i: this thread's last copy to that position was a zero fill
   int stage = 0;
   uint32_t phase = 0, idx_phase = 0;  // idx_phase bit b: parity to wait for on idx_full[b]
   int buf = 0;
@@ -381,7 +390,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
         // Most rows of a block have no neighbour (LiDAR: about 5 of 27 offsets per voxel).  A position this thread
         // zero-filled the last time it wrote the stage is still zero (nobody else writes it), so a zero row over a
         // zero row is skipped: it would only spend shared-memory bandwidth the tensor core needs.
-        const uint32_t was_zero = (uint32_t)(zero_rows >> (stage * 8)) & 0xFFu;
+        const uint32_t was_zero = (uint32_t)(zero_rows >> (stage * kBits)) & ((1u << kBits) - 1u);
         uint32_t now_zero = was_zero;
 #pragma unroll
         for (int e = 0; e < kGroup; ++e)
@@ -397,7 +406,8 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
                            src, valid ? 16u : 0u);
             if (run) now_zero = valid ? (now_zero & ~bit) : (now_zero | bit);
           }
-        zero_rows = (zero_rows & ~(0xFFull << (stage * 8))) | ((uint64_t)now_zero << (stage * 8));
+        zero_rows = (zero_rows & ~((unsigned long long)((1u << kBits) - 1u) << (stage * kBits))) |
+                    ((uint64_t)now_zero << (stage * kBits));
         cp_async_arrive(&sh->full[stage]);  // one arrival per producer thread once its copies have landed
         if (++stage == p.stages) stage = 0, phase ^= 1;
       }
@@ -597,26 +607,26 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
   }
 }
 
-// kSteps = kchunk / 16 (1, 2, 4, 8), kGroup = offsets per stage (1, 2, 4, 8).
-template <int kSteps, int kGroup>
-__global__ void __launch_bounds__(kThreads, 1)
+// kSteps = kchunk / 16 (1, 2, 4, 8), kGroup = offsets per stage (1, 2, 4, 8), kProd = producer threads (256 or 128).
+template <int kSteps, int kGroup, int kProd>
+__global__ void __launch_bounds__(threads_of(kProd), kProd == 256 ? 1 : 2)
 spconv_mm_tc_kernel(const __grid_constant__ CUtensorMap map_b, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
   const Smem s = carve_smem(smem_raw, p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t tmem_base = cta_setup(p, s);
-  if (warp < kProducerThreads / 32) {
-    producer_role<2 * kSteps, kGroup>(p, s, threadIdx.x);
-  } else if (warp == kMmaWarp) {
+  const uint32_t tmem_base = cta_setup<kProd>(p, s);
+  if (warp < kProd / 32) {
+    producer_role<2 * kSteps, kGroup, kProd>(p, s, threadIdx.x);
+  } else if (warp == mma_warp_of(kProd)) {
     mma_role<kSteps, kGroup>(p, s, tmem_base);
     __syncwarp();
-  } else if (warp == kControlWarp) {
+  } else if (warp == mma_warp_of(kProd) + 1) {
     if (lane == 0) control_role(p, s, &map_b);
     __syncwarp();
   } else {
     epilogue_role(p, s, tmem_base, warp & 3);
   }
-  cta_teardown(p, tmem_base);
+  cta_teardown<kProd>(p, tmem_base);
 }
 
 // ---- host --------------------------------------------------------------------------------------------------------
@@ -702,14 +712,15 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.num_tiles = (int)((m_max + kTileRows - 1) / kTileRows);
   p.row_bytes = (int)box_cols * 2;
   p.idx_bytes = (uint32_t)kvol * kTileRows * 4;
-  // shared-memory budget: 227 KB per CTA minus alignment slack, the two neighbour-id buffers, bias and control block
+  // control data of a CTA: alignment slack, the two neighbour-id buffers, bias, barriers
   const size_t ctrl = 1024 + 2 * (size_t)p.idx_bytes + align_up((size_t)cout * 4 + 8, 16) + sizeof(Shared);
-  const size_t budget = 227 * 1024 - ctrl;
+  const size_t budget_one = 227 * 1024 - ctrl;  // one CTA per SM
   // a block holds `kchunk` <= 128 input channels of one kernel offset; split further until two stages fit
   int kchunk = cin > 128 ? 128 : cin;
   while (kchunk > 64 &&
-         2 * (align_up((size_t)kTileRows * kchunk * 2, 1024) + align_up((size_t)cout * kchunk * 2, 1024)) > budget)
+         2 * (align_up((size_t)kTileRows * kchunk * 2, 1024) + align_up((size_t)cout * kchunk * 2, 1024)) > budget_one)
     kchunk /= 2;
+  const int ksteps = kchunk / 16;
   p.kchunk = kchunk;
   p.kparts = cin / kchunk;
   p.chunks = kchunk <= 64 ? 1 : kchunk / 64;
@@ -726,45 +737,77 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.residual = a.residual;
   p.relu = a.relu;
   p.is_bf16 = a.dtype == D3D_BF16;
-  // small layers keep all weight blocks in shared memory for the whole kernel instead of reloading one per stage
   const size_t bres_bytes = (size_t)kvol * p.b_bytes;
-  p.b_resident = (p.kparts == 1 && bres_bytes <= 64 * 1024) ? 1 : 0;
-  const size_t ring_budget = budget - (p.b_resident ? bres_bytes : 0);
-  // several offsets share a stage when their blocks are small, so that the per-stage hand-over cost is amortised
-  const size_t blk_bytes = (size_t)p.a_bytes + (p.b_resident ? 0 : p.b_bytes);
-  int group = 1;
-  if (p.kparts == 1)
-    while (group < kMaxGroup && (size_t)(2 * group) * blk_bytes <= 48 * 1024 && 2 * group * (kchunk / 16) <= 8)
-      group *= 2;
-  p.group = group;
-  const size_t stage_bytes = (size_t)group * blk_bytes;
-  int stages = (int)(ring_budget / stage_bytes);
-  stages = stages > kMaxStages ? kMaxStages : stages;
-  D3D_REQUIRE(stages >= 2, D3D_ERR_TOO_LARGE);
-  p.stages = stages;
-  size_t smem = ctrl + (size_t)stages * stage_bytes + (p.b_resident ? bres_bytes : 0);
-  if (smem < 120 * 1024) smem = 120 * 1024;  // one CTA per SM: it owns the SM's tensor memory
-  // one kernel instance per (MMAs per block, offsets per stage)
+  // Shared-memory plan for one CTA per SM (256 producer threads) or two (128 each, half the memory).  Small layers
+  // keep all weight blocks resident instead of reloading one per stage; several offsets share a stage when their
+  // blocks are small, so that the per-stage hand-over cost is amortised (a stage holds at most 8 K-step blocks).
+  struct Plan {
+    int resident, group, stages;
+    size_t smem;
+  };
+  auto make_plan = [&](bool two_per_sm, Plan* out) -> bool {
+    if (two_per_sm && (p.kparts != 1 || kchunk > 64 || ctrl + 2048 > 113 * 1024)) return false;
+    const size_t budget = (two_per_sm ? 113 * 1024 : 227 * 1024) - ctrl;
+    const size_t resident_limit = two_per_sm ? 32 * 1024 : 64 * 1024;
+    Plan pl;
+    pl.resident = (p.kparts == 1 && bres_bytes <= resident_limit) ? 1 : 0;
+    if (pl.resident && bres_bytes + 2 * (size_t)p.a_bytes > budget) pl.resident = 0;
+    const size_t ring = budget - (pl.resident ? bres_bytes : 0);
+    const size_t blk = (size_t)p.a_bytes + (pl.resident ? 0 : p.b_bytes);
+    const size_t stage_target = two_per_sm ? ring / 2 : 48 * 1024;
+    pl.group = 1;
+    if (p.kparts == 1)
+      while (pl.group < kMaxGroup && (size_t)(2 * pl.group) * blk <= stage_target && 2 * pl.group * ksteps <= 8)
+        pl.group *= 2;
+    const size_t stage_bytes = (size_t)pl.group * blk;
+    pl.stages = (int)(ring / stage_bytes);
+    // the producers keep per-stage zero-row flags in one 64-bit word: 8 bits per stage, 16 when a thread owns more
+    const int flag_bits = pl.group * ksteps * (two_per_sm ? 2 : 1) <= 8 ? 8 : 16;
+    const int max_stages = 64 / flag_bits < kMaxStages ? 64 / flag_bits : kMaxStages;
+    pl.stages = pl.stages > max_stages ? max_stages : pl.stages;
+    if (pl.stages < 2) return false;
+    pl.smem = ctrl + (size_t)pl.stages * stage_bytes + (pl.resident ? bres_bytes : 0);
+    // pin the number of CTAs per SM through the request: more than half (a third) of the SM's shared memory
+    const size_t floor_bytes = two_per_sm ? 80 * 1024 : 120 * 1024;
+    if (pl.smem < floor_bytes) pl.smem = floor_bytes;
+    *out = pl;
+    return true;
+  };
+  Plan pl;
+  bool two_per_sm = h->kernel_choice != 3 && make_plan(true, &pl);
+  if (!two_per_sm) D3D_REQUIRE(make_plan(false, &pl), D3D_ERR_TOO_LARGE);
+  p.b_resident = pl.resident, p.group = pl.group, p.stages = pl.stages;
+  const size_t smem = pl.smem;
+  // one kernel instance per (MMAs per block, offsets per stage, producer threads)
   typedef void (*KernelFn)(const CUtensorMap, const TcParams);
-  // (a stage holds at most 8 K-step blocks: K steps x offsets <= 8)
-  static const KernelFn kernels[4][4] = {
-      {spconv_mm_tc_kernel<1, 1>, spconv_mm_tc_kernel<1, 2>, spconv_mm_tc_kernel<1, 4>, spconv_mm_tc_kernel<1, 8>},
-      {spconv_mm_tc_kernel<2, 1>, spconv_mm_tc_kernel<2, 2>, spconv_mm_tc_kernel<2, 4>, nullptr},
-      {spconv_mm_tc_kernel<4, 1>, spconv_mm_tc_kernel<4, 2>, nullptr, nullptr},
-      {spconv_mm_tc_kernel<8, 1>, nullptr, nullptr, nullptr}};
+  static const KernelFn kernels[2][4][4] = {
+      {{spconv_mm_tc_kernel<1, 1, 256>, spconv_mm_tc_kernel<1, 2, 256>, spconv_mm_tc_kernel<1, 4, 256>,
+        spconv_mm_tc_kernel<1, 8, 256>},
+       {spconv_mm_tc_kernel<2, 1, 256>, spconv_mm_tc_kernel<2, 2, 256>, spconv_mm_tc_kernel<2, 4, 256>, nullptr},
+       {spconv_mm_tc_kernel<4, 1, 256>, spconv_mm_tc_kernel<4, 2, 256>, nullptr, nullptr},
+       {spconv_mm_tc_kernel<8, 1, 256>, nullptr, nullptr, nullptr}},
+      {{spconv_mm_tc_kernel<1, 1, 128>, spconv_mm_tc_kernel<1, 2, 128>, spconv_mm_tc_kernel<1, 4, 128>,
+        spconv_mm_tc_kernel<1, 8, 128>},
+       {spconv_mm_tc_kernel<2, 1, 128>, spconv_mm_tc_kernel<2, 2, 128>, spconv_mm_tc_kernel<2, 4, 128>, nullptr},
+       {spconv_mm_tc_kernel<4, 1, 128>, spconv_mm_tc_kernel<4, 2, 128>, nullptr, nullptr},
+       {nullptr, nullptr, nullptr, nullptr}}};
   const int si = kchunk == 16 ? 0 : kchunk == 32 ? 1 : kchunk == 64 ? 2 : 3;
-  const int gi = group == 1 ? 0 : group == 2 ? 1 : group == 4 ? 2 : 3;
-  D3D_REQUIRE(kernels[si][gi] != nullptr, D3D_ERR_TOO_LARGE);
-  static bool attr_set[64][4][4] = {};
+  const int gi = pl.group == 1 ? 0 : pl.group == 2 ? 1 : pl.group == 4 ? 2 : 3;
+  const int di = two_per_sm ? 1 : 0;
+  D3D_REQUIRE(kernels[di][si][gi] != nullptr, D3D_ERR_TOO_LARGE);
+  static bool attr_set[64][2][4][4] = {};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return D3D_ERR_CUDA;
-  if (!attr_set[dev][si][gi]) {
-    if (cudaFuncSetAttribute(kernels[si][gi], cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+  if (!attr_set[dev][di][si][gi]) {
+    if (cudaFuncSetAttribute(kernels[di][si][gi], cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
+        cudaSuccess)
       return D3D_ERR_CUDA;
-    attr_set[dev][si][gi] = true;
+    attr_set[dev][di][si][gi] = true;
   }
-  const int grid = p.num_tiles < kNumSMs ? p.num_tiles : kNumSMs;
-  kernels[si][gi]<<<grid, kThreads, smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(st->map_b, p);
+  const int ctas = kNumSMs * (two_per_sm ? 2 : 1);
+  const int grid = p.num_tiles < ctas ? p.num_tiles : ctas;
+  kernels[di][si][gi]<<<grid, threads_of(two_per_sm ? 128 : 256), smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(
+      st->map_b, p);
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }

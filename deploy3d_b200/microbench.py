@@ -25,7 +25,7 @@ def main():
     ap.add_argument("--voxels", type=int, default=66000)
     ap.add_argument("--grid", type=int, nargs=3, default=[11, 360, 360], help="Z Y X of the voxel grid")
     ap.add_argument("--stride", type=int, default=1)
-    ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 SIMT, 2 tcgen05")
+    ap.add_argument("--kernel", type=int, default=0, help="0 auto, 1 SIMT, 2 tcgen05, 3 tcgen05 with one CTA per SM")
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)

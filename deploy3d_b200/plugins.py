@@ -157,7 +157,7 @@ class SPConvMMPlugin(_Plugin):
         check("d3d_spconv_mm_configure", lib().d3d_spconv_mm_configure(self.handle, _TORCH2D3D[torch_dtype]))
 
     def set_kernel(self, which):
-        """0 automatic, 1 SIMT, 2 tcgen05."""
+        """0 automatic, 1 SIMT, 2 tcgen05, 3 tcgen05 with one CTA per SM."""
         check("d3d_spconv_mm_set_kernel", lib().d3d_spconv_mm_set_kernel(self.handle, int(which)))
 
     # two-step form: one neighbour table shared by all layers over the same rulebook

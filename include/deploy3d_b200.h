@@ -170,8 +170,9 @@ int d3d_spconv_mm_run(d3d_spconv_mm_t handle, int dtype, const void* in_feats, i
                       const int32_t* num_act_out, const void* table, void* out_feats,
                       const d3d_spconv_mm_epilogue* epilogue, void* stream);
 /* Kernel choice for tests and profiling: 0 = automatic, 1 = SIMT fp32-FMA path, 2 = tcgen05 tensor-core path (what
- * "automatic" picks for eligible shapes; fails with D3D_ERR_INVALID_ARGUMENT at run time when the shape is not
- * eligible). */
+ * "automatic" picks for eligible shapes), 3 = tcgen05 path restricted to one CTA per SM (layers of at most 64 input
+ * channels otherwise run two half-size CTAs per SM).  2 and 3 fail with D3D_ERR_INVALID_ARGUMENT at run time when
+ * the shape is not eligible. */
 int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t handle, int which);
 
 /* ---------------------------------------------------------------------------------------------

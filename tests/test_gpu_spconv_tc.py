@@ -46,7 +46,7 @@ def _run(d3d, orc, outs, num_in, num_out, n_in, n_out_max, cin, cout, ks, invers
     tdt = torch.float16 if dtype == "fp16" else torch.bfloat16
     table = SPConvMMPlugin.prepare(kvol, inverse, n_out_max, outs[0], outs[1])
     got = {}
-    for which in (2, 1):  # tcgen05, SIMT
+    for which in (2, 3, 1):  # tcgen05 (two CTAs per SM where it applies), tcgen05 with one CTA per SM, SIMT
         plug = deserialize_plugin("SPConvMM", d3d.data_s_spconv_mm(ks, cin, cout, n_out_max, False, inverse, w, b))
         plug.configure(tdt)
         plug.set_kernel(which)
@@ -60,6 +60,7 @@ def _run(d3d, orc, outs, num_in, num_out, n_in, n_out_max, cin, cout, ks, invers
     if relu:
         want = np.maximum(want, 0)
     assert_feats_close(got[2], want, 1e-2, "tcgen05 vs oracle")
+    assert (got[2] == got[3]).all(), "one or two CTAs per SM accumulate in the same order: identical results"
     assert_feats_close(got[2], got[1], 1e-2, "tcgen05 vs SIMT")
     return got[2]
 
