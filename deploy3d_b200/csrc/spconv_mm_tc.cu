@@ -720,12 +720,17 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   while (kchunk > 64 &&
          2 * (align_up((size_t)kTileRows * kchunk * 2, 1024) + align_up((size_t)cout * kchunk * 2, 1024)) > budget_one)
     kchunk /= 2;
-  const int ksteps = kchunk / 16;
-  p.kchunk = kchunk;
-  p.kparts = cin / kchunk;
-  p.chunks = kchunk <= 64 ? 1 : kchunk / 64;
-  p.a_bytes = (uint32_t)align_up((size_t)kTileRows * kchunk * 2, 1024);
-  p.b_bytes = (uint32_t)align_up((size_t)cout * kchunk * 2, 1024);
+  int ksteps = 0;
+  auto set_chunk = [&](int kc) {
+    kchunk = kc, ksteps = kc / 16;
+    p.kchunk = kc;
+    p.kparts = cin / kc;
+    p.chunks = kc <= 64 ? 1 : kc / 64;
+    p.a_bytes = (uint32_t)align_up((size_t)kTileRows * kc * 2, 1024);
+    p.b_bytes = (uint32_t)align_up((size_t)cout * kc * 2, 1024);
+  };
+  const int kchunk_one = kchunk;  // block width with one CTA per SM; two per SM use at most 64 channels per block
+  set_chunk(kchunk_one);
   p.layout_type = p.row_bytes == 32 ? 6u : p.row_bytes == 64 ? 4u : 2u;
   const uint32_t fmt = a.dtype == D3D_BF16 ? 1u : 0u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(cout >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
@@ -737,7 +742,6 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.residual = a.residual;
   p.relu = a.relu;
   p.is_bf16 = a.dtype == D3D_BF16;
-  const size_t bres_bytes = (size_t)kvol * p.b_bytes;
   // Shared-memory plan for one CTA per SM (256 producer threads) or two (128 each, half the memory).  Small layers
   // keep all weight blocks resident instead of reloading one per stage; several offsets share a stage when their
   // blocks are small, so that the per-stage hand-over cost is amortised (a stage holds at most 8 K-step blocks).
@@ -746,7 +750,8 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
     size_t smem;
   };
   auto make_plan = [&](bool two_per_sm, Plan* out) -> bool {
-    if (two_per_sm && (p.kparts != 1 || kchunk > 64 || ctrl + 2048 > 113 * 1024)) return false;
+    if (two_per_sm && (kchunk > 64 || ctrl + 2048 > 113 * 1024)) return false;
+    const size_t bres_bytes = (size_t)kvol * p.b_bytes;
     const size_t budget = (two_per_sm ? 113 * 1024 : 227 * 1024) - ctrl;
     const size_t resident_limit = two_per_sm ? 32 * 1024 : 64 * 1024;
     Plan pl;
@@ -774,8 +779,17 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
     return true;
   };
   Plan pl;
-  bool two_per_sm = h->kernel_choice != 3 && make_plan(true, &pl);
-  if (!two_per_sm) D3D_REQUIRE(make_plan(false, &pl), D3D_ERR_TOO_LARGE);
+  bool two_per_sm = false;
+  // 128 input channels: two CTAs per SM (K split in two) measure about even with one; they win for few tiles per
+  // SM, where twice as many CTAs quantise the tile count better
+  if (h->kernel_choice != 3 && (cin < 128 || (cin == 128 && p.num_tiles <= 8 * kNumSMs))) {
+    set_chunk(kchunk_one < 64 ? kchunk_one : 64);
+    two_per_sm = make_plan(true, &pl);
+  }
+  if (!two_per_sm) {
+    set_chunk(kchunk_one);
+    D3D_REQUIRE(make_plan(false, &pl), D3D_ERR_TOO_LARGE);
+  }
   p.b_resident = pl.resident, p.group = pl.group, p.stages = pl.stages;
   const size_t smem = pl.smem;
   // one kernel instance per (MMAs per block, offsets per stage, producer threads)
