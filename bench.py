@@ -162,8 +162,9 @@ def run_reference(args):
 # GPU arm
 # ------------------------------------------------------------------------------------------------------------------
 # dram__bytes_read.sum + dram__bytes_write.sum over the 21 SPConvMM launches of one config-4 frame, from the ncu capture
-# summarised in profiles/spconv_mm_tc_bench_layers_dram.md (cold L2 per launch: an upper bound for the stream)
-CONV_DRAM_BYTES_PER_FRAME = 5.12e9
+# summarised in profiles/spconv_mm_tc_bench_layers_dram.md (L2 flushed before every launch; outputs still in L2 at the
+# end of a launch are written back later and not counted)
+CONV_DRAM_BYTES_PER_FRAME = 1.43e9
 INNER_LAUNCHES = 4  # timed launches per layer and frame in the per-layer pass
 
 
