@@ -20,6 +20,9 @@ namespace {
 constexpr int kIdxThreads = 256;  // inputs per CTA in every pass; the granularity of the per-CTA counts
 constexpr int kSegment = 128;     // every kernel-offset segment starts at a multiple of 128 (trt/spconv/index.cu:21)
 constexpr int kMaxKernelVol = 512;
+// SubM tables are sized for a load factor of at most 0.25: four of five neighbour probes miss, and a miss walks on
+// until it meets an empty slot, so the sectors a miss touches (what bounds the probe kernel) fall with the load
+constexpr int kSubmFan = 2;
 
 struct Geometry {
   int ndim;
@@ -109,7 +112,7 @@ __global__ void reset_table_kernel(unsigned long long* table, const int32_t* num
 __global__ void subm_insert_kernel(unsigned long long* table, const int32_t* __restrict__ coors,
                                    const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max) {
   int n = live_count(num_act_in, n_max);
-  uint32_t mask = hash_capacity(n, cap_max) - 1;
+  uint32_t mask = hash_capacity((long long)n * kSubmFan, cap_max) - 1;
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int c[D3D_MAX_NDIM + 1];
@@ -131,7 +134,7 @@ __global__ void subm_probe_kernel(const unsigned long long* __restrict__ table, 
   __shared__ int cnt[kBatch];
   int n = live_count(num_act_in, n_max);
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
-  uint32_t mask = hash_capacity(n, cap_max) - 1;
+  uint32_t mask = hash_capacity((long long)n * kSubmFan, cap_max) - 1;
   int row = blockIdx.y;
   int i = blockIdx.x * kIdxThreads + threadIdx.x;
   int c[D3D_MAX_NDIM + 1];
@@ -185,7 +188,7 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
   for (int t = threadIdx.x; t < g.kvol; t += kIdxThreads) cnt[t] = 0;
   __syncthreads();
-  const uint32_t mask = hash_capacity(n, cap_max) - 1;
+  const uint32_t mask = hash_capacity((long long)n * kSubmFan, cap_max) - 1;
   const int i = blockIdx.x * kIdxThreads + threadIdx.x;
   const bool live = i < n;
   int4 c = make_int4(-1, 0, 0, 0);
@@ -214,8 +217,32 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
         key[b] = key_k0 - (uint32_t)(k1 * g.dil[1]) * s3 - (uint32_t)(k2 * g.dil[2]);
         first[b] = probe[b] ? __ldg(&table[home_slot(key[b], mask)]) : kEmptySlot;
       }
+      // resolve all nine in lock step: a collision moves on to its next bucket together with the other unresolved
+      // probes, so the dependent-load chain is the longest probe sequence, not the sum of them
+      uint32_t slot[9];
+      uint32_t pending = 0;
 #pragma unroll
-      for (int b = 0; b < 9; ++b) v[b] = probe[b] ? hash_lookup_resolve(table, mask, key[b], first[b]) : -1;
+      for (int b = 0; b < 9; ++b) {
+        v[b] = -1;
+        if (probe[b]) {
+          if ((uint32_t)(first[b] >> 32) == key[b]) v[b] = (int32_t)(uint32_t)first[b];
+          else if (first[b] != kEmptySlot) pending |= 1u << b;
+        }
+        slot[b] = (home_slot(key[b], mask) + 4u) & mask;
+      }
+      for (uint32_t round = 0; pending && round <= (mask >> 2); ++round) {
+        unsigned long long cur[9];
+#pragma unroll
+        for (int b = 0; b < 9; ++b) cur[b] = ((pending >> b) & 1u) ? __ldg(&table[slot[b]]) : kEmptySlot;
+#pragma unroll
+        for (int b = 0; b < 9; ++b) {
+          if ((pending >> b) & 1u) {
+            if ((uint32_t)(cur[b] >> 32) == key[b]) v[b] = (int32_t)(uint32_t)cur[b], pending &= ~(1u << b);
+            else if (cur[b] == kEmptySlot) pending &= ~(1u << b);
+            else slot[b] = (slot[b] + 4u) & mask;
+          }
+        }
+      }
 #pragma unroll
       for (int b = 0; b < 9; ++b) {
         if (live) pair_out[(int64_t)(k + b) * n_max + i] = v[b];
@@ -663,7 +690,7 @@ int make_plan(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n
   D3D_REQUIRE(plan->n_max >= 0 && plan->n_max * (int64_t)g.kvol < (1ll << 31), D3D_ERR_TOO_LARGE);
   plan->row_len = (int64_t)g.kvol * (plan->n_max + 128);
   plan->nblk = (int)ceil_div(plan->n_max > 0 ? plan->n_max : 1, kIdxThreads);
-  plan->fan = p->subm ? 1 : (int)(fan < g.kvol ? fan : g.kvol);
+  plan->fan = p->subm ? kSubmFan : (int)(fan < g.kvol ? fan : g.kvol);
   size_t cap = next_pow2((size_t)(plan->n_max > 8 ? plan->n_max : 8) * plan->fan * 2);
   D3D_REQUIRE(cap <= (1ull << 30), D3D_ERR_TOO_LARGE);
   plan->cap_max = (uint32_t)(cap < 16 ? 16 : cap);
