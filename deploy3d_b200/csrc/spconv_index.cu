@@ -621,9 +621,17 @@ __global__ void fill_padding_kernel(const int32_t* __restrict__ seg, int kvol, i
   if (tail <= 0) return;
   if ((row_len & 3) == 0 && (reinterpret_cast<uintptr_t>(index) & 15) == 0) {
     const int64_t tail4 = tail >> 2;
+    const int4 fill = make_int4(-1, -1, -1, -1);
     for (int r = 0; r < 3; ++r) {
       int4* dst = reinterpret_cast<int4*>(index + r * row_len + num_index);
-      for (int64_t p = tid; p < tail4; p += nthreads) dst[p] = make_int4(-1, -1, -1, -1);
+      int64_t p = tid;
+      for (; p + 3 * nthreads < tail4; p += 4 * nthreads) {  // four independent 16-byte stores in flight
+        dst[p] = fill;
+        dst[p + nthreads] = fill;
+        dst[p + 2 * nthreads] = fill;
+        dst[p + 3 * nthreads] = fill;
+      }
+      for (; p < tail4; p += nthreads) dst[p] = fill;
     }
   } else {
     for (int r = 0; r < 3; ++r)

@@ -26,10 +26,17 @@ namespace {
 // writers, one value) and packed into the per-tile bit masks afterwards: atomics on the masks themselves serialise
 // on the few words all offsets of a tile share.
 __global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* flags32, int64_t flag_words) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (int64_t)gridDim.x * blockDim.x) {
-    table[i] = make_int4(-1, -1, -1, -1);
-    if (i < flag_words) flags32[i] = 0u;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int4 fill = make_int4(-1, -1, -1, -1);
+  int64_t i = tid;
+  for (; i + 3 * nthreads < n16; i += 4 * nthreads) {  // four independent 16-byte stores in flight
+    table[i] = fill;
+    table[i + nthreads] = fill;
+    table[i + 2 * nthreads] = fill;
+    table[i + 3 * nthreads] = fill;
   }
+  for (; i < n16; i += nthreads) table[i] = fill;
+  for (int64_t w = tid; w < flag_words; w += nthreads) flags32[w] = 0u;
 }
 
 // One warp per tile: lane k reads the flag of offset k.
