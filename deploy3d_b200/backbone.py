@@ -115,8 +115,10 @@ class SparseNet:
     """
 
     def __init__(self, layers, spatial, caps, dtype=torch.float16, device="cuda:0", seed=0, kernel=0,
-                 pad_input=True):
+                 pad_input=True, overlap_rulebooks=False):
         self.layers, self.device, self.dtype = layers, torch.device(device), dtype
+        self.overlap_rulebooks = overlap_rulebooks
+        self.side = torch.cuda.Stream(device=self.device) if overlap_rulebooks else None
         self.kernel = kernel
         weights = make_weights(layers, seed)
         self.rulebooks = {}
@@ -200,9 +202,38 @@ class SparseNet:
     def set_input(self, coors, num):
         self.sets["in"]["coors"], self.sets["in"]["num"] = coors, num
 
+    def _build_rulebook(self, rb):
+        src, dst = self.sets[rb.in_set], self.sets[rb.out_set]
+        if rb.kind == "subm":
+            rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor, outputs=[rb.index, rb.num_index])
+        else:
+            rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor,
+                              outputs=[rb.index, rb.num_index, dst["coors"], dst["num"], rb.out_shape_tensor])
+        SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd,
+                               mirror=rb.mirror)
+        if rb.table_inv is not None:
+            SPConvMMPlugin.prepare(rb.kvol, True, src["cap"], rb.index, rb.num_index, table=rb.table_inv)
+
     def forward(self, feats):
         """feats [cap_in, Cin] in the net dtype; coordinates / count as given to set_input.  Returns
-        (out_feats, out_coors, num_act_out); every tensor is a static buffer of the net."""
+        (out_feats, out_coors, num_act_out); every tensor is a static buffer of the net.
+
+        Rulebooks and neighbour tables depend on coordinates only, never on features, so with `overlap_rulebooks`
+        the whole chain of them is enqueued on a side stream ahead of the convolutions; a layer waits for the event
+        of its own rulebook.  Inside a CUDA graph capture this becomes a second branch of the graph."""
+        main = torch.cuda.current_stream(self.device)
+        ready = {}
+        if self.overlap_rulebooks:
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                done = set()
+                for L in self.layers:
+                    if L.key not in done:
+                        done.add(L.key)
+                        self._build_rulebook(self.rulebooks[L.key])
+                        ev = torch.cuda.Event()
+                        ev.record(self.side)
+                        ready[L.key] = ev
         built = set()
         saved = {}
         x = feats
@@ -211,23 +242,18 @@ class SparseNet:
                 x = saved[L.source]
             rb = self.rulebooks[L.key]
             if L.key not in built:
-                src, dst = self.sets[rb.in_set], self.sets[rb.out_set]
-                if rb.kind == "subm":
-                    rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor, outputs=[rb.index, rb.num_index])
+                if self.overlap_rulebooks:
+                    main.wait_event(ready[L.key])
                 else:
-                    rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor,
-                                      outputs=[rb.index, rb.num_index, dst["coors"], dst["num"],
-                                               rb.out_shape_tensor])
-                SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd,
-                                       mirror=rb.mirror)
-                if rb.table_inv is not None:
-                    SPConvMMPlugin.prepare(rb.kvol, True, src["cap"], rb.index, rb.num_index, table=rb.table_inv)
+                    self._build_rulebook(rb)
                 built.add(L.key)
             table = rb.table_inv if L.kind == "inverse" else rb.table_fwd
             res = saved[L.residual] if L.residual else None
             x = plug.run(x, self.sets[out_set]["num"], table, out=out_buf, relu=L.relu, residual=res)
             if L.save:
                 saved[L.save] = x
+        if self.overlap_rulebooks:
+            main.wait_stream(self.side)
         o = self.sets[self.out_set]
         return x, o["coors"], o["num"]
 

@@ -20,7 +20,7 @@ class DetectionPipeline:
     """CenterPoint-shaped (``kind='centerpoint'``) or SECOND-shaped (``kind='second'``) frame pipeline."""
 
     def __init__(self, kind="centerpoint", device="cuda:0", caps=None, kernel=0, n_class=10, topk=1000,
-                 iou_threshold=0.2, dtype=torch.float16, n_pts=None):
+                 iou_threshold=0.2, dtype=torch.float16, n_pts=None, overlap_rulebooks=True):
         self.kind, self.device, self.dtype = kind, torch.device(device), dtype
         if kind == "centerpoint":
             frame = synth.config4_points()
@@ -48,7 +48,8 @@ class DetectionPipeline:
             self.vox_coors = torch.zeros((cap_in, 4), dtype=torch.int32, device=dev)
             self.vox_num = torch.zeros(1, dtype=torch.int32, device=dev)
             spatial_b = [self.spatial[0]] + list(self.spatial[2:])
-            self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel)
+            self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel,
+                                          overlap_rulebooks=overlap_rulebooks)
             # low-precision copy of the voxel features, zero-padded to the channel count the first layer runs with
             self.vox_feats_lp = torch.zeros((cap_in, self.net.in_channels), dtype=dtype, device=dev)
             self.net.set_input(self.vox_coors, self.vox_num)
