@@ -385,15 +385,18 @@ __device__ __forceinline__ uint32_t winner_bits(const unsigned long long* __rest
 
 __global__ void conv_count_winners_kernel(const unsigned long long* __restrict__ table,
                                           const int32_t* __restrict__ pair_out, const int32_t* num_act_in,
-                                          int64_t n_max, int kvol, int32_t* __restrict__ winners) {
+                                          int64_t n_max, int kvol, int32_t* __restrict__ winners,
+                                          uint32_t* __restrict__ win_bits) {
   __shared__ int scratch[40];
   int n = live_count(num_act_in, n_max);
   int i = blockIdx.x * kIdxThreads + threadIdx.x;
   int cnt = 0;
   if (i < n) {
-    if (kvol <= 32)
-      cnt = __popc(winner_bits(table, pair_out, n_max, kvol, i));
-    else
+    if (kvol <= 32) {
+      const uint32_t bits = winner_bits(table, pair_out, n_max, kvol, i);
+      win_bits[i] = bits;  // kept for the numbering pass: it needs the same two dependent gathers per offset
+      cnt = __popc(bits);
+    } else
       for (int k = 0; k < kvol; ++k)
         cnt += is_winner(table, pair_out[(int64_t)k * n_max + i], (uint32_t)(i * kvol + k));
   }
@@ -405,7 +408,8 @@ __global__ void conv_count_winners_kernel(const unsigned long long* __restrict__
 // Number the output voxels in pair-id order and write their coordinates (index.cu:104-121).
 __global__ void conv_assign_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ pair_out,
                                    const int32_t* num_act_in, int64_t n_max, Geometry g,
-                                   const int32_t* __restrict__ winners_base, int32_t max_out,
+                                   const int32_t* __restrict__ winners_base,
+                                   const uint32_t* __restrict__ win_bits, int32_t max_out,
                                    int32_t* __restrict__ slot_out, int32_t* __restrict__ out_coors) {
   __shared__ int scratch[40];
   int n = live_count(num_act_in, n_max);
@@ -416,7 +420,7 @@ __global__ void conv_assign_kernel(const unsigned long long* __restrict__ table,
   const bool small = g.kvol <= 32;
   if (i < n) {
     if (small) {
-      bits = winner_bits(table, pair_out, n_max, g.kvol, i);
+      bits = win_bits[i];
       cnt = __popc(bits);
     } else {
       for (int k = 0; k < g.kvol; ++k)
@@ -653,6 +657,7 @@ struct Plan {
   int32_t* seg;
   int32_t* slot_out;
   int32_t* winners;
+  uint32_t* win_bits;  // per input: which of its offsets won an output voxel (kvol <= 32)
   size_t bytes;
 };
 
@@ -709,6 +714,7 @@ int make_plan(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n
   plan->seg = w.take<int32_t>(2 * (size_t)g.kvol + 2);
   plan->slot_out = p->subm ? nullptr : w.take<int32_t>(plan->cap_max);
   plan->winners = p->subm ? nullptr : w.take<int32_t>((size_t)plan->nblk + 1);
+  plan->win_bits = p->subm ? nullptr : w.take<uint32_t>((size_t)(plan->n_max > 0 ? plan->n_max : 1));
   plan->bytes = w.off;
   return D3D_OK;
 }
@@ -831,9 +837,10 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
       conv_insert_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
                                                                      plan.fan, plan.cap_max, plan.pair_out);
     conv_count_winners_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g.kvol,
-                                                            plan.winners);
+                                                            plan.winners, plan.win_bits);
     scan_totals_kernel<<<1, 1024, 0, st>>>(plan.winners, nblk, p->max_num_act_out, num_act_out);
     conv_assign_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g, plan.winners,
+                                                     plan.win_bits,
                                                      p->max_num_act_out, plan.slot_out, out_coors);
     conv_translate_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max, g.kvol,
                                                             plan.block_counts, nblk);
