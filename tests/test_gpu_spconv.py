@@ -45,7 +45,8 @@ def check_index(orc, outs, coors, n_max, shape_b, ks, st, pd, dl, op, max_out, s
     wc, wpairs, _ = orc.canonical_conv(want[0], want[1], want[2], want[3], kvol)
     out_coors = outs[2].cpu().numpy()
     nout = int(outs[3].item())
-    assert list(outs[4].shape) == [want[4][0], 0] + want[4][1:]
+    if len(outs) > 4:  # the plugin's fifth output; absent when `outs` come from the reference's builders
+        assert list(outs[4].shape) == [want[4][0], 0] + want[4][1:]
     assert nout == min(want[3], max_out)
     got = out_coors[:nout]
     if nout == want[3]:
