@@ -63,10 +63,12 @@ def spconv_index(coors_t, n_max, out_shape_b, ksize, stride, pad, dil, max_num_a
     kvol = int(np.prod(ksize))
     row_len = kvol * (n_max + 128)
     dev = coors_t.device
-    index = torch.zeros((3, row_len), dtype=torch.int32, device=dev)
-    num_index = torch.zeros(1, dtype=torch.int32, device=dev)
-    out_coors = None if subm else torch.zeros((max_num_act_out, 4), dtype=torch.int32, device=dev)
-    num_act_out = None if subm else torch.zeros(1, dtype=torch.int32, device=dev)
+    # uninitialised on purpose (no extra kernels in a timed call): the reference fills `index` with -1 itself and
+    # writes both counts; rows of out_coors beyond num_act_out stay undefined, as in the plugin
+    index = torch.empty((3, row_len), dtype=torch.int32, device=dev)
+    num_index = torch.empty(1, dtype=torch.int32, device=dev)
+    out_coors = None if subm else torch.empty((max_num_act_out, 4), dtype=torch.int32, device=dev)
+    num_act_out = None if subm else torch.empty(1, dtype=torch.int32, device=dev)
     ks, ksp = _v3(ksize)
     st, stp = _v3(stride)
     pd, pdp = _v3(pad)

@@ -60,7 +60,8 @@ def test_rulebook_matches_reference_gpu(d3d, orc, ref, case):
     coors = unique_coors(r, n, shape_b)
     kvol = int(np.prod(ks))
     out_shape_b = shape_b if subm else orc.out_shape(shape_b, ks, st, pd, dl, op, tr)
-    r_index, r_num, r_coors, r_nout = ref.spconv_index(_t(coors), n_max, out_shape_b, ks, st, pd, dl, max_out, subm, tr)
+    r_index, r_num, r_coors, r_nout = ref.spconv_index(_t(coors), n_max, out_shape_b, ks, st, pd, dl, max_out, subm,
+                                                       tr)
     ref_outs = [r_index, r_num] if subm else [r_index, r_num, r_coors, r_nout]
     # 1. the reference against the CPU oracle (pins the oracle)
     check_index(orc, ref_outs, coors, n_max, shape_b, ks, st, pd, dl, op, max_out, subm, tr)
@@ -68,14 +69,17 @@ def test_rulebook_matches_reference_gpu(d3d, orc, ref, case):
     spatial = [shape_b[0], 0] + shape_b[1:]
     outs, _ = run_index(d3d, coors, n_max, spatial, ks, st, pd, dl, op, max_out, subm, tr)
     got_num, ref_num = int(outs[1].item()), int(r_num.item())
-    assert got_num == ref_num
     if subm:
+        assert got_num == ref_num
         assert torch.equal(outs[0], r_index), "SubM rulebook differs from the reference's byte for byte"
         return
     ref_nout, got_nout = int(r_nout.item()), int(outs[3].item())
     assert got_nout == ref_nout
     assert list(outs[4].shape) == [out_shape_b[0], 0] + list(out_shape_b[1:])
+    # when maxNumActOut truncates, WHICH outputs survive is the reference's hash-slot order (implementation defined):
+    # both sides were checked against the oracle's rules for the kept subset above and in test_gpu_spconv.py
     if ref_nout < max_out:  # nothing truncated: same output set, same pairs
+        assert got_num == ref_num
         gc, gp, _ = orc.canonical_conv(outs[0].cpu().numpy(), got_num, outs[2].cpu().numpy(), got_nout, kvol)
         rc, rp, _ = orc.canonical_conv(r_index.cpu().numpy(), ref_num, r_coors.cpu().numpy(), ref_nout, kvol)
         assert (gc == rc).all(), "output coordinate sets differ from the reference's"
