@@ -1,9 +1,12 @@
-"""TEST INFRASTRUCTURE ONLY -- the reference's own GPU rulebook builders and indexed convolution.
+"""TEST INFRASTRUCTURE ONLY -- the reference's own GPU code: rulebook builders, indexed convolution, and its other
+plugins (voxel encoders, point <-> voxel mapping, BEV densify, NMS, box decode) through their plugin classes.
 
 ``oracle/_ref/libref_spconv.so`` is compiled by ``make -C oracle ref_spconv`` from the reference's
 trt/spconv/index.cu and trt/spconv/mm.h where those sources lie (wrappers: ``oracle/ref_spconv.cu``); it is a
 build product that is kept out of the history.  The functions here call it the way the reference's plugins do
-(trt/spconv/index_trt.cu:189-248, trt/spconv/mm_trt.cu:146-205), on torch CUDA tensors.
+(trt/spconv/index_trt.cu:189-248, trt/spconv/mm_trt.cu:146-205), on torch CUDA tensors.  The other plugins are one
+library each (``oracle/_ref/libref_<name>.so``, wrapper ``oracle/ref_plugin.cu``): the reference's plugin class is
+constructed from its serialised parameters and its own configurePlugin / getWorkspaceSize / enqueue run.
 
 Only the GPU parity tests and ``oracle/ref_gpu_timing.py`` may import this module; the product package never does.
 """
@@ -103,3 +106,59 @@ def spconv_mm(in_feats_t, weight_t, bias_t, index_t, num_index_t, inverse, max_n
     if rc != 0:
         raise RuntimeError("reference convolution: status %d" % rc)
     return out
+
+
+# ---- the reference's other plugins, driven through their own plugin classes --------------------------------------
+_PLUGIN_LIBS = {}
+
+
+class _Desc(ctypes.Structure):
+    _fields_ = [("dtype", ctypes.c_int32), ("nb_dims", ctypes.c_int32), ("dims", ctypes.c_int64 * 8)]
+
+
+def plugin_lib(name):
+    """oracle/_ref/libref_<name>.so (built by `make -C oracle ref_plugins`), or None when it was never built."""
+    if name not in _PLUGIN_LIBS:
+        path = os.path.join(_HERE, "_ref", "libref_%s.so" % name)
+        L = None
+        if os.path.exists(path):
+            L = ctypes.CDLL(path)
+            L.ref_plugin_num_outputs.restype = ctypes.c_int
+            L.ref_plugin_num_outputs.argtypes = [ctypes.c_char_p, ctypes.c_size_t]
+            L.ref_plugin_run.restype = ctypes.c_int
+            L.ref_plugin_run.argtypes = [ctypes.c_char_p, ctypes.c_size_t, ctypes.POINTER(_Desc), ctypes.c_int,
+                                         ctypes.POINTER(_Desc), ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                         ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p]
+        _PLUGIN_LIBS[name] = L
+    return _PLUGIN_LIBS[name]
+
+
+def _descs(tensors):
+    import torch
+    code = {torch.float32: 0, torch.float16: 1, torch.int8: 2, torch.int32: 3, torch.bool: 4}
+    arr = (_Desc * len(tensors))()
+    ptrs = (ctypes.c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i].dtype, arr[i].nb_dims = code[t.dtype], t.dim()
+        for d in range(t.dim()):
+            arr[i].dims[d] = int(t.shape[d])
+        ptrs[i] = t.data_ptr() if t.numel() else None
+    return arr, ptrs
+
+
+def run_plugin(name, data_s, inputs, outputs):
+    """Runs the reference plugin `name` (library suffix, e.g. "simple_mean") built from the serialised parameters
+    `data_s` on torch CUDA tensors; zero-element tensors carry shapes only, as in the reference.  `outputs` are
+    written in place.  Synchronises the device before returning."""
+    import torch
+    L = plugin_lib(name)
+    data_s = bytes(data_s)
+    assert L.ref_plugin_num_outputs(data_s, len(data_s)) == len(outputs)
+    inputs = [t.contiguous() for t in inputs]
+    din, pin = _descs(inputs)
+    dout, pout = _descs(outputs)
+    stream = torch.cuda.current_stream(outputs[0].device).cuda_stream
+    rc = L.ref_plugin_run(data_s, len(data_s), din, len(inputs), dout, len(outputs), pin, pout, stream)
+    if rc != 0:
+        raise RuntimeError("reference plugin %s: status %d" % (name, rc))
+    return outputs

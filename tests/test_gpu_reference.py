@@ -126,3 +126,175 @@ def test_features_match_reference_gpu(d3d, orc, ref, kind, cin, cout):
     assert np.allclose(want, exact, rtol=1e-2, atol=1e-1)
     # one rounding of an fp32 accumulator is no further from it than a chain of half-precision atomic adds
     assert np.sqrt(((got - exact) ** 2).sum()) <= 1.05 * np.sqrt(((want - exact) ** 2).sum()) + 1e-6
+
+
+# ---- the reference's other plugins, run through their own plugin classes (oracle/ref_plugin.cu) ------------------
+# Each test feeds the product library and the reference plugin the same tensors and the same serialised parameters
+# (the blob the reference's exporter writes), compares the two directly, and holds the CPU oracle against the
+# reference's output as well (which is what pins the oracle for these operators).
+
+def _ref_plugin(ref, name):
+    if ref.plugin_lib(name) is None:
+        pytest.skip("oracle/_ref/libref_%s.so was not built" % name)
+    return lambda data_s, inputs, outputs: ref.run_plugin(name, data_s, inputs, outputs)
+
+
+def _shape_t(s):
+    return torch.empty(s, dtype=torch.int32, device=DEV)
+
+
+def _by_coors(orc, coors, num, *arrays):
+    o = orc.lex_order(coors[:num])
+    return (coors[:num][o],) + tuple(a[:num][o] for a in arrays)
+
+
+def test_simple_mean_matches_reference_gpu(d3d, orc, ref):
+    from deploy3d_b200.ops import data_s_voxel_encoder
+    from tests.test_gpu_encoders import _mean_inputs
+    run = _ref_plugin(ref, "simple_mean")
+    pts, batch, cfg, shape = _mean_inputs(45, n=60000)
+    pts[::997, 1] = np.nan
+    batch[::991] = -1
+    max_out = 60000
+    ins = [_t(pts), _t(batch), _t(cfg), _shape_t(shape)]
+    got = d3d.simple_mean_encoder(*ins, max_out)
+    want = run(data_s_voxel_encoder(max_out), ins, [torch.zeros_like(t) for t in got])
+    torch.cuda.synchronize()
+    gn, wn = int(got[2].item()), int(want[2].item())
+    assert gn == wn
+    gc, gf = _by_coors(orc, got[1].cpu().numpy(), gn, got[0].cpu().numpy())
+    wc, wf = _by_coors(orc, want[1].cpu().numpy(), wn, want[0].cpu().numpy())
+    assert (gc == wc).all(), "voxel sets differ from the reference's"
+    assert np.allclose(gf, wf, atol=1e-3, rtol=1e-3)  # float atomics in a different order
+    of, oc, on = orc.simple_mean(pts, batch, cfg, shape, max_out)
+    assert on == wn
+    oc, of = _by_coors(orc, oc, on, of)
+    assert (oc == wc).all() and np.allclose(of, wf, atol=1e-3, rtol=1e-3)
+
+
+def test_cylinder_matches_reference_gpu(d3d, orc, ref):
+    from deploy3d_b200.ops import data_s_voxel_encoder
+    from deploy3d_b200.synth import drop_edge_points
+    run = _ref_plugin(ref, "cylinder")
+    r = rng(46)
+    n = 60000
+    pts = np.stack([r.standard_normal(n) * 100, r.standard_normal(n) * 100, r.standard_normal(n) * 3 + 1,
+                    r.standard_normal(n)], 1).astype(np.float32)
+    batch = r.integers(0, 2, n).astype(np.int32)
+    batch[::983] = -1
+    cfg = np.array([-2, -np.pi, 0, 4, np.pi, 50], np.float32)
+    shape = [2, 0, 480, 360, 32]
+    rho, phi = np.sqrt(pts[:, 0] ** 2 + pts[:, 1] ** 2), np.arctan2(pts[:, 1], pts[:, 0])
+    step = (cfg[3:] - cfg[:3]) / np.array([32, 360, 480], np.float32)
+    keep = drop_edge_points(np.stack([pts[:, 2], phi, rho], 1), cfg[:3], step)
+    pts, batch = pts[keep], batch[keep]
+    n = len(pts)
+    ins = [_t(pts), _t(batch), _t(cfg), _shape_t(shape)]
+    got = [t.cpu().numpy() for t in d3d.cylinder_encoder(*ins, n)]
+    want = run(data_s_voxel_encoder(n), ins, [torch.zeros_like(_t(g)) for g in got])
+    want = [t.cpu().numpy() for t in want]
+    (g_aug, g_st, g_sc, g_co, g_n), (w_aug, w_st, w_sc, w_co, w_n) = got, want
+    gn, wn = int(g_n[0]), int(w_n[0])
+    assert gn == wn
+    valid = w_st >= 0
+    assert ((g_st >= 0) == valid).all()
+    assert np.allclose(g_aug[valid], w_aug[valid], atol=1e-5, rtol=1e-5)
+    # same point -> voxel mapping up to the (race-dependent) voxel numbering
+    assert (g_co[:gn][g_st[valid]] == w_co[:wn][w_st[valid]]).all()
+    gc, gs = _by_coors(orc, g_co, gn, g_sc)
+    wc, ws = _by_coors(orc, w_co, wn, w_sc)
+    assert (gc == wc).all() and (gs == ws).all()
+    o_aug, o_st, o_sc, o_co, o_n = orc.cylinder(pts, batch, cfg, shape, n)
+    assert o_n == wn and ((o_st >= 0) == valid).all()
+    assert np.allclose(o_aug[valid], w_aug[valid], atol=1e-3, rtol=1e-3)  # host libm vs device atan2f / sqrtf
+    assert (o_co[:o_n][o_st[valid]] == w_co[:wn][w_st[valid]]).all()
+
+
+@pytest.mark.parametrize("reduce_type", [0, 1])
+def test_scatter_to_matches_reference_gpu(d3d, orc, ref, reduce_type):
+    from deploy3d_b200.ops import data_s_scatter_to
+    run = _ref_plugin(ref, "scatter_to")
+    r = rng(52 + reduce_type)
+    n, m, num_act, c = 100000, 32768, 30000, 9
+    base = np.arange(-1, num_act, dtype=np.int32)
+    idx = np.concatenate([base, r.integers(-1, num_act, n - base.size).astype(np.int32)])[r.permutation(n)]
+    cnt = np.zeros(m, np.int32)
+    u, k = np.unique(idx[idx >= 0], return_counts=True)
+    cnt[u] = k
+    x = r.standard_normal((n, c)).astype(np.float32)
+    ins = [_t(x), _t(idx), _t(cnt)]
+    got = d3d.scatter_to(*ins, reduce_type)
+    want = run(data_s_scatter_to(reduce_type), ins, [torch.zeros_like(got)])[0]
+    got, want = got.cpu().numpy(), want.cpu().numpy()
+    oracle_out = orc.scatter_to(x, idx, cnt, reduce_type)
+    if reduce_type == 0:
+        assert (got == want).all() and (oracle_out == want).all()  # max is exact, untouched rows included
+    else:
+        assert np.allclose(got, want, atol=1e-3, rtol=1e-3) and np.allclose(oracle_out, want, atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("fill_val", [None, 6.9])
+def test_gather_back_matches_reference_gpu(d3d, orc, ref, fill_val):
+    from deploy3d_b200.ops import data_s_gather_back, gather_back
+    run = _ref_plugin(ref, "gather_back")
+    r = rng(61)
+    n, m = 100000, 32768
+    idx = r.integers(-1, m, n).astype(np.int32)
+    x = r.standard_normal((m, 9)).astype(np.float32)
+    init = torch.full((n, 9), 3.25, dtype=torch.float32, device=DEV)
+    got = gather_back(_t(x), _t(idx), fill_val, out=init.clone()).cpu().numpy()
+    want = run(data_s_gather_back(fill_val), [_t(x), _t(idx)], [init.clone()])[0].cpu().numpy()
+    assert (got == want).all()
+    assert (orc.gather_back(x, idx, fill_val, out_init=np.full((n, 9), 3.25, np.float32)) == want).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_bev_densify_matches_reference_gpu(d3d, orc, ref, dtype):
+    from deploy3d_b200.ops import data_s_bev_densify
+    run = _ref_plugin(ref, "bev_densify")
+    r = rng(71)
+    n_max, num_act, c = 10000, 8000, 128
+    shape = [2, 0, 2, 128, 128]
+    coors = np.zeros((n_max, 4), np.int32)
+    coors[:num_act] = unique_coors(r, num_act, [2, 2, 128, 128])
+    feats = torch.from_numpy(r.standard_normal((n_max, c)).astype(np.float32)).to(dtype).to(DEV)
+    ins = [feats, _t(coors), torch.tensor([num_act], dtype=torch.int32, device=DEV), _shape_t(shape)]
+    got = d3d.bev_densify(*ins, c * 2)
+    want = run(data_s_bev_densify(c * 2), ins, [torch.full_like(got, 7.0)])[0]  # the reference clears the map itself
+    assert torch.equal(got, want)
+    assert (orc.bev_densify(feats.float().cpu().numpy(), coors, num_act, shape) == want.float().cpu().numpy()).all()
+
+
+def test_nms3d_matches_reference_gpu(d3d, orc, ref):
+    from deploy3d_b200 import synth
+    run = _ref_plugin(ref, "nms3d")
+    b = synth.config4_boxes(4, 700)
+    scores, boxes = _t(b["scores"]), _t(b["boxes"])
+    got = d3d.nms3d(scores, boxes)  # the plugin's constant threshold 0.1 (trt/decoder/nms3d.cu:138)
+    want = run(b"", [scores, boxes], [torch.zeros_like(got)])[0]
+    assert torch.equal(got, want)
+    assert (orc.nms3d(b["scores"], b["boxes"], 0.1) == want.cpu().numpy()).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_yolox3d_decode_matches_reference_gpu(d3d, orc, ref, dtype):
+    from deploy3d_b200.ops import data_s_yolox3d_decode
+    from tests.test_gpu_decoder import _head
+    run = _ref_plugin(ref, "yolox3d_decode")
+    r = rng(13)
+    scores, preds = _head(r, 2, 3, 96, 104, 2)
+    cfg = np.array([-54.0, -54.0, -5.0, 0.075, 0.075, 0.2], dtype=np.float32)
+    stride, class_ids, topk = 8, (0, 3, 7), 300
+    ins = [_t(scores).to(dtype), _t(preds).to(dtype), _t(cfg)]
+    got = d3d.yolox3d_decode(*ins, stride, class_ids, topk)
+    want = run(data_s_yolox3d_decode(stride, class_ids, topk), ins, [torch.zeros_like(t) for t in got])
+    orc_out = orc.yolox3d_decode(ins[0].float().cpu().numpy(), ins[1].float().cpu().numpy(), cfg, stride, class_ids,
+                                 topk)
+    for ci in range(len(class_ids)):
+        g_ids, g_sc, g_bx = (t.cpu().numpy() for t in got[3 * ci:3 * ci + 3])
+        w_ids, w_sc, w_bx = (t.cpu().numpy() for t in want[3 * ci:3 * ci + 3])
+        assert (g_ids == w_ids).all() and (g_sc == w_sc).all(), "class %d: selection differs from the reference" % ci
+        np.testing.assert_allclose(g_bx, w_bx, rtol=1e-5, atol=1e-5)
+        o_ids, o_sc, o_bx = orc_out[ci]
+        assert (o_ids == w_ids).all() and (o_sc == w_sc).all()
+        np.testing.assert_allclose(o_bx, w_bx, rtol=1e-5, atol=1e-5)

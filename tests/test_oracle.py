@@ -58,6 +58,58 @@ def test_rulebook_golden(orc):
     assert (oc[orc.lex_order(oc[:nout])] == g["down_out_coors"]).all()
 
 
+def _ref_gpu_golden():
+    path = os.path.join(GOLD, "spconv_ref_gpu.npz")
+    return np.load(path) if os.path.exists(path) else None
+
+
+REF_GPU_CASES = ["subm", "subm_pad", "subm_dil", "subm_313", "down221", "down222", "down_k2", "up222"]
+
+
+@pytest.mark.parametrize("name", REF_GPU_CASES)
+def test_rulebook_matches_reference_gpu_golden(orc, name):
+    """The oracle against rulebooks the reference's own GPU code produced on a B200 (trt/spconv/index.cu compiled
+    for sm_100a; generator tests/golden/make_golden_gpu.py): SubM byte for byte with the padding, strided and
+    transposed after the canonicalisation that removes the reference's race-dependent output numbering."""
+    g = _ref_gpu_golden()
+    assert g is not None, "tests/golden/spconv_ref_gpu.npz is part of the repository"
+    p = [int(v) for v in g[name + "_params"]]
+    ks, st, pd, dl, op = (tuple(p[i * 3:i * 3 + 3]) for i in range(5))
+    tr, subm, n_max, max_out = bool(p[15]), bool(p[16]), p[17], p[18]
+    coors, shape = g[name + "_coors"], [int(v) for v in g[name + "_shape"]]
+    kvol = int(np.prod(ks))
+    if subm:
+        index, num = orc.rulebook_subm(coors, shape, ks, st, pd, dl, max_num_act_in=n_max)
+        assert num == int(g[name + "_num"])
+        assert index.shape == g[name + "_index"].shape and (index == g[name + "_index"]).all()
+        return
+    index, num, oc, nout, _ = orc.rulebook_conv(coors, shape, ks, st, pd, dl, op, tr, max_out, max_num_act_in=n_max)
+    assert num == int(g[name + "_num"])
+    cc, pairs, _ = orc.canonical_conv(index, num, oc, nout, kvol)
+    assert cc.shape == g[name + "_out_coors"].shape and (cc == g[name + "_out_coors"]).all()
+    flat = np.concatenate([np.concatenate([np.full((len(pairs[k]), 1), k, np.int64), pairs[k]], 1)
+                           for k in range(kvol)])
+    assert flat.shape == g[name + "_pairs"].shape and (flat == g[name + "_pairs"]).all()
+
+
+@pytest.mark.parametrize("tag,index_key,inverse", [("mm_subm", "subm_index", False),
+                                                   ("mm_down221", "mm_down221_index", False),
+                                                   ("mm_down221_inv", "mm_down221_inv_index", True)])
+def test_conv_matches_reference_gpu_golden(orc, tag, index_key, inverse):
+    """The oracle's fp32 gather-GEMM-scatter against the reference's indexedSpConv output (fp16 operands, half
+    atomic adds, trt/spconv/mm.h:35-71) recorded on a B200, at the tolerance of the reference's own test
+    (tests/spconv/test_spconv.py:152-161: rtol 1e-2, atol 1e-1)."""
+    g = _ref_gpu_golden()
+    assert g is not None
+    index, want = g[index_key], g[tag + "_out"].astype(np.float32)
+    num = int(g["subm_num"] if tag == "mm_subm" else g["down221_num"])
+    got = orc.spconv_mm(g[tag + "_feats"].astype(np.float32), g[tag + "_w"].astype(np.float32),
+                        g[tag + "_b"].astype(np.float32), index, num, inverse, want.shape[0])
+    assert got.shape == want.shape
+    assert np.allclose(got, want, rtol=1e-2, atol=1e-1), "worst |diff| %.3e" % np.abs(got - want).max()
+    assert np.sqrt(((got - want) ** 2).sum() / (want ** 2).sum()) < 5e-3
+
+
 CASES = [
     # ksize, stride, pad, dil, out_pad, transpose, subm
     ((3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), (0, 0, 0), False, True),
