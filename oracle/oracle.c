@@ -13,9 +13,12 @@
  * canonicalisation (see oracle.py).
  *
  * Parity pins: the rotated-IoU arithmetic is checked bit-for-bit against the reference's
- * own trt/decoder/iou_rotated.cuh compiled for the host (oracle/_ref); the rulebook layout
- * is checked against the properties the reference's tests assert
- * (tests/spconv/test_spconv.py:72-124) and against a brute-force dictionary model.
+ * own trt/decoder/iou_rotated.cuh compiled for the host (oracle/_ref); rulebooks and the
+ * convolution are checked against golden vectors the reference's own GPU code (trt/spconv/index.cu,
+ * trt/spconv/mm.h compiled for sm_100a) wrote on a B200 (tests/golden/spconv_ref_gpu.npz), and every
+ * operator against the reference's plugin classes run on the GPU (tests/test_gpu_reference.py);
+ * beside those, the properties the reference's tests assert (tests/spconv/test_spconv.py:72-124)
+ * and a brute-force dictionary model of the rulebook.
  */
 #include <math.h>
 #include <stdint.h>
