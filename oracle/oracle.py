@@ -24,8 +24,12 @@ _f32p = ctypes.POINTER(ctypes.c_float)
 
 
 def build():
-    """Compile the oracle (and the host build of the reference IoU header when the reference is present)."""
-    subprocess.run(["make", "-C", _HERE, "--no-print-directory"], check=True, capture_output=True)
+    """Compile the oracle and, when the reference checkout is present, the reference-derived libraries under
+    oracle/_ref (host build of its IoU header; its GPU sources for sm_100a).  Only the oracle itself is required:
+    a reference target that cannot be built here leaves the prebuilt library, if any, in place."""
+    subprocess.run(["make", "-C", _HERE, "--no-print-directory", "liboracle.so"], check=True, capture_output=True)
+    subprocess.run(["make", "-C", _HERE, "--no-print-directory", "-k", "ref", "ref_spconv", "ref_plugins"],
+                   check=False, capture_output=True)
 
 
 def lib():
