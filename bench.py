@@ -155,7 +155,32 @@ def run_reference(args):
         "e2e": {"value": fps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    gpu = reference_gpu_kernels()
+    if gpu is not None:
+        line["reference_gpu"] = gpu
     print(json.dumps(line))
+
+
+def reference_gpu_kernels():
+    """Extra, informational key of the reference arm: the reference has no CPU implementation (the value of this arm
+    is the CPU port of its algorithm), but its own CUDA kernels compile for sm_100a (oracle/_ref/libref_spconv.so).
+    When that library and a GPU are present, time its rulebook builders and convolution launches on the benchmark
+    frame, one after the other with CUDA events.  Not a frames/s figure of a complete reference pipeline: its ReLU /
+    add graph ops, encoder, densify, NMS and host synchronisations are not included, so 1 / (sum) bounds it from above."""
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return None
+        from oracle import ref_gpu_timing
+        r = ref_gpu_timing.measure(reps=5)
+        ref_ms = (r["rulebook_us"][0] + r["conv_us"][0]) * 1e-3
+        return {"rulebook_ms_per_frame": r["rulebook_us"][0] * 1e-3, "conv_ms_per_frame": r["conv_us"][0] * 1e-3,
+                "frames_per_s_upper_bound": 1e3 / ref_ms,
+                "what": "reference CUDA kernels (trt/spconv/index.cu, trt/spconv/mm.h) recompiled for sm_100a, "
+                        "rulebooks + 21 convolution launches of one config-4 frame, back to back on one B200"}
+    except Exception as e:  # the arm's value does not depend on this
+        sys.stderr.write("reference_gpu skipped: %s\n" % e)
+        return None
 
 
 # ------------------------------------------------------------------------------------------------------------------

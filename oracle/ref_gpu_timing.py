@@ -28,19 +28,25 @@ def _time(fn, reps):
     return e0.elapsed_time(e1) * 1e3 / reps  # microseconds
 
 
-def main():
+def measure(reps=5, out=None):
+    """Times both sides and returns {"rulebook_us": (reference, product), "conv_us": (reference, product)} per
+    frame; prints the per-rulebook / per-layer table to `out` when given.  Raises RuntimeError when the reference
+    library is not built."""
+    import argparse as _argparse
     import torch
     from deploy3d_b200 import synth
     from deploy3d_b200.backbone import make_weights
     from deploy3d_b200.pipeline import DetectionPipeline
     from oracle import ref_gpu
 
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--reps", type=int, default=5)
-    args = ap.parse_args()
+    def print(*a):  # noqa: A001 -- the table goes to `out` or nowhere
+        if out is not None:
+            out.write(" ".join(str(x) for x in a) + "\n")
+
+    args = _argparse.Namespace(reps=reps)
     L = ref_gpu.lib()
     if L is None or not L.has_mm:
-        raise SystemExit("oracle/_ref/libref_spconv.so (with the convolution) is not built")
+        raise RuntimeError("oracle/_ref/libref_spconv.so (with the convolution) is not built")
     frame, boxes = synth.config4_points(), synth.config4_boxes()
     probe = DetectionPipeline("centerpoint", "cuda:0")
     probe.load_frame(frame, boxes)
@@ -71,6 +77,7 @@ def main():
         print("%-8s %-7s %9d %9d | %12.1f %12.1f %6.1fx" % (key, rb.kind, n, counts[rb.out_set], t_ref, t_our,
                                                             t_ref / t_our))
     print("%-36s | %12.1f %12.1f %6.1fx" % ("all rulebooks of a frame", tot_ref, tot_our, tot_ref / tot_our))
+    result = {"rulebook_us": (tot_ref, tot_our)}
 
     print("\nconvolution layers (microseconds per launch)")
     print("%-5s %-9s %9s | %12s %12s %7s" % ("layer", "channels", "M out", "reference", "product", "ratio"))
@@ -103,6 +110,19 @@ def main():
         print("%-5d %3d->%-4d %9d | %12.1f %12.1f %6.1fx" % (li, w.shape[1], w.shape[2], counts[out_set], t_ref, t_our,
                                                              t_ref / t_our))
     print("%-25s | %12.1f %12.1f %6.1fx" % ("all layers of a frame", tot_ref, tot_our, tot_ref / tot_our))
+    result["conv_us"] = (tot_ref, tot_our)
+    return result
+
+
+def main():
+    import sys
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reps", type=int, default=5)
+    args = ap.parse_args()
+    try:
+        measure(args.reps, sys.stdout)
+    except RuntimeError as e:
+        raise SystemExit(str(e))
 
 
 if __name__ == "__main__":

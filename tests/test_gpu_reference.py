@@ -298,3 +298,41 @@ def test_yolox3d_decode_matches_reference_gpu(d3d, orc, ref, dtype):
         o_ids, o_sc, o_bx = orc_out[ci]
         assert (o_ids == w_ids).all() and (o_sc == w_sc).all()
         np.testing.assert_allclose(o_bx, w_bx, rtol=1e-5, atol=1e-5)
+
+
+def test_config4_rulebooks_match_reference_gpu(d3d, orc, ref):
+    """Benchmark size: the first SubM rulebook (about 281 000 voxels) and the first strided rulebook (-> about
+    463 000 outputs) of a config-4 frame, product against the reference's builders: SubM byte for byte, strided
+    after canonicalisation (output coordinate sets and every per-offset pair list)."""
+    from deploy3d_b200 import synth
+    frame = synth.config4_points()
+    cfg, shape = frame["voxel_config"], frame["spatial_shape"]
+    pts = frame["points"]
+    pts = pts[synth.drop_edge_points(pts[:, :3], cfg[:3], cfg[3:])]
+    n_pts = len(pts)
+    _, coors, num = d3d.simple_mean_encoder(_t(pts), _t(np.zeros(n_pts, np.int32)), _t(cfg),
+                                            torch.empty(shape, dtype=torch.int32, device=DEV), n_pts)
+    n = int(num.item())
+    coors = coors[:n].contiguous()
+    shape_b = [shape[0]] + list(shape[2:])
+    one, ks = (1, 1, 1), (3, 3, 3)
+    num_t = torch.tensor([n], dtype=torch.int32, device=DEV)
+    shp = torch.empty(shape, dtype=torch.int32, device=DEV)
+    # SubM
+    got = d3d.spconv_index(coors, num_t, shp, ks, one, one, one, (0, 0, 0), n, True, False)
+    want = ref.spconv_index(coors, n, shape_b, ks, one, one, one, n, True, False)
+    assert int(got[1].item()) == int(want[1].item())
+    assert torch.equal(got[0], want[0])
+    del got, want
+    # strided 2x2x2
+    st = (2, 2, 2)
+    oshape = orc.out_shape(shape_b, ks, st, one, one, (0, 0, 0), False)
+    cap = 2 * n
+    got = d3d.spconv_index(coors, num_t, shp, ks, st, one, one, (0, 0, 0), cap, False, False)
+    want = ref.spconv_index(coors, n, oshape, ks, st, one, one, cap, False, False)
+    g_num, w_num, g_out, w_out = (int(t.item()) for t in (got[1], want[1], got[3], want[3]))
+    assert (g_num, g_out) == (w_num, w_out) and w_out < cap
+    gc, gp, _ = orc.canonical_conv(got[0].cpu().numpy(), g_num, got[2].cpu().numpy(), g_out, 27)
+    wc, wp, _ = orc.canonical_conv(want[0].cpu().numpy(), w_num, want[2].cpu().numpy(), w_out, 27)
+    assert (gc == wc).all()
+    pairs_equal(gp, wp, 27)
