@@ -105,6 +105,7 @@ SIGNATURES = {
     "d3d_spconv_mm_run": (ctypes.c_int, [_vp, ctypes.c_int, _vp, ctypes.c_int64, _vp, _vp, _vp,
                                           ctypes.POINTER(SpconvMMEpilogue), _vp]),
     "d3d_spconv_mm_set_kernel": (ctypes.c_int, [_vp, ctypes.c_int]),
+    "d3d_spconv_mm_set_dependent_launch": (ctypes.c_int, [_vp, ctypes.c_int]),
     "d3d_bev_densify_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(BevDensifyParams)]),
     "d3d_bev_densify_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(BevDensifyParams))),
     "d3d_bev_densify_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(BevDensifyParams))),

@@ -192,6 +192,9 @@ class SparseNet:
                     L.ksize, cin, L.cout, self.sets[out_set]["cap"], L.kind == "subm", L.kind == "inverse", w, b))
                 plug.configure(dtype)
                 plug.set_kernel(kernel)
+                # single-stream execution: the next layer's prologue overlaps this layer's tail; with the rulebook
+                # chain on a side stream its kernels fill those tails instead (measured: 1 % better per frame)
+                plug.set_dependent_launch(not overlap_rulebooks)
                 out_buf = torch.zeros((self.sets[out_set]["cap"], L.cout), dtype=dtype, device=self.device)
                 self.mm.append((plug, out_buf, out_set))
                 cur = out_set

@@ -352,6 +352,12 @@ extern "C" int d3d_spconv_mm_destroy(d3d_spconv_mm_t h) {
   return D3D_OK;
 }
 
+extern "C" int d3d_spconv_mm_set_dependent_launch(d3d_spconv_mm_t h, int enable) {
+  D3D_REQUIRE(h, D3D_ERR_INVALID_ARGUMENT);
+  h->dependent_launch = enable ? 1 : 0;
+  return D3D_OK;
+}
+
 extern "C" int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t h, int which) {
   D3D_REQUIRE(h && which >= 0 && which <= 3, D3D_ERR_INVALID_ARGUMENT);
   h->kernel_choice = which;

@@ -16,6 +16,7 @@ struct d3d_spconv_mm_s {
   void* wt_dev = nullptr;    // [kVol][Cout][Cin] in `dtype` (K-major B operand of the tcgen05 kernel)
   float* b_dev = nullptr;    // bias in fp32 (zeros when the blob has no bias)
   int kernel_choice = 0;     // 0 auto, 1 SIMT, 2 tcgen05
+  int dependent_launch = 0;  // tcgen05 path: launch with the programmatic stream-serialisation attribute
   void* tc_state = nullptr;  // tensor maps of the tcgen05 path (owned by spconv_mm_tc.cu)
 };
 

@@ -161,6 +161,12 @@ __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
+// Programmatic dependent launch.  `pdl_release` lets the next kernel of the stream start its prologue once every CTA
+// of this grid has called it (the CTAs of the next grid become resident as this grid's CTAs leave their SMs);
+// `pdl_wait` blocks until the preceding grid has completed and its memory is visible.  Both are no-ops when the
+// kernels were launched without the programmatic attribute.
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit_if(uint32_t run, uint64_t* bar) {
@@ -364,6 +370,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   uint32_t phase = 0, idx_phase = 0;  // idx_phase bit b: parity to wait for on idx_full[b]
   int buf = 0;
   bool ok = true;
+  pdl_wait();  // masks, ids and features may come from the preceding kernels
   uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
   for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
     const int next = tile + gridDim.x;
@@ -429,8 +436,7 @@ __device__ __forceinline__ void control_role(const TcParams& p, const Smem& s, c
   const int ids_per_tile = p.kvol * kTileRows;
   const uint32_t gmask = (1u << p.group) - 1u;
   if ((int)blockIdx.x >= p.num_tiles) return;
-  mbar_arrive_expect_tx(&sh->idx_full[0], p.idx_bytes);
-  bulk_load_1d(&sh->idx_full[0], s.idx, p.table + (int64_t)blockIdx.x * ids_per_tile, p.idx_bytes);
+  // the weights are constants of the layer: their load does not wait for the preceding kernel
   if (p.b_resident) {  // in the layout the per-stage loads would have produced
     mbar_arrive_expect_tx(&sh->b_ready, (uint32_t)p.kvol * b_tx);
     for (int k = 0; k < p.kvol; ++k)
@@ -438,6 +444,9 @@ __device__ __forceinline__ void control_role(const TcParams& p, const Smem& s, c
         tma_load_2d(map_b, &sh->b_ready, s.bres + (size_t)k * p.b_bytes + (size_t)c * p.cout * p.row_bytes, c * 64,
                     k * p.cout);
   }
+  pdl_wait();
+  mbar_arrive_expect_tx(&sh->idx_full[0], p.idx_bytes);
+  bulk_load_1d(&sh->idx_full[0], s.idx, p.table + (int64_t)blockIdx.x * ids_per_tile, p.idx_bytes);
   int stage = 0, buf = 0;
   uint32_t phase = 0, free_phase = 0;  // free_phase bit b: parity to wait for on idx_free[b]
   bool first_tile = true;
@@ -509,6 +518,7 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
   uint32_t phase = 0, acc_phase = 0;
   const int num_stages = p.stages, kvol = p.kvol, kparts = p.kparts;
   const uint32_t lane0 = (threadIdx.x & 31) == 0 ? 1u : 0u;  // the lane that issues; the others keep it company
+  pdl_wait();
   uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
     const int next = tile + gridDim.x;
@@ -566,6 +576,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
   const int lane = threadIdx.x & 31;
   int acc = 0;
   uint32_t acc_phase = 0;
+  pdl_wait();  // residual rows come from an earlier layer; output rows may still be read by the preceding kernel
   uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
     const int next = tile + gridDim.x;
@@ -615,6 +626,7 @@ spconv_mm_tc_kernel(const __grid_constant__ CUtensorMap map_b, const TcParams p)
   const Smem s = carve_smem(smem_raw, p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t tmem_base = cta_setup<kProd>(p, s);
+  pdl_release();
   if (warp < kProd / 32) {
     producer_role<2 * kSteps, kGroup, kProd>(p, s, threadIdx.x);
   } else if (warp == mma_warp_of(kProd)) {
@@ -820,8 +832,18 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   }
   const int ctas = kNumSMs * (two_per_sm ? 2 : 1);
   const int grid = p.num_tiles < ctas ? p.num_tiles : ctas;
-  kernels[di][si][gi]<<<grid, threads_of(two_per_sm ? 128 : 256), smem, reinterpret_cast<cudaStream_t>(a.stream)>>>(
-      st->map_b, p);
+  // programmatic dependent launch (opt-in per handle): the prologue of this kernel (barriers, tensor memory,
+  // weights) may overlap the tail of the preceding kernel of the stream; every role waits for that kernel before
+  // it touches its data.  Measured on B200: 3-4 us less per launch for layers run back to back on one stream; a
+  // loss where other streams have kernels that would otherwise fill the tail of the preceding kernel.
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(threads_of(two_per_sm ? 128 : 256));
+  cfg.dynamicSmemBytes = smem, cfg.stream = reinterpret_cast<cudaStream_t>(a.stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr, cfg.numAttrs = h->dependent_launch ? 1 : 0;
+  if (cudaLaunchKernelEx(&cfg, kernels[di][si][gi], st->map_b, p) != cudaSuccess) return D3D_ERR_CUDA;
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }

@@ -160,6 +160,11 @@ class SPConvMMPlugin(_Plugin):
         """0 automatic, 1 SIMT, 2 tcgen05, 3 tcgen05 with one CTA per SM."""
         check("d3d_spconv_mm_set_kernel", lib().d3d_spconv_mm_set_kernel(self.handle, int(which)))
 
+    def set_dependent_launch(self, enable):
+        """Programmatic dependent launch of the tensor-core kernel, for layers enqueued back to back on one stream."""
+        check("d3d_spconv_mm_set_dependent_launch",
+              lib().d3d_spconv_mm_set_dependent_launch(self.handle, int(bool(enable))))
+
     # two-step form: one neighbour table shared by all layers over the same rulebook
     @staticmethod
     def table_bytes(kernel_vol, max_num_act_out):

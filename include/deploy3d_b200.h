@@ -174,6 +174,12 @@ int d3d_spconv_mm_run(d3d_spconv_mm_t handle, int dtype, const void* in_feats, i
  * channels otherwise run two half-size CTAs per SM).  2 and 3 fail with D3D_ERR_INVALID_ARGUMENT at run time when
  * the shape is not eligible. */
 int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t handle, int which);
+/* Opt-in for callers that enqueue layers back to back on ONE stream (as TensorRT does): the tensor-core kernel is
+ * launched with the programmatic stream-serialisation attribute, so that its prologue overlaps the tail of the
+ * preceding kernel of the stream; it waits for that kernel before reading or writing any tensor.  Results are
+ * unchanged.  Off by default: where other streams run kernels beside the layers, those fill the tails better.
+ * No reference counterpart. */
+int d3d_spconv_mm_set_dependent_launch(d3d_spconv_mm_t handle, int enable);
 
 /* ---------------------------------------------------------------------------------------------
  * BEVDensify.  Replaces spconv::BEVDensifyPlugin (trt/spconv/bev_densify_trt.cu:52-178).

@@ -139,3 +139,41 @@ def test_mirror_table_build_gives_the_same_table(d3d, ks, dil):
     mask_a = plain[ids_bytes_aligned:ids_bytes_aligned + 4 * tiles].view(torch.int32)
     mask_b = mirrored[ids_bytes_aligned:ids_bytes_aligned + 4 * tiles].view(torch.int32)
     assert (mask_a == mask_b).all() and (mask_a != 0).any()
+
+
+def test_dependent_launch_is_bit_identical(d3d):
+    """Three layers chained on one stream, launched with and without the programmatic stream-serialisation attribute:
+    every layer waits for its predecessor before it reads, so the results are the same bit for bit."""
+    from deploy3d_b200 import synth
+    from deploy3d_b200.ops import data_s_spconv_index, data_s_spconv_mm
+    from deploy3d_b200.plugins import SPConvMMPlugin, deserialize_plugin
+    r = np.random.Generator(np.random.PCG64(321))
+    vox = synth.lidar_like_voxels(r, 60000, (21, 400, 400))
+    n = len(vox)
+    coors = torch.from_numpy(np.concatenate([np.zeros((n, 1), np.int32), vox], 1)).cuda()
+    num = torch.tensor([n], dtype=torch.int32, device="cuda")
+    shape = torch.empty([1, 0, 21, 400, 400], dtype=torch.int32, device="cuda")
+    ip = deserialize_plugin("SPConvIdx3d", data_s_spconv_index((3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), (0, 0, 0),
+                                                                n, True, False))
+    index, num_index = ip.enqueue(coors, num, shape)
+    table = SPConvMMPlugin.prepare(27, False, n, index, num_index)
+    chans = [(16, 32), (32, 32), (32, 64)]
+    plugs = []
+    for cin, cout in chans:
+        w = synth.kaiming_weight(r, 27, cin, cout)
+        b = (r.standard_normal(cout) * 0.1).astype(np.float32)
+        pl = deserialize_plugin("SPConvMM", data_s_spconv_mm((3, 3, 3), cin, cout, n, True, False, w, b))
+        pl.configure(torch.float16)
+        plugs.append(pl)
+    x0 = torch.randn((n, 16), device="cuda").half()
+    outs = {}
+    for enable in (False, True):
+        for pl in plugs:
+            pl.set_dependent_launch(enable)
+        for _ in range(3):  # repeated: a layer must not overwrite what its predecessor still reads
+            x = x0
+            for pl in plugs:
+                x = pl.run(x, num, table, relu=True)
+        torch.cuda.synchronize()
+        outs[enable] = x.clone()
+    assert torch.equal(outs[False], outs[True])
