@@ -119,6 +119,7 @@ class SparseNet:
         self.layers, self.device, self.dtype = layers, torch.device(device), dtype
         self.overlap_rulebooks = overlap_rulebooks
         self.side = torch.cuda.Stream(device=self.device) if overlap_rulebooks else None
+        self.side_subm = torch.cuda.Stream(device=self.device) if overlap_rulebooks else None
         self.kernel = kernel
         weights = make_weights(layers, seed)
         self.rulebooks = {}
@@ -222,21 +223,31 @@ class SparseNet:
         (out_feats, out_coors, num_act_out); every tensor is a static buffer of the net.
 
         Rulebooks and neighbour tables depend on coordinates only, never on features, so with `overlap_rulebooks`
-        the whole chain of them is enqueued on a side stream ahead of the convolutions; a layer waits for the event
-        of its own rulebook.  Inside a CUDA graph capture this becomes a second branch of the graph."""
+        the chains of them are enqueued on two side streams ahead of the convolutions; a layer waits for the event
+        of its own rulebook.  Inside a CUDA graph capture these become further branches of the graph."""
         main = torch.cuda.current_stream(self.device)
         ready = {}
         if self.overlap_rulebooks:
+            # two chains: the strided rulebooks follow each other (each creates the voxel set of the next); the SubM
+            # rulebook of a level needs only that level's coordinates, so it runs beside the next strided one.
+            # (A third stream for the strided rulebooks' neighbour tables measured no further gain.)
             self.side.wait_stream(main)
-            with torch.cuda.stream(self.side):
-                done = set()
-                for L in self.layers:
-                    if L.key not in done:
-                        done.add(L.key)
-                        self._build_rulebook(self.rulebooks[L.key])
-                        ev = torch.cuda.Event()
-                        ev.record(self.side)
-                        ready[L.key] = ev
+            self.side_subm.wait_stream(main)
+            done = set()
+            for L in self.layers:
+                if L.key in done:
+                    continue
+                done.add(L.key)
+                rb = self.rulebooks[L.key]
+                stream = self.side_subm if rb.kind == "subm" else self.side
+                with torch.cuda.stream(stream):
+                    # rb.in_set is named after the strided rulebook that wrote its coordinates ('in': the caller)
+                    if rb.kind == "subm" and rb.in_set in ready:
+                        stream.wait_event(ready[rb.in_set])
+                    self._build_rulebook(rb)
+                    ev = torch.cuda.Event()
+                    ev.record(stream)
+                    ready[L.key] = ev
         built = set()
         saved = {}
         x = feats
@@ -257,6 +268,7 @@ class SparseNet:
                 saved[L.save] = x
         if self.overlap_rulebooks:
             main.wait_stream(self.side)
+            main.wait_stream(self.side_subm)
         o = self.sets[self.out_set]
         return x, o["coors"], o["num"]
 
