@@ -279,9 +279,18 @@ def run_ours(args):
     caps = probe.calibrate(frames)
     del probe
     torch.cuda.empty_cache()
-    pipe = DetectionPipeline("centerpoint", dev, caps=caps, kernel=args.kernel)
-    pipe.load_frame(frames[0], boxes)
-    pipe.capture()
+    # `in_flight` pipelines, each with its own buffers, CUDA graph and stream, take the frames in turn: frame i+1
+    # starts (voxelisation, first rulebooks) while frame i runs its last, narrow layers -- what a serving loop over a
+    # stream of frames does with two execution contexts.  Every frame still runs the whole path.
+    n_pipes = max(1, args.in_flight)
+    pipes = []
+    for _ in range(n_pipes):
+        q = DetectionPipeline("centerpoint", dev, caps=caps, kernel=args.kernel)
+        q.load_frame(frames[0], boxes)
+        q.capture()
+        pipes.append(q)
+    pipe = pipes[0]
+    run_streams = [torch.cuda.Stream(device=dev) for _ in range(n_pipes)]
     torch.cuda.synchronize()
     dev_pts = [torch.from_numpy(f["points"]).to(dev) for f in frames]
     working_set = pipe.buffer_bytes()
@@ -292,37 +301,64 @@ def run_ours(args):
         torch.cuda.synchronize()
 
     # ---- device-resident throughput: graph replay, inputs already in HBM ------------------------------------------
-    def device_loop(n):
-        for i in range(n):
-            pipe.points.copy_(dev_pts[i % N_ROTATE], non_blocking=True)
-            pipe.replay()
+    main_stream = torch.cuda.current_stream()
 
+    def fork():
+        for st in run_streams:
+            st.wait_stream(main_stream)
+
+    def join():
+        for st in run_streams:
+            main_stream.wait_stream(st)
+
+    def device_loop(n, marks=None):
+        for i in range(n):
+            k = i % n_pipes
+            with torch.cuda.stream(run_streams[k]):
+                if marks is not None:
+                    marks.append((torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)))
+                    marks[-1][0].record(run_streams[k])
+                pipes[k].points.copy_(dev_pts[i % N_ROTATE], non_blocking=True)
+                pipes[k].replay()
+                if marks is not None:
+                    marks[-1][1].record(run_streams[k])
+
+    fork()
     device_loop(args.warmup)
+    join()
     barrier()
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
+    e0.record()  # on the launching stream; the run streams start after it and are joined before e1
+    fork()
     device_loop(args.steps)
+    join()
     e1.record()
     barrier()
     elapsed = e0.elapsed_time(e1) * 1e-3
     clocks = sampler.stop() if rank == 0 else None
+    # latency of one frame at that throughput (untimed extra pass: start and end events around every frame)
+    marks = []
+    fork()
+    device_loop(4 * n_pipes + 4, marks)
+    join()
+    torch.cuda.synchronize()
+    frame_latency_ms = float(np.median([a.elapsed_time(b) for a, b in marks[n_pipes:]]))
 
     # ---- end to end: pinned host -> device -> pipeline -> host ----------------------------------------------------
     host_pts = [torch.from_numpy(f["points"]).pin_memory() for f in frames]
     host_batch = torch.from_numpy(frames[0]["batch"]).pin_memory()
     host_scores = torch.from_numpy(boxes["scores"]).pin_memory()
     host_boxes = torch.from_numpy(boxes["boxes"]).pin_memory()
-    count_tensors = [pipe.vox_num] + [s["num"] for k, s in pipe.net.sets.items() if k != "in"]
+    count_tensors = [[q.vox_num] + [s["num"] for k, s in q.net.sets.items() if k != "in"] for q in pipes]
     h2d = host_pts[0].numel() * 4 + host_batch.numel() * 4 + host_scores.numel() * 4 + host_boxes.numel() * 4
-    d2h = host_scores.numel() * 4 + 4 * len(count_tensors)
+    d2h = host_scores.numel() * 4 + 4 * len(count_tensors[0])
     # Two frames in flight, as a serving loop would run it: the host-to-device copy of frame i+1 (copy stream, into
     # one of two staging sets) overlaps the pipeline of frame i; the host picks up the result of frame i-1 while
     # frame i runs.  Every frame still pays its own H2D, device-to-device hand-over, graph replay and D2H.
     copy_stream = torch.cuda.Stream(device=dev)
-    comp_stream = torch.cuda.current_stream()
     staging = [dict(points=torch.empty_like(pipe.points), batch=torch.empty_like(pipe.batch),
                     scores=torch.empty_like(pipe.scores), boxes=torch.empty_like(pipe.boxes)) for _ in range(2)]
     out_scores = [torch.empty_like(host_scores).pin_memory() for _ in range(2)]
@@ -341,24 +377,30 @@ def run_ours(args):
                 staging[s]["scores"].copy_(host_scores, non_blocking=True)
                 staging[s]["boxes"].copy_(host_boxes, non_blocking=True)
                 h2d_done[s].record(copy_stream)
-            comp_stream.wait_event(h2d_done[s])
-            pipe.points.copy_(staging[s]["points"], non_blocking=True)
-            pipe.batch.copy_(staging[s]["batch"], non_blocking=True)
-            pipe.scores.copy_(staging[s]["scores"], non_blocking=True)
-            pipe.boxes.copy_(staging[s]["boxes"], non_blocking=True)
-            pipe.replay()
-            out_scores[s].copy_(pipe.nms_scores, non_blocking=True)
-            for j, t in enumerate(count_tensors):
-                out_counts[s][j:j + 1].copy_(t, non_blocking=True)
-            frame_done[s].record(comp_stream)
+            q, comp_stream = pipes[s % n_pipes], run_streams[s % n_pipes]
+            with torch.cuda.stream(comp_stream):
+                comp_stream.wait_event(h2d_done[s])
+                q.points.copy_(staging[s]["points"], non_blocking=True)
+                q.batch.copy_(staging[s]["batch"], non_blocking=True)
+                q.scores.copy_(staging[s]["scores"], non_blocking=True)
+                q.boxes.copy_(staging[s]["boxes"], non_blocking=True)
+                q.replay()
+                out_scores[s].copy_(q.nms_scores, non_blocking=True)
+                for j, t in enumerate(count_tensors[s % n_pipes]):
+                    out_counts[s][j:j + 1].copy_(t, non_blocking=True)
+                frame_done[s].record(comp_stream)
         for s in range(min(n, 2)):
             frame_done[s].synchronize()
 
+    fork()
     e2e_loop(args.warmup)
+    join()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
+    fork()
     e2e_loop(args.steps)
+    join()
     f1.record()
     barrier()
     e2e_elapsed = f0.elapsed_time(f1) * 1e-3
@@ -387,6 +429,7 @@ def run_ours(args):
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
             "data": "synthetic",
             "config": {"workload": WORKLOAD, "frames_per_gpu_per_step": 1, "parallelism": "frame replicas x%d" % world,
+                       "frames_in_flight_per_gpu": n_pipes, "frame_latency_ms": frame_latency_ms,
                        "voxels": {k: int(v) for k, v in pipe.net.counts().items()},
                        "l2": "no flush: a frame rewrites %.0f MB of rulebooks/tables/activations (> 126 MB L2) and "
                              "inputs rotate over %d frames" % (working_set / 1e6, N_ROTATE),
@@ -458,6 +501,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel", type=int, default=0, help="SPConvMM kernel: 0 auto, 1 SIMT, 2 tcgen05")
+    ap.add_argument("--in-flight", type=int, default=2,
+                    help="pipelines (buffers + CUDA graph + stream each) that take the frames in turn")
     ap.add_argument("--layers", action="store_true", help="print the per-layer SPConvMM table to stderr")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
