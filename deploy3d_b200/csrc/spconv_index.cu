@@ -314,12 +314,27 @@ __global__ void conv_insert_kernel(unsigned long long* table, const int32_t* __r
   }
 }
 
+// Packed candidate list of a strided rulebook.  A forward convolution with stride s reaches an output only through
+// the taps whose offset has the right remainder modulo s, so an input has at most prod(ceil(ksize / stride)) valid
+// offsets (8 of 27 for the usual 3x3x3 / stride 2).  Instead of kvol entries per input, most of them -1, the strided
+// path then keeps kPackedSlots entries per input, ascending by offset: entry = offset << 26 | value (a hash slot,
+// later an output id; both below 2^26), -1 = unused.  Every pass over the pair table reads and writes 8 rows of it
+// instead of 27; the index tensor that comes out is the same.
+constexpr int kPackedSlots = 8;
+constexpr int kPackedShift = 26;
+constexpr int kPackedValueMask = (1 << kPackedShift) - 1;
+__device__ __forceinline__ int pack_entry(int k, int v) { return (k << kPackedShift) | v; }
+__device__ __forceinline__ int entry_offset(int e) { return e >> kPackedShift; }
+__device__ __forceinline__ int entry_value(int e) { return e & kPackedValueMask; }
+
 // 3-D specialisation for kernels of at most 3 taps per axis, same outputs.  One thread per input voxel: the output
 // coordinate of every tap is resolved once per axis (3 + 3 + 3 small computations, the only divisions), then the
 // offsets are walked with those in registers; only the combinations valid on all three axes touch the hash table.
+template <bool kPacked>
 __global__ void __launch_bounds__(kIdxThreads)
 conv_insert3_kernel(unsigned long long* table, const int32_t* __restrict__ coors, const int32_t* num_act_in,
                     int64_t n_max, Geometry g, int fan, uint32_t cap_max, int32_t* __restrict__ pair_out) {
+  constexpr bool kPacked_ = kPacked;
   const int n = live_count(num_act_in, n_max);
   const int i = blockIdx.x * kIdxThreads + threadIdx.x;
   if (i >= n) return;
@@ -336,6 +351,7 @@ conv_insert3_kernel(unsigned long long* table, const int32_t* __restrict__ coors
   }
   const uint32_t s1 = (uint32_t)g.shape[1], s2 = (uint32_t)g.shape[2], s3 = (uint32_t)g.shape[3];
   const uint32_t pair_base = (uint32_t)(i * g.kvol);
+  int filled = 0;  // packed form: entries written so far
 #pragma unroll
   for (int k0 = 0; k0 < 3; ++k0) {
 #pragma unroll
@@ -350,11 +366,18 @@ conv_insert3_kernel(unsigned long long* table, const int32_t* __restrict__ coors
             const uint32_t slot = hash_insert_min(table, mask, key, pair_base + (uint32_t)k);
             v = slot == 0xFFFFFFFFu ? -1 : (int)slot;
           }
-          pair_out[(int64_t)k * n_max + i] = v;
+          if (!kPacked_) {
+            pair_out[(int64_t)k * n_max + i] = v;
+          } else if (v >= 0 && filled < kPackedSlots) {
+            pair_out[(int64_t)filled * n_max + i] = pack_entry(k, v);
+            ++filled;
+          }
         }
       }
     }
   }
+  if (kPacked_)
+    for (; filled < kPackedSlots; ++filled) pair_out[(int64_t)filled * n_max + i] = -1;
 }
 
 // A pair "wins" its output voxel when its id is the one left in the slot.
@@ -383,9 +406,26 @@ __device__ __forceinline__ uint32_t winner_bits(const unsigned long long* __rest
   return bits;
 }
 
+// Packed form of the same test: bit j of the result = entry j of input i wins its output voxel.
+__device__ __forceinline__ uint32_t winner_bits_packed(const unsigned long long* __restrict__ table,
+                                                       const int32_t* __restrict__ pair_out, int64_t n_max, int kvol,
+                                                       int i) {
+  int e[kPackedSlots];
+  unsigned long long cur[kPackedSlots];
+#pragma unroll
+  for (int j = 0; j < kPackedSlots; ++j) e[j] = __ldg(pair_out + (int64_t)j * n_max + i);
+#pragma unroll
+  for (int j = 0; j < kPackedSlots; ++j) cur[j] = e[j] >= 0 ? __ldg(table + entry_value(e[j])) : kEmptySlot;
+  uint32_t bits = 0;
+#pragma unroll
+  for (int j = 0; j < kPackedSlots; ++j)
+    if (e[j] >= 0 && (uint32_t)cur[j] == (uint32_t)(i * kvol + entry_offset(e[j]))) bits |= 1u << j;
+  return bits;
+}
+
 __global__ void conv_count_winners_kernel(const unsigned long long* __restrict__ table,
                                           const int32_t* __restrict__ pair_out, const int32_t* num_act_in,
-                                          int64_t n_max, int kvol, int32_t* __restrict__ winners,
+                                          int64_t n_max, int kvol, bool packed, int32_t* __restrict__ winners,
                                           uint32_t* __restrict__ win_bits) {
   __shared__ int scratch[40];
   int n = live_count(num_act_in, n_max);
@@ -393,7 +433,8 @@ __global__ void conv_count_winners_kernel(const unsigned long long* __restrict__
   int cnt = 0;
   if (i < n) {
     if (kvol <= 32) {
-      const uint32_t bits = winner_bits(table, pair_out, n_max, kvol, i);
+      const uint32_t bits = packed ? winner_bits_packed(table, pair_out, n_max, kvol, i)
+                                   : winner_bits(table, pair_out, n_max, kvol, i);
       win_bits[i] = bits;  // kept for the numbering pass: it needs the same two dependent gathers per offset
       cnt = __popc(bits);
     } else
@@ -409,7 +450,7 @@ __global__ void conv_count_winners_kernel(const unsigned long long* __restrict__
 __global__ void conv_assign_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ pair_out,
                                    const int32_t* num_act_in, int64_t n_max, Geometry g,
                                    const int32_t* __restrict__ winners_base,
-                                   const uint32_t* __restrict__ win_bits, int32_t max_out,
+                                   const uint32_t* __restrict__ win_bits, int32_t max_out, bool packed,
                                    int32_t* __restrict__ slot_out, int32_t* __restrict__ out_coors) {
   __shared__ int scratch[40];
   int n = live_count(num_act_in, n_max);
@@ -430,9 +471,12 @@ __global__ void conv_assign_kernel(const unsigned long long* __restrict__ table,
   int total;
   int id = winners_base[blockIdx.x] + block_exclusive_scan(cnt, scratch, &total);
   if (i >= n || cnt == 0) return;
-  for (int k = 0; k < g.kvol; ++k) {
+  // packed: the bits and the loop run over the entries of the input (ascending by offset, so the numbering is the same)
+  const int steps = packed ? kPackedSlots : g.kvol;
+  for (int k = 0; k < steps; ++k) {
     if (small && !((bits >> k) & 1u)) continue;
     int slot = pair_out[(int64_t)k * n_max + i];
+    if (packed) slot = entry_value(slot);
     if (!small && !is_winner(table, slot, (uint32_t)(i * g.kvol + k))) continue;
     if (id < max_out) {
       slot_out[slot] = id;
@@ -472,6 +516,36 @@ conv_translate_all_kernel(int32_t* __restrict__ pair_out, const int32_t* __restr
         const unsigned hits = __ballot_sync(0xffffffffu, v[j] >= 0);
         if (lane_id() == 0 && hits) atomicAdd(&cnt[k0 + j], __popc(hits));
       }
+    }
+  }
+  __syncthreads();
+  for (int t = threadIdx.x; t < kvol; t += kIdxThreads) block_counts[(int64_t)t * nblk + blockIdx.x] = cnt[t];
+}
+
+// Packed form: entries keep their offset, the value becomes the output id (or the entry becomes -1 when the output
+// voxel fell beyond maxNumActOut); the per-(offset, input block) counts are collected with shared-memory atomics.
+__global__ void __launch_bounds__(kIdxThreads)
+conv_translate_packed_kernel(int32_t* __restrict__ pair_out, const int32_t* __restrict__ slot_out,
+                             const int32_t* num_act_in, int64_t n_max, int kvol, int32_t* __restrict__ block_counts,
+                             int nblk) {
+  __shared__ int cnt[kMaxKernelVol];
+  const int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  for (int t = threadIdx.x; t < kvol; t += kIdxThreads) cnt[t] = 0;
+  __syncthreads();
+  const int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  if (i < n) {
+    int e[kPackedSlots], id[kPackedSlots];
+#pragma unroll
+    for (int j = 0; j < kPackedSlots; ++j) e[j] = pair_out[(int64_t)j * n_max + i];
+#pragma unroll
+    for (int j = 0; j < kPackedSlots; ++j) id[j] = e[j] >= 0 ? __ldg(slot_out + entry_value(e[j])) : -1;
+#pragma unroll
+    for (int j = 0; j < kPackedSlots; ++j) {
+      if (e[j] < 0) continue;  // entries are dense from the front, but -1 is written once and stays
+      const int k = entry_offset(e[j]);
+      pair_out[(int64_t)j * n_max + i] = id[j] >= 0 ? pack_entry(k, id[j]) : -1;
+      if (id[j] >= 0) atomicAdd(&cnt[k], 1);
     }
   }
   __syncthreads();
@@ -602,6 +676,58 @@ compact_all_kernel(const int32_t* __restrict__ pair_out, const int32_t* __restri
   }
 }
 
+// compact_all_kernel for the packed pair table (kvol <= 32): the entries of an input sit in registers; for every
+// offset a ballot of the lanes that hold it gives the position inside the segment, ascending by input index.
+__global__ void __launch_bounds__(kIdxThreads)
+compact_packed_kernel(const int32_t* __restrict__ pair_out, const int32_t* __restrict__ block_prefix,
+                      const int32_t* __restrict__ seg, const int32_t* num_act_in, int64_t n_max, int nblk, int kvol,
+                      int32_t* __restrict__ index, int64_t row_len) {
+  constexpr int kWarps = kIdxThreads / 32;
+  __shared__ int warp_cnt[32][kWarps];
+  const int n = live_count(num_act_in, n_max);
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  const int i = blockIdx.x * kIdxThreads + threadIdx.x;
+  const int warp = threadIdx.x >> 5;
+  int e[kPackedSlots];
+  uint32_t kmask = 0;  // offsets this input holds
+#pragma unroll
+  for (int j = 0; j < kPackedSlots; ++j) {
+    e[j] = i < n ? __ldg(pair_out + (int64_t)j * n_max + i) : -1;
+    if (e[j] >= 0) kmask |= 1u << entry_offset(e[j]);
+  }
+  for (int k = 0; k < kvol; ++k) {
+    const unsigned hits = __ballot_sync(0xffffffffu, (kmask >> k) & 1u);
+    if (lane_id() == 0) warp_cnt[k][warp] = __popc(hits);
+  }
+  __syncthreads();
+  if (threadIdx.x < kvol) {
+    const int k = threadIdx.x;
+    int pos = seg[k] + block_prefix[(int64_t)k * nblk + blockIdx.x];
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const int c = warp_cnt[k][w];
+      warp_cnt[k][w] = pos;
+      pos += c;
+    }
+  }
+  __syncthreads();
+  for (int k = 0; k < kvol; ++k) {
+    const bool has = (kmask >> k) & 1u;
+    const unsigned hits = __ballot_sync(0xffffffffu, has);
+    if (!has) continue;
+    int v = -1;
+#pragma unroll
+    for (int j = 0; j < kPackedSlots; ++j)
+      if (e[j] >= 0 && entry_offset(e[j]) == k) v = entry_value(e[j]);
+    const int64_t pos = (int64_t)warp_cnt[k][warp] + __popc(hits & lanemask_lt());
+    if (pos < row_len) {
+      index[pos] = i;
+      index[row_len + pos] = v;
+      index[2 * row_len + pos] = k;
+    }
+  }
+}
+
 // Everything that is not a pair is -1: the unused tail of each 128-aligned segment and the rows beyond
 // numIndex (the reference memsets the three rows beforehand, trt/spconv/index.cu:352-354).
 __global__ void fill_padding_kernel(const int32_t* __restrict__ seg, int kvol, int32_t* __restrict__ index,
@@ -658,6 +784,7 @@ struct Plan {
   int32_t* slot_out;
   int32_t* winners;
   uint32_t* win_bits;  // per input: which of its offsets won an output voxel (kvol <= 32)
+  bool packed;         // strided rulebook kept as kPackedSlots entries per input instead of kvol
   size_t bytes;
 };
 
@@ -678,7 +805,11 @@ int make_plan(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n
     D3D_REQUIRE(p->kernel_size[d] >= 1 && p->stride[d] >= 1 && p->dilation[d] >= 1, D3D_ERR_INVALID_ARGUMENT);
     g.ksize[d] = p->kernel_size[d], g.stride[d] = p->stride[d], g.pad[d] = p->padding[d], g.dil[d] = p->dilation[d];
     g.kvol *= g.ksize[d];
-    fan *= g.transpose ? g.ksize[d] : (g.ksize[d] + g.stride[d] - 1) / g.stride[d];
+    // taps that can reach an output from one input: those with the right remainder modulo the stride; when the
+    // dilation shares a factor with the stride the remainders repeat sooner, so every tap is counted then
+    int common = g.stride[d], rest = g.dil[d] % g.stride[d];
+    while (rest) { const int t = common % rest; common = rest, rest = t; }  // gcd(stride, dilation)
+    fan *= (g.transpose || common != 1) ? g.ksize[d] : (g.ksize[d] + g.stride[d] - 1) / g.stride[d];
   }
   D3D_REQUIRE(g.kvol <= kMaxKernelVol, D3D_ERR_TOO_LARGE);
   g.klast = g.ksize[ndim - 1];
@@ -715,6 +846,9 @@ int make_plan(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n
   plan->slot_out = p->subm ? nullptr : w.take<int32_t>(plan->cap_max);
   plan->winners = p->subm ? nullptr : w.take<int32_t>((size_t)plan->nblk + 1);
   plan->win_bits = p->subm ? nullptr : w.take<uint32_t>((size_t)(plan->n_max > 0 ? plan->n_max : 1));
+  plan->packed = !p->subm && !g.transpose && ndim == 3 && g.ksize[0] <= 3 && g.ksize[1] <= 3 && g.ksize[2] <= 3 &&
+                 fan <= kPackedSlots && g.kvol > kPackedSlots /* the pair table has kvol rows */ && plan->cap_max <= (1u << kPackedShift) &&
+                 p->max_num_act_out <= (1 << kPackedShift);
   plan->bytes = w.off;
   return D3D_OK;
 }
@@ -830,23 +964,33 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
     int32_t* num_act_out = reinterpret_cast<int32_t*>(outputs[3]);
     D3D_REQUIRE(out_coors && num_act_out, D3D_ERR_INVALID_ARGUMENT);
     D3D_REQUIRE(out[2].dims[0] >= p->max_num_act_out, D3D_ERR_INVALID_ARGUMENT);
-    if (g.ndim == 3 && g.ksize[0] <= 3 && g.ksize[1] <= 3 && g.ksize[2] <= 3)
-      conv_insert3_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.fan,
-                                                        plan.cap_max, plan.pair_out);
+    if (plan.packed)
+      conv_insert3_kernel<true><<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.fan,
+                                                              plan.cap_max, plan.pair_out);
+    else if (g.ndim == 3 && g.ksize[0] <= 3 && g.ksize[1] <= 3 && g.ksize[2] <= 3)
+      conv_insert3_kernel<false><<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.fan,
+                                                               plan.cap_max, plan.pair_out);
     else
       conv_insert_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
                                                                      plan.fan, plan.cap_max, plan.pair_out);
     conv_count_winners_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g.kvol,
-                                                            plan.winners, plan.win_bits);
+                                                            plan.packed, plan.winners, plan.win_bits);
     scan_totals_kernel<<<1, 1024, 0, st>>>(plan.winners, nblk, p->max_num_act_out, num_act_out);
     conv_assign_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g, plan.winners,
                                                      plan.win_bits,
-                                                     p->max_num_act_out, plan.slot_out, out_coors);
-    conv_translate_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max, g.kvol,
-                                                            plan.block_counts, nblk);
+                                                     p->max_num_act_out, plan.packed, plan.slot_out, out_coors);
+    if (plan.packed)
+      conv_translate_packed_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max,
+                                                                 g.kvol, plan.block_counts, nblk);
+    else
+      conv_translate_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max, g.kvol,
+                                                              plan.block_counts, nblk);
   }
   segment_scan_kernel<<<1, 1024, 0, st>>>(plan.block_counts, nblk, g.kvol, num_act_in, n_max, plan.seg, num_index);
-  if (g.kvol <= kCompactAllMaxVol)
+  if (!p->subm && plan.packed)
+    compact_packed_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in, n_max,
+                                                        nblk, g.kvol, index, plan.row_len);
+  else if (g.kvol <= kCompactAllMaxVol)
     compact_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in, n_max,
                                                      nblk, g.kvol, index, plan.row_len);
   else

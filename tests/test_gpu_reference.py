@@ -46,6 +46,10 @@ CASES = [
      7077, 200000),
     ("strided_3x1x1", (3, 1, 1), (2, 1, 1), (0, 0, 0), (1, 1, 1), (0, 0, 0), False, False, [2, 5, 60, 50], 6000, 6077,
      200000),
+    ("strided_222_dilated_2", (3, 3, 3), (2, 2, 2), (2, 2, 2), (2, 2, 2), (0, 0, 0), False, False, [1, 20, 20, 12], 3000,
+     3077, 200000),
+    ("strided_212", (3, 3, 3), (2, 1, 2), (1, 1, 1), (1, 1, 1), (0, 0, 0), False, False, [2, 20, 14, 12], 4000, 4077,
+     200000),
     ("transposed_222", (3, 3, 3), (2, 2, 2), (1, 1, 1), (1, 1, 1), (1, 1, 1), True, False, [2, 20, 24, 10], 3000, 3077,
      200000),
     ("transposed_k2", (2, 2, 2), (2, 2, 2), (0, 0, 0), (1, 1, 1), (0, 0, 0), True, False, [1, 16, 16, 16], 1000, 1077,

@@ -131,6 +131,9 @@ EXTRA = [
     ((3, 3), (1, 1), (1, 1), (1, 1), (0, 0), False, True, [3, 100, 90], 8000),
     ((3,), (2,), (1,), (1,), (0,), False, False, [4, 3000], 4000),
     ((3, 3, 3, 3), (1, 1, 1, 1), (1, 1, 1, 1), (1, 1, 1, 1), (0, 0, 0, 0), False, True, [1, 8, 8, 8, 8], 1500),
+    # dilation and stride share a factor: an even coordinate reaches an output through all three taps of an axis
+    ((3, 3, 3), (2, 2, 2), (2, 2, 2), (2, 2, 2), (0, 0, 0), False, False, [1, 20, 20, 12], 3000),
+    ((3, 3, 3), (2, 1, 2), (1, 1, 1), (1, 1, 1), (0, 0, 0), False, False, [2, 20, 14, 12], 4000),
 ]
 
 
