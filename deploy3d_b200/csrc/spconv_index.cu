@@ -688,12 +688,15 @@ compact_packed_kernel(const int32_t* __restrict__ pair_out, const int32_t* __res
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
   const int i = blockIdx.x * kIdxThreads + threadIdx.x;
   const int warp = threadIdx.x >> 5;
-  int e[kPackedSlots];
-  uint32_t kmask = 0;  // offsets this input holds
+  __shared__ int value_of[32][kIdxThreads];  // [offset][thread]: the output id this input pairs with at that offset
+  uint32_t kmask = 0;                        // offsets this input holds
 #pragma unroll
   for (int j = 0; j < kPackedSlots; ++j) {
-    e[j] = i < n ? __ldg(pair_out + (int64_t)j * n_max + i) : -1;
-    if (e[j] >= 0) kmask |= 1u << entry_offset(e[j]);
+    const int e = i < n ? __ldg(pair_out + (int64_t)j * n_max + i) : -1;
+    if (e >= 0) {
+      kmask |= 1u << entry_offset(e);
+      value_of[entry_offset(e)][threadIdx.x] = entry_value(e);
+    }
   }
   for (int k = 0; k < kvol; ++k) {
     const unsigned hits = __ballot_sync(0xffffffffu, (kmask >> k) & 1u);
@@ -715,10 +718,7 @@ compact_packed_kernel(const int32_t* __restrict__ pair_out, const int32_t* __res
     const bool has = (kmask >> k) & 1u;
     const unsigned hits = __ballot_sync(0xffffffffu, has);
     if (!has) continue;
-    int v = -1;
-#pragma unroll
-    for (int j = 0; j < kPackedSlots; ++j)
-      if (e[j] >= 0 && entry_offset(e[j]) == k) v = entry_value(e[j]);
+    const int v = value_of[k][threadIdx.x];  // written by this thread above
     const int64_t pos = (int64_t)warp_cnt[k][warp] + __popc(hits & lanemask_lt());
     if (pos < row_len) {
       index[pos] = i;
