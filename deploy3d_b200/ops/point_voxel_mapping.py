@@ -16,7 +16,8 @@ def scatter_to(batch_point_feats, scatter_to, scatter_count, reduce_type):
 
 def data_s_gather_back(fill_val=None):
     data = np.array([fill_val is not None], dtype=np.bool_).tobytes()
-    data += np.array([0.0 if fill_val is None else fill_val], dtype=np.float32).tobytes()
+    # without a fill value the exporter serialises None as float32, i.e. NaN; the flag byte is what counts
+    data += np.array([np.nan if fill_val is None else fill_val], dtype=np.float32).tobytes()
     return data
 
 

@@ -1,0 +1,67 @@
+"""Generates tests/golden/plugin_blobs.npz: the `data_s` blobs (and plugin name, version, number of outputs) that the
+REFERENCE's own exporter writes, obtained by calling the `symbolic()` of every autograd Function under
+deploy3d/symfun/ops with a recording stand-in for the ONNX graph.  Run where the reference checkout exists:
+
+    python tests/golden/make_golden_blobs.py [/path/to/reference]
+
+The reference's code predates numpy 1.24 (`np.bool`); the alias is restored for this script only.  The parameter
+sets are listed in CASES so that the test can rebuild the same blobs with deploy3d_b200.ops.data_s_*."""
+import os
+import sys
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+W = (np.arange(27 * 4 * 8, dtype=np.float32).reshape(27, 4, 8) / 100.0 - 3.0)
+B = np.linspace(-1, 1, 8, dtype=np.float32)
+CASES = [
+    # (key, op class name, positional parameters after the tensor inputs)
+    ("index_subm", "SPConvIdx3d", ((3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), (0, 0, 0), 20000, True, False)),
+    ("index_down", "SPConvIdx3d", ((3, 3, 3), (2, 2, 1), (1, 1, 1), (1, 1, 1), (0, 0, 0), 50000, False, False)),
+    ("index_up", "SPConvIdx3d", ((3, 1, 3), (2, 1, 2), (1, 0, 1), (1, 2, 1), (0, 1, 0), 4321, False, True)),
+    ("mm_bias", "SPConvMM", ((3, 3, 3), 4, 8, 1234, True, False, W, B)),
+    ("mm_nobias_inverse", "SPConvMM", ((3, 3, 3), 4, 8, 99, False, True, W, None)),
+    ("densify", "BEVDensify", (256,)),
+    ("mean", "SimpleMeanEncoder", (60000,)),
+    ("cylinder", "CylinderEncoder", (120000,)),
+    ("scatter_max", "ScatterTo", (0,)),
+    ("scatter_mean", "ScatterTo", (1,)),
+    ("gather_fill", "GatherBack", (6.9,)),
+    ("gather_keep", "GatherBack", (None,)),
+    ("nms", "NMS3d", ()),
+    ("decode", "YoloX3dDecode", (8, (0, 3, 7), 500)),
+]
+N_TENSOR_INPUTS = {"SPConvIdx3d": 3, "SPConvMM": 5, "BEVDensify": 4, "SimpleMeanEncoder": 4, "CylinderEncoder": 4,
+                   "ScatterTo": 3, "GatherBack": 2, "NMS3d": 2, "YoloX3dDecode": 3}
+
+
+class RecordingGraph:
+    """Stands in for torch._C.Graph: keeps the attributes of the one node a symbolic() emits."""
+
+    def op(self, kind, *inputs, **attrs):
+        self.kind, self.n_inputs, self.attrs = kind, len(inputs), attrs
+        return None
+
+
+def main():
+    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    np.bool = np.bool_  # removed from numpy; the reference's exporter still spells it this way
+    sys.path.insert(0, ref)
+    import deploy3d.symfun.ops as ops
+    out = {}
+    for key, cls, params in CASES:
+        g = RecordingGraph()
+        getattr(ops, cls).symbolic(g, *([None] * N_TENSOR_INPUTS[cls]), *params)
+        assert g.kind == "TRT_PluginV2" and g.n_inputs == N_TENSOR_INPUTS[cls]
+        out[key + "_data"] = np.frombuffer(g.attrs["data_s"], dtype=np.uint8).copy()
+        out[key + "_name"] = np.frombuffer(g.attrs["name_s"], dtype=np.uint8).copy()
+        out[key + "_version"] = np.frombuffer(g.attrs["version_s"], dtype=np.uint8).copy()
+        out[key + "_outputs"] = np.int64(g.attrs["outputs"])
+    path = os.path.join(HERE, "plugin_blobs.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, os.path.getsize(path), "bytes")
+
+
+if __name__ == "__main__":
+    main()

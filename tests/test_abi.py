@@ -124,3 +124,53 @@ def test_ops_refuse_cpu_tensors(d3d):
     import torch
     with pytest.raises(RuntimeError):
         d3d.nms3d(torch.zeros(1, 4), torch.zeros(1, 4, 7))
+
+
+def test_blobs_match_the_reference_exporter(d3d):
+    """tests/golden/plugin_blobs.npz holds the `data_s` the reference's own exporter writes (the symbolic() of every
+    op under deploy3d/symfun/ops, recorded by tests/golden/make_golden_blobs.py).  The blob builders of this package
+    must produce the same bytes for the same parameters, and the plugin objects must accept the reference's bytes and
+    report the exporter's number of outputs."""
+    import importlib.util
+    import os
+    import numpy as np
+    from deploy3d_b200 import ops
+    from deploy3d_b200.plugins import deserialize_plugin
+    here = os.path.join(os.path.dirname(__file__), "golden")
+    spec = importlib.util.spec_from_file_location("make_golden_blobs", os.path.join(here, "make_golden_blobs.py"))
+    gen = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(gen)
+    g = np.load(os.path.join(here, "plugin_blobs.npz"))
+    build = {"SPConvIdx3d": ops.data_s_spconv_index, "SPConvMM": ops.data_s_spconv_mm,
+             "BEVDensify": ops.data_s_bev_densify, "SimpleMeanEncoder": ops.data_s_voxel_encoder,
+             "CylinderEncoder": ops.data_s_voxel_encoder, "ScatterTo": ops.data_s_scatter_to,
+             "GatherBack": ops.data_s_gather_back, "NMS3d": lambda: b"", "YoloX3dDecode": ops.data_s_yolox3d_decode}
+    for key, cls, params in gen.CASES:
+        want = bytes(g[key + "_data"])
+        assert bytes(g[key + "_name"]).decode() == cls and bytes(g[key + "_version"]) == b"2.0"
+        got = bytes(build[cls](*params))
+        assert got == want, "%s: blob differs from the reference exporter's" % key
+        plug = deserialize_plugin(cls, want)
+        import torch
+        from deploy3d_b200.plugins import _desc_of
+        f32, i32 = torch.float32, torch.int32
+        inputs = {  # shapes of the reference's plugin inputs (CPU tensors: only descriptors are taken)
+            "SPConvIdx3d": [torch.empty((100, 4), dtype=i32), torch.empty(1, dtype=i32),
+                            torch.empty((2, 0, 8, 16, 16), dtype=i32)],
+            "SPConvMM": [torch.empty((100, 4), dtype=torch.float16), torch.empty(1, dtype=i32),
+                         torch.empty(1, dtype=i32), torch.empty((3, 27 * 228), dtype=i32), torch.empty(1, dtype=i32)],
+            "BEVDensify": [torch.empty((100, 128), dtype=f32), torch.empty((100, 4), dtype=i32),
+                           torch.empty(1, dtype=i32), torch.empty((2, 0, 2, 16, 16), dtype=i32)],
+            "SimpleMeanEncoder": [torch.empty((500, 4), dtype=f32), torch.empty(500, dtype=i32),
+                                  torch.empty(6, dtype=f32), torch.empty((2, 0, 8, 16, 16), dtype=i32)],
+            "CylinderEncoder": [torch.empty((500, 4), dtype=f32), torch.empty(500, dtype=i32),
+                                torch.empty(6, dtype=f32), torch.empty((2, 0, 48, 36, 8), dtype=i32)],
+            "ScatterTo": [torch.empty((500, 9), dtype=f32), torch.empty(500, dtype=i32), torch.empty(64, dtype=i32)],
+            "GatherBack": [torch.empty((64, 9), dtype=f32), torch.empty(500, dtype=i32)],
+            "NMS3d": [torch.empty((2, 50), dtype=f32), torch.empty((2, 50, 7), dtype=f32)],
+            "YoloX3dDecode": [torch.empty((2, 3, 32, 32), dtype=f32), torch.empty((2, 9, 32, 32), dtype=f32),
+                              torch.empty(6, dtype=f32)],
+        }[cls]
+        n_out = len(plug.output_descs([_desc_of(t) for t in inputs]))
+        assert n_out == int(g[key + "_outputs"]), "%s: %d outputs, the exporter declares %d" % (
+            key, n_out, int(g[key + "_outputs"]))
