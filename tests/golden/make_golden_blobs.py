@@ -1,6 +1,7 @@
 """Generates tests/golden/plugin_blobs.npz: the `data_s` blobs (and plugin name, version, number of outputs) that the
 REFERENCE's own exporter writes, obtained by calling the `symbolic()` of every autograd Function under
-deploy3d/symfun/ops with a recording stand-in for the ONNX graph.  Run where the reference checkout exists:
+deploy3d/symfun/ops with a recording stand-in for the ONNX graph, and the output shapes / dtypes its shape-only
+`forward()` allocates for fixed input shapes.  Run where the reference checkout exists:
 
     python tests/golden/make_golden_blobs.py [/path/to/reference]
 
@@ -32,8 +33,24 @@ CASES = [
     ("nms", "NMS3d", ()),
     ("decode", "YoloX3dDecode", (8, (0, 3, 7), 500)),
 ]
-N_TENSOR_INPUTS = {"SPConvIdx3d": 3, "SPConvMM": 5, "BEVDensify": 4, "SimpleMeanEncoder": 4, "CylinderEncoder": 4,
-                   "ScatterTo": 3, "GatherBack": 2, "NMS3d": 2, "YoloX3dDecode": 3}
+# tensor inputs of every op: (shape, dtype name); zero-element tensors carry spatial shapes, as in the reference
+INPUTS = {
+    "SPConvIdx3d": [((100, 4), "int32"), ((1,), "int32"), ((2, 0, 8, 16, 16), "int32")],
+    "SPConvMM": [((100, 4), "float16"), ((1,), "int32"), ((1,), "int32"), ((3, 27 * 228), "int32"), ((1,), "int32")],
+    "BEVDensify": [((100, 128), "float32"), ((100, 4), "int32"), ((1,), "int32"), ((2, 0, 2, 16, 16), "int32")],
+    "SimpleMeanEncoder": [((500, 4), "float32"), ((500,), "int32"), ((6,), "float32"), ((2, 0, 8, 16, 16), "int32")],
+    "CylinderEncoder": [((500, 4), "float32"), ((500,), "int32"), ((6,), "float32"), ((2, 0, 48, 36, 8), "int32")],
+    "ScatterTo": [((500, 9), "float32"), ((500,), "int32"), ((64,), "int32")],
+    "GatherBack": [((64, 9), "float32"), ((500,), "int32")],
+    "NMS3d": [((2, 50), "float32"), ((2, 50, 7), "float32")],
+    "YoloX3dDecode": [((2, 3, 32, 32), "float32"), ((2, 9, 32, 32), "float32"), ((6,), "float32")],
+}
+N_TENSOR_INPUTS = {k: len(v) for k, v in INPUTS.items()}
+
+
+def make_inputs(cls):
+    import torch
+    return [torch.zeros(shape, dtype=getattr(torch, dt)) for shape, dt in INPUTS[cls]]
 
 
 class RecordingGraph:
@@ -58,6 +75,13 @@ def main():
         out[key + "_name"] = np.frombuffer(g.attrs["name_s"], dtype=np.uint8).copy()
         out[key + "_version"] = np.frombuffer(g.attrs["version_s"], dtype=np.uint8).copy()
         out[key + "_outputs"] = np.int64(g.attrs["outputs"])
+        # forward() of the reference's Function only allocates outputs of the right shape and dtype: record them
+        res = getattr(ops, cls).forward(None, *make_inputs(cls), *params)
+        res = res if isinstance(res, (tuple, list)) else (res,)
+        assert len(res) == int(g.attrs["outputs"])
+        for oi, t in enumerate(res):
+            out["%s_out%d_shape" % (key, oi)] = np.array(list(t.shape), dtype=np.int64)
+            out["%s_out%d_dtype" % (key, oi)] = np.frombuffer(str(t.dtype).encode(), dtype=np.uint8).copy()
     path = os.path.join(HERE, "plugin_blobs.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, os.path.getsize(path), "bytes")

@@ -152,25 +152,16 @@ def test_blobs_match_the_reference_exporter(d3d):
         assert got == want, "%s: blob differs from the reference exporter's" % key
         plug = deserialize_plugin(cls, want)
         import torch
-        from deploy3d_b200.plugins import _desc_of
-        f32, i32 = torch.float32, torch.int32
-        inputs = {  # shapes of the reference's plugin inputs (CPU tensors: only descriptors are taken)
-            "SPConvIdx3d": [torch.empty((100, 4), dtype=i32), torch.empty(1, dtype=i32),
-                            torch.empty((2, 0, 8, 16, 16), dtype=i32)],
-            "SPConvMM": [torch.empty((100, 4), dtype=torch.float16), torch.empty(1, dtype=i32),
-                         torch.empty(1, dtype=i32), torch.empty((3, 27 * 228), dtype=i32), torch.empty(1, dtype=i32)],
-            "BEVDensify": [torch.empty((100, 128), dtype=f32), torch.empty((100, 4), dtype=i32),
-                           torch.empty(1, dtype=i32), torch.empty((2, 0, 2, 16, 16), dtype=i32)],
-            "SimpleMeanEncoder": [torch.empty((500, 4), dtype=f32), torch.empty(500, dtype=i32),
-                                  torch.empty(6, dtype=f32), torch.empty((2, 0, 8, 16, 16), dtype=i32)],
-            "CylinderEncoder": [torch.empty((500, 4), dtype=f32), torch.empty(500, dtype=i32),
-                                torch.empty(6, dtype=f32), torch.empty((2, 0, 48, 36, 8), dtype=i32)],
-            "ScatterTo": [torch.empty((500, 9), dtype=f32), torch.empty(500, dtype=i32), torch.empty(64, dtype=i32)],
-            "GatherBack": [torch.empty((64, 9), dtype=f32), torch.empty(500, dtype=i32)],
-            "NMS3d": [torch.empty((2, 50), dtype=f32), torch.empty((2, 50, 7), dtype=f32)],
-            "YoloX3dDecode": [torch.empty((2, 3, 32, 32), dtype=f32), torch.empty((2, 9, 32, 32), dtype=f32),
-                              torch.empty(6, dtype=f32)],
-        }[cls]
-        n_out = len(plug.output_descs([_desc_of(t) for t in inputs]))
+        from deploy3d_b200.plugins import _D3D2TORCH, _desc_of
+        inputs = gen.make_inputs(cls)  # CPU tensors: only their descriptors are taken
+        descs = plug.output_descs([_desc_of(t) for t in inputs])
+        n_out = len(descs)
         assert n_out == int(g[key + "_outputs"]), "%s: %d outputs, the exporter declares %d" % (
             key, n_out, int(g[key + "_outputs"]))
+        # shapes and dtypes the reference's shape-only forward() allocates for the same inputs
+        for oi, d in enumerate(descs):
+            want_shape = [int(v) for v in g["%s_out%d_shape" % (key, oi)]]
+            want_dtype = bytes(g["%s_out%d_dtype" % (key, oi)]).decode()
+            assert list(d.dims[:d.nb_dims]) == want_shape, "%s output %d: %s vs %s" % (
+                key, oi, list(d.dims[:d.nb_dims]), want_shape)
+            assert str(_D3D2TORCH[d.dtype]) == want_dtype, "%s output %d: dtype" % (key, oi)
