@@ -178,7 +178,7 @@ __global__ void subm_probe_kernel(const unsigned long long* __restrict__ table, 
 // kPlane3x3: the two trailing kernel extents are 3 x 3 (the usual case); the nine probes of a leading tap are
 // then issued together.
 template <bool kPlane3x3>
-__global__ void __launch_bounds__(kIdxThreads)
+__global__ void __launch_bounds__(kIdxThreads, 4)
 subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ coors,
                    const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
                    int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk) {
