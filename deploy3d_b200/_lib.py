@@ -86,6 +86,7 @@ SIGNATURES = {
     "d3d_version": (ctypes.c_char_p, []),
     "d3d_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "d3d_debug_take_kernel_error": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "d3d_debug_set_tc_plan": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "d3d_spconv_index_parse": (ctypes.c_int, [ctypes.c_int, _vp, _sz, ctypes.POINTER(SpconvIndexParams)]),
     "d3d_spconv_index_num_outputs": (ctypes.c_int, [ctypes.POINTER(SpconvIndexParams)]),
     "d3d_spconv_index_output_desc": (ctypes.c_int, [ctypes.POINTER(SpconvIndexParams), _descp, ctypes.c_int,

@@ -340,6 +340,11 @@ extern "C" int d3d_spconv_mm_configure(d3d_spconv_mm_t h, int dtype) {
     release_device(h);
     return D3D_ERR_CUDA;
   }
+  rc = spconv_mm_tc_prepare(h, dtype);  // tensor map over the transposed weights (nothing for fp32 / odd channels)
+  if (rc != D3D_OK) {
+    release_device(h);
+    return rc;
+  }
   h->dtype = dtype;
   h->device = dev;
   return D3D_OK;
@@ -440,9 +445,12 @@ extern "C" int d3d_spconv_mm_enqueue(d3d_spconv_mm_t h, const d3d_tensor_desc* i
               D3D_ERR_INVALID_ARGUMENT);
   size_t need = d3d_spconv_mm_table_bytes(h->p.kernel_vol, h->p.max_num_act_out);
   D3D_REQUIRE(h->p.max_num_act_out == 0 || (workspace && workspace_bytes >= need), D3D_ERR_WORKSPACE_TOO_SMALL);
-  int rc = d3d_spconv_mm_configure(h, dtype);  // no-op when already configured for this dtype
-  if (rc != D3D_OK) return rc;
-  rc = d3d_spconv_mm_prepare(h->p.kernel_vol, h->p.inverse, h->p.max_num_act_out,
+  // configurePlugin (d3d_spconv_mm_configure) uploads the weights; enqueue itself allocates nothing and copies
+  // nothing from the host (the reference uploads in configurePlugin too, trt/spconv/mm_trt.cu:127-142)
+  int dev = -1;
+  D3D_REQUIRE(cudaGetDevice(&dev) == cudaSuccess, D3D_ERR_CUDA);
+  D3D_REQUIRE(h->dtype == dtype && h->device == dev, D3D_ERR_INVALID_ARGUMENT);
+  int rc = d3d_spconv_mm_prepare(h->p.kernel_vol, h->p.inverse, h->p.max_num_act_out,
                              reinterpret_cast<const int32_t*>(inputs[3]), in[3].dims[1],
                              reinterpret_cast<const int32_t*>(inputs[4]), workspace, stream);
   if (rc != D3D_OK) return rc;

@@ -17,7 +17,7 @@ struct d3d_spconv_mm_s {
   float* b_dev = nullptr;    // bias in fp32 (zeros when the blob has no bias)
   int kernel_choice = 0;     // 0 auto, 1 SIMT, 2 tcgen05
   int dependent_launch = 0;  // tcgen05 path: launch with the programmatic stream-serialisation attribute
-  void* tc_state = nullptr;  // tensor maps of the tcgen05 path (owned by spconv_mm_tc.cu)
+  void* tc_state = nullptr;  // tensor map of the tcgen05 path (owned by spconv_mm_tc.cu, created by configure)
 };
 
 namespace d3d {
@@ -45,6 +45,8 @@ int launch_spconv_mm_simt(const MmLaunch& a);
 // Returns D3D_ERR_INVALID_ARGUMENT when the shape/dtype is not eligible for the tensor-core path.
 bool spconv_mm_tc_eligible(const d3d_spconv_mm_s* h, int dtype);
 int launch_spconv_mm_tc(const MmLaunch& a);
+// Per-handle state of the tensor-core path: created while configuring (device weights exist), freed with them.
+int spconv_mm_tc_prepare(d3d_spconv_mm_s* h, int dtype);
 void spconv_mm_tc_release(d3d_spconv_mm_s* h);
 
 }  // namespace d3d

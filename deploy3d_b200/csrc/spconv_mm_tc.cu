@@ -14,21 +14,42 @@
 // swizzled layout.  A TMA tile::gather4 producer was measured on B200 at about 11 ns per gathered row whatever the
 // row width (a request-rate limit), 2-3x slower than cp.async for these row sizes, and is not used.
 //
-// What bounds the kernel is shared-memory bandwidth (every A block is written once and read once by the tensor
-// core, 128 B/clk per SM) and, for a single issuing thread, the scalar instructions between two tcgen05.mma; the
-// roles below therefore keep their inner loops to a handful of instructions per copy / per MMA:
-//   8 (4) producer warps  thread t owns piece t % P of rows t / P + i * (threads / P) of every block (P = 16-byte
-//                      pieces per row), so its shared-memory offsets are constants; ids come from the tile's id buffer
-//   1 MMA warp         one lane issues tcgen05.mma from precomputed descriptor words; owns the TMEM allocation
-//   1 control warp     prefetches the neighbour ids of the next tile (one bulk copy) and loads B by TMA
+// What bounds this kernel, measured on B200 (profiles/spconv_mm_tc_role_cycles.md):
+//   * the instruction streams of its roles.  The kernel ran no faster with every MMA predicated off, nor with every
+//     copy and id load removed.  One warp that waits for a stage, fences and issues eight M128 K16 MMAs needs about
+//     750 cycles for what the tensor core executes in 320 to 512; two such warps on one SM keep it busy.  A lone
+//     warp issues a dependent instruction every four cycles or so, so what a role executes per stage besides its
+//     copies / MMAs (walking the stage sequence, waits, address arithmetic) costs as much as the work itself.
+//   * for layers of 64 channels and more, the shared-memory data pipe (128 B per clock and SM): every A block is
+//     written once by cp.async and read once by the tensor core, every B block likewise unless it is resident, so
+//     a 64 -> 64 offset block moves 24 KB in and about 19 KB out in the 192 cycles its four MMAs need.
+// Hence:
+//   * layers run TWO CTAs per SM wherever shared and tensor memory allow (two independent issue streams);
+//   * the MMA warp keeps every value that feeds an MMA warp-uniform in a way the compiler can see (offset masks
+//     pass through a shuffle from lane 0), computes all descriptors of a stage first and lets the lane chosen by
+//     elect.sync issue the MMAs as straight-line code; it probes the following stage's barrier before it issues;
+//   * the neighbour ids are read from global memory by the producer lanes themselves, a stage ahead (and the
+//     table lines of the next tile are prefetched into L2), not staged in shared memory: that memory is a third
+//     pipeline stage instead;
+//   * the producer warps work in teams of four that take the stages in turn, so that the per-stage overhead of a
+//     warp is paid once per two stages of the pipeline; address arithmetic of all copies of a stage comes first,
+//     the copies follow as independent instruction groups; a zero fill uses the ignore-src form of cp.async;
+//   * every role loads the offset mask of its next tile while it works on the current one;
+//   * the epilogue handles 16 columns per tensor-memory load, which keeps the kernel at 61-72 registers (two
+//     CTAs of 448 threads per SM).
+// Roles of a CTA, for W = 4 or 8 producer warps:
+//   W producer warps   teams of four; warp q of a team copies rows [32q, 32q + 32) of every A block of the team's
+//                      stages: lane = (row, 16-byte piece), so its shared-memory offsets are constants
+//   1 MMA warp         waits for a stage, one elected lane issues its tcgen05.mma and commits; owns the TMEM allocation
+//   1 control warp     one lane loads B by TMA (all offsets once when they fit, else per stage)
 //   4 epilogue warps   TMEM -> registers -> global
-// Layers of at most 64 input channels run TWO such CTAs per SM (4 producer warps and half the shared memory each):
-// their bound is the serial fill -> issue -> commit chain of a tile, not a hardware unit, and two independent
-// chains per SM overlap each other's hand-over time (measured: 18-24 % faster at 16 / 32 / 64 channels).
 // Every role derives the stage sequence of a tile from the tile's offset mask (built with the neighbour table), so
 // no per-stage metadata is exchanged.  Stages and accumulators are handed over through mbarriers; every wait is
 // bounded (about one second) and on expiry raises an error word, lets the CTA drain and return instead of spinning.
 #include <cuda.h>
+
+#include <mutex>
+#include <new>
 
 #include "common.cuh"
 #include "spconv_mm_internal.h"
@@ -40,14 +61,24 @@ constexpr int kTileRows = 128;
 constexpr int kMaxStages = 8;
 constexpr int kNumAcc = 2;
 constexpr int kMaxGroup = 8;  // kernel offsets that may share one pipeline stage
-// Warp roles, for kProd producer threads (256: one CTA per SM; 128: two CTAs per SM, each with half the shared
-// memory, which gives small layers two independent producer -> MMA -> epilogue chains per SM): producers first, then
-// the MMA warp, the control warp and four epilogue warps (whose index mod 4 covers the four TMEM lane quarters).
-__host__ __device__ constexpr int mma_warp_of(int prod) { return prod / 32; }
-__host__ __device__ constexpr int threads_of(int prod) { return prod + 6 * 32; }
+// Warp roles for W producer warps: producers first, then the MMA warp, the control warp and four epilogue warps
+// (whose index mod 4 covers the four TMEM lane quarters).
+__host__ __device__ constexpr int threads_of(int prod_warps) { return (prod_warps + 6) * 32; }
 constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
 __device__ int g_tc_error;  // 0 ok; otherwise the code of the first wait that gave up
+
+// Cycle accounting per role (CTA 0 only), compiled in with -DD3D_TC_PROFILE for tuning builds.
+#ifdef D3D_TC_PROFILE
+__device__ long long g_prof[3][8];
+#define PROF_DECL long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tprev_ = clock64();
+#define PROF(x) do { long long n_ = clock64(); prof_[x] += n_ - tprev_; tprev_ = n_; } while (0)
+#define PROF_STORE(role, cond) if (blockIdx.x == 0 && (cond)) for (int i_ = 0; i_ < 8; ++i_) g_prof[role][i_] = prof_[i_];
+#else
+#define PROF_DECL
+#define PROF(x)
+#define PROF_STORE(role, cond)
+#endif
 
 struct TcParams {
   const int32_t* table;        // [tiles][kvol][128]
@@ -58,9 +89,7 @@ struct TcParams {
   int kvol, cin, cout;
   int num_tiles;
   int stages;
-  int group;                  // kernel offsets per stage (> 1 only when kparts == 1)
-  uint32_t a_bytes, b_bytes;  // per (offset, K part) block, each a multiple of 1024
-  uint32_t idx_bytes;         // kvol * 512: neighbour ids of one tile
+  uint32_t a_bytes, b_bytes;  // per (offset, K part) block
   int row_bytes;              // bytes of one smem row = min(cin, 64) * 2
   int kchunk;                 // input channels per block (cin, or a 64-multiple part of it when cin is large)
   int kparts;                 // cin / kchunk: blocks per kernel offset
@@ -99,6 +128,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Non-blocking test of a barrier phase.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
 __device__ __forceinline__ unsigned long long global_ns() {
   unsigned long long t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -120,6 +161,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     }
   }
 }
+// One lane waits, the warp learns the outcome.  __syncwarp orders the other lanes' later accesses after the
+// observation of lane 0.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int code) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, code) ? 1 : 0;
+  __syncwarp();
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
 
 __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* bar, void* dst, int x, int y) {
   asm volatile(
@@ -128,23 +177,17 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* ba
       : "r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
-// Contiguous global -> shared copy (both 16-byte aligned, size a multiple of 16) signalled on an mbarrier.
-__device__ __forceinline__ void bulk_load_1d(uint64_t* bar, void* dst, const void* src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               :
-               : "r"(smem_u32(dst)), "l"((uint64_t)src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-// 16-byte asynchronous copy; src_bytes = 0 writes 16 zero bytes without reading global memory.  No memory clobber:
-// it touches only the operand ring, which the issuing thread never accesses with ordinary loads or stores, and the
-// compiler may then overlap the id loads of the next block with these copies.
-// Predicated on `run` != 0 instead of branched around.
-__device__ __forceinline__ void cp_async_16_if(uint32_t run, uint32_t dst, const void* src, uint32_t src_bytes) {
+// 16-byte asynchronous copy; with `zero` != 0 it writes 16 zero bytes and ignores the source (the ignore-src
+// predicate form: one instruction either way).  No memory clobber: it touches only the operand ring, which the
+// issuing thread never accesses with ordinary loads or stores, and the compiler may then overlap the id loads of
+// the next stage with these copies.  Predicated on `run` != 0 instead of branched around.
+__device__ __forceinline__ void cp_async_16_if(uint32_t run, uint32_t dst, const void* src, uint32_t zero) {
   asm volatile(
-      "{\n\t.reg .pred q;\n\t"
+      "{\n\t.reg .pred q, z;\n\t"
       "setp.ne.b32 q, %3, 0;\n\t"
-      "@q cp.async.cg.shared.global [%0], [%1], 16, %2;\n\t}" ::"r"(dst),
-      "l"(src), "r"(src_bytes), "r"(run));
+      "setp.ne.b32 z, %2, 0;\n\t"
+      "@q cp.async.cg.shared.global [%0], [%1], 16, z;\n\t}" ::"r"(dst),
+      "l"(src), "r"(zero), "r"(run));
 }
 // The barrier receives one arrival (counted in its expected arrivals) once all cp.async issued so far by this
 // thread have landed.
@@ -169,13 +212,19 @@ __device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit_if(uint32_t run, uint64_t* bar) {
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
   asm volatile(
-      "{\n\t.reg .pred q;\n\t"
-      "setp.ne.b32 q, %1, 0;\n\t"
-      "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_u32(bar)),
-      "r"(run)
-      : "memory");
+      "{\n\t.reg .pred P;\n\t.reg .b32 r;\n\t"
+      "elect.sync r|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
 }
 // D (+)= A * B, issued only when `run` != 0 (predicated, not branched around).
 __device__ __forceinline__ void umma_f16_if(uint32_t run, uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
@@ -188,17 +237,6 @@ __device__ __forceinline__ void umma_f16_if(uint32_t run, uint32_t tmem_d, uint6
       :
       : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(run)
       : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, "
-      "%24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
 }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(
@@ -215,108 +253,144 @@ struct __align__(8) Shared {
   uint64_t empty[kMaxStages];  // MMA (tcgen05.commit) -> producers, control
   uint64_t acc_full[kNumAcc];
   uint64_t acc_empty[kNumAcc];
-  uint64_t idx_full[2];  // neighbour ids of a tile have landed
-  uint64_t idx_free[2];  // all producer warps are done with them
-  uint64_t b_ready;      // resident weights have landed
+  uint64_t b_ready;  // resident weights have landed
   uint32_t tmem_base;
   int abort_flag;
+  // zero-row flags of the producers: bit e * passes + i of zero_flags[slot][t] says that producer thread t (of a
+  // team) last zero-filled that position of the slot, so it still holds zeros.  In shared memory because the teams
+  // take the stages in turn and may meet the same slot.
+  uint32_t zero_flags[kMaxStages][kTileRows];
 };
 
 // Carved dynamic shared memory: [stages x (group A blocks | group B blocks)] aligned to 1024, the resident weights,
-// two neighbour-id buffers [kvol][128], the bias, the control block.
+// the bias, the control block.
 struct Smem {
   unsigned char* tiles;
   unsigned char* bres;  // resident weights [kvol][b_bytes] (when p.b_resident)
-  int32_t* idx;
   float* bias;
   Shared* sh;
   uint32_t stage_bytes;
 };
-__device__ __forceinline__ Smem carve_smem(unsigned char* raw, const TcParams& p) {
+template <int kGroup> __device__ __forceinline__ Smem carve_smem(unsigned char* raw, const TcParams& p) {
   Smem s;
   const uint32_t raw_addr = smem_u32(raw);
   s.tiles = raw + ((1024u - (raw_addr & 1023u)) & 1023u);
-  s.stage_bytes = (uint32_t)p.group * (p.a_bytes + (p.b_resident ? 0u : p.b_bytes));
+  s.stage_bytes = (uint32_t)kGroup * (p.a_bytes + (p.b_resident ? 0u : p.b_bytes));
   s.bres = s.tiles + (size_t)p.stages * s.stage_bytes;
-  s.idx = reinterpret_cast<int32_t*>(s.bres + (p.b_resident ? (size_t)p.kvol * p.b_bytes : 0));
-  s.bias = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(s.idx) + 2 * (size_t)p.idx_bytes);
+  s.bias = reinterpret_cast<float*>(s.bres + (p.b_resident ? (size_t)p.kvol * p.b_bytes : 0));
   s.sh = reinterpret_cast<Shared*>(s.bias + ((p.cout + 1) & ~1));
   return s;
 }
 
 // The stage sequence of a tile is derived identically by every role from the tile's offset mask: the kernel
-// offsets are cut into windows of `group` consecutive offsets; a window with at least one offset present is one
-// stage per K part (kparts > 1 implies group == 1), and offset `base + e` of the window owns block slot e of the
-// stage whether or not its neighbours in the window are present.  All addresses are then plain increments.
+// offsets are cut into windows of kGroup consecutive offsets; a window with at least one offset present is one
+// stage per K part, and offset `base + e` of the window owns block slot e of the stage whether or not its
+// neighbours in the window are present.  All addresses are then plain increments.
+struct StageIter {
+  int tile;
+  uint32_t mask;       // offset mask of `tile`
+  uint32_t mask_next;  // of the CTA's next tile, loaded while this one is walked (a load per tile is a round trip to L2)
+  int base;
+  int part;
+  uint32_t take;  // offsets of the window [base, base + kGroup) that are present
+};
+__device__ __forceinline__ uint32_t load_mask(const TcParams& p, int tile) {
+  return tile < p.num_tiles ? __ldg(p.tile_mask + tile) : 0u;
+}
+template <int kGroup> __device__ __forceinline__ void first_tile(const TcParams& p, StageIter& it) {
+  it.tile = blockIdx.x;
+  it.mask = load_mask(p, it.tile);
+  it.mask_next = load_mask(p, it.tile + gridDim.x);
+  it.base = -kGroup;
+  it.part = p.kparts - 1;
+  it.take = 0;
+}
+// Moves to the next stage of this CTA's tiles; false when there is none.
+template <int kGroup> __device__ __forceinline__ bool next_stage(const TcParams& p, StageIter& it) {
+  constexpr uint32_t gmask = (1u << kGroup) - 1u;
+  if (++it.part < p.kparts) return true;
+  it.part = 0;
+  it.base += kGroup;
+  for (;;) {
+    if (it.tile >= p.num_tiles) return false;
+    while (it.base < p.kvol) {
+      const uint32_t take = (it.mask >> it.base) & gmask;
+      if (take) {
+        it.take = take;
+        return true;
+      }
+      it.base += kGroup;
+    }
+    it.tile += gridDim.x;
+    it.base = 0;
+    it.mask = it.mask_next;
+    it.mask_next = load_mask(p, it.tile + gridDim.x);
+  }
+}
 
+// 16 accumulator columns starting at col0 of this thread's row: bias (+ residual), ReLU, convert, two 16-byte stores.
 template <bool kBf16>
-__device__ __forceinline__ void store_chunk(const uint32_t* acc, int n, const float* bias_s, int col0, void* out_row,
+__device__ __forceinline__ void store_chunk(const uint32_t* acc, const float* bias_s, int col0, void* out_row,
                                             const void* res_row, int relu) {
-  // n = 16 or 32 accumulator columns starting at col0 of this thread's row
-  float v[32];
+  float v[16];
 #pragma unroll
-  for (int j = 0; j < 32; ++j)
-    if (j < n) v[j] = __uint_as_float(acc[j]) + bias_s[col0 + j];
+  for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(acc[j]) + bias_s[col0 + j];
   if (res_row) {
     const uint4* r4 = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(res_row) + col0);
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      if (q * 8 < n) {
-        uint4 raw = __ldg(r4 + q);
-        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    for (int q = 0; q < 2; ++q) {
+      uint4 raw = __ldg(r4 + q);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float lo, hi;
-          if (kBf16) {
-            lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xFFFF0000u);
-          } else {
-            __half2 h = *reinterpret_cast<const __half2*>(&w[e]);
-            lo = __low2float(h), hi = __high2float(h);
-          }
-          v[q * 8 + 2 * e] += lo, v[q * 8 + 2 * e + 1] += hi;
+      for (int e = 0; e < 4; ++e) {
+        float lo, hi;
+        if (kBf16) {
+          lo = __uint_as_float(w[e] << 16), hi = __uint_as_float(w[e] & 0xFFFF0000u);
+        } else {
+          __half2 h = *reinterpret_cast<const __half2*>(&w[e]);
+          lo = __low2float(h), hi = __high2float(h);
         }
+        v[q * 8 + 2 * e] += lo, v[q * 8 + 2 * e + 1] += hi;
       }
     }
   }
   uint4* o4 = reinterpret_cast<uint4*>(reinterpret_cast<unsigned short*>(out_row) + col0);
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    if (q * 8 < n) {
-      uint32_t w[4];
+  for (int q = 0; q < 2; ++q) {
+    uint32_t w[4];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float a = v[q * 8 + 2 * e], b = v[q * 8 + 2 * e + 1];
-        if (relu) a = fmaxf(a, 0.f), b = fmaxf(b, 0.f);
-        if (kBf16) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-          w[e] = *reinterpret_cast<uint32_t*>(&h);
-        } else {
-          __half2 h = __floats2half2_rn(a, b);
-          w[e] = *reinterpret_cast<uint32_t*>(&h);
-        }
+    for (int e = 0; e < 4; ++e) {
+      float a = v[q * 8 + 2 * e], b = v[q * 8 + 2 * e + 1];
+      if (relu) a = fmaxf(a, 0.f), b = fmaxf(b, 0.f);
+      if (kBf16) {
+        __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+        w[e] = *reinterpret_cast<uint32_t*>(&h);
+      } else {
+        __half2 h = __floats2half2_rn(a, b);
+        w[e] = *reinterpret_cast<uint32_t*>(&h);
       }
-      o4[q] = make_uint4(w[0], w[1], w[2], w[3]);
     }
+    o4[q] = make_uint4(w[0], w[1], w[2], w[3]);
   }
 }
 
 // Barrier initialisation, bias staging and the TMEM allocation (by the MMA warp); returns the TMEM base address.
-template <int kProd>
+template <int kProdWarps>
 __device__ __forceinline__ uint32_t cta_setup(const TcParams& p, const Smem& s) {
   Shared* sh = s.sh;
   if (threadIdx.x == 0) {
     // a stage is full once every producer thread's copies have landed and, when B travels with the stage, its
     // TMA bytes too (the control warp's expect_tx arrival)
-    const int full_count = kProd + (p.b_resident ? 0 : 1);
+    const int full_count = kTileRows + (p.b_resident ? 0 : 1);  // the four warps of one producer team
     for (int i = 0; i < p.stages; ++i) mbar_init(&sh->full[i], full_count), mbar_init(&sh->empty[i], 1);
     for (int a = 0; a < kNumAcc; ++a) mbar_init(&sh->acc_full[a], 1), mbar_init(&sh->acc_empty[a], 4);
-    for (int b = 0; b < 2; ++b) mbar_init(&sh->idx_full[b], 1), mbar_init(&sh->idx_free[b], kProd / 32);
     mbar_init(&sh->b_ready, 1);
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  for (int i = threadIdx.x; i < kMaxStages * kTileRows; i += blockDim.x) (&sh->zero_flags[0][0])[i] = 0u;
   for (int c = threadIdx.x; c < p.cout; c += blockDim.x) s.bias[c] = p.bias[c];
-  if ((int)(threadIdx.x >> 5) == mma_warp_of(kProd)) tmem_alloc(&sh->tmem_base, p.tmem_cols);
+  if ((int)(threadIdx.x >> 5) == kProdWarps) tmem_alloc(&sh->tmem_base, p.tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -324,117 +398,157 @@ __device__ __forceinline__ uint32_t cta_setup(const TcParams& p, const Smem& s) 
 }
 
 // All roles meet, then the allocating warp returns the tensor memory.
-template <int kProd>
+template <int kProdWarps>
 __device__ __forceinline__ void cta_teardown(const TcParams& p, uint32_t tmem_base) {
   tc_fence_before();
   __syncthreads();
-  if ((int)(threadIdx.x >> 5) == mma_warp_of(kProd)) {
+  if ((int)(threadIdx.x >> 5) == kProdWarps) {
     tc_fence_after();
     tmem_dealloc(tmem_base, p.tmem_cols);
   }
 }
 
 // ---- producers ---------------------------------------------------------------------------------------------------
-// kPieces = 16-byte pieces per block row (kchunk / 8).  The kProd producer threads cover a [128 x kPieces] block in
-// 128 * kPieces / kProd passes; thread t copies piece t % kPieces of row t / kPieces + pass * (kProd / kPieces).  Consecutive
-// lanes take consecutive pieces of a row (whole rows per warp instruction on the global side, whole 128-byte lines
-// on the shared side), and because a pass advances by a multiple of 8 rows the XOR swizzle term of the destination
-// is the same in every pass: one per-thread offset, the rest are immediates.
-// The body of a stage is branch-free and fully unrolled over the kGroup block slots (absent offsets are predicated
-// off): a taken branch costs a lone warp tens of cycles, more than the copies it would skip.
-template <int kPieces, int kGroup, int kProd>
-__device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, int t) {
-  constexpr int kPasses = kTileRows * kPieces / kProd;
-  constexpr uint32_t kBlockBytes = kTileRows * kPieces * 16;  // = p.a_bytes
-  constexpr uint32_t gmask = (1u << kGroup) - 1u;
-  constexpr int kRowsPerPass = kProd / kPieces;
-  static_assert(kRowsPerPass % 8 == 0, "a pass must advance by whole swizzle periods");
-  constexpr int kBits = kGroup * kPasses <= 8 ? 8 : 16;  // zero-row flags per stage
-  constexpr int kRowBytes = kPieces >= 8 ? 128 : kPieces * 16;
+// kPieces = 16-byte pieces per row of a 64-column block (2, 4 or 8), kChunks = 64-column blocks per A block.
+// The producer warps form teams of four; a team fills a whole stage (warp q of the team copies rows [32q, 32q + 32)
+// of every block) and the teams take the stages in turn.  What a warp spends per stage besides the copies -- walking
+// the stage sequence, loading ids, waiting for the slot -- is then paid once per kTeams stages of the pipeline.
+// A warp instruction covers 32 / kPieces whole rows (lane = row * kPieces + piece: whole rows on the global side,
+// whole swizzle spans on the shared side); because a pass advances by a multiple of 4 rows and the warp's first row by
+// a multiple of 32, the XOR swizzle term of the destination is a per-lane constant (128-byte rows: two constants,
+// by pass parity).  The neighbour ids of the lane's rows come straight from the table in global memory (the lanes
+// of a row load the same word); the loads of the team's next stage are issued before the copies of this one.
+template <int kPieces, int kChunks, int kGroup, int kProdWarps>
+__device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, int warp, int lane) {
+  constexpr int kTeams = kProdWarps / 4;
+  constexpr int kRows = 32;                   // rows of a block per warp
+  constexpr int kRowsPerPass = 32 / kPieces;  // 16, 8 or 4
+  constexpr int kPasses = kRows / kRowsPerPass;
+  constexpr int kRowBytes = kPieces * 16;
+  constexpr uint32_t kChunkBytes = kTileRows * kRowBytes;      // one 64-column block
+  constexpr uint32_t kBlockBytes = kChunkBytes * kChunks;      // = p.a_bytes
   constexpr int kSwzShift = kRowBytes == 128 ? 0 : kRowBytes == 64 ? 1 : 2;
   constexpr int kSwzMask = kRowBytes == 128 ? 7 : kRowBytes == 64 ? 3 : 1;
+  static_assert(kGroup * kPasses <= 32, "one zero-row flag per (block slot, pass)");
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
-  const int lane = t & 31;
-  const int j = t % kPieces, rsub = t / kPieces;
-  const uint32_t dst_lane = (uint32_t)(j >> 3) * (kTileRows * 128) + (uint32_t)rsub * kRowBytes +
-                            ((((uint32_t)j & 7u) ^ (uint32_t)((rsub >> kSwzShift) & kSwzMask)) << 4);
+  const int team = warp / 4, quarter = warp % 4;
+  const int j = lane % kPieces, rsub = lane / kPieces;
+  const int row0 = kRows * quarter + rsub;  // the row this lane copies in pass 0
+  const uint32_t dst_lane =
+      (uint32_t)row0 * kRowBytes + ((uint32_t)(j ^ ((row0 >> kSwzShift) & kSwzMask)) << 4);
   const unsigned char* src_j = reinterpret_cast<const unsigned char*>(p.in_feats) + j * 16;
   const uint32_t row_src_bytes = (uint32_t)p.cin * 2;
   const uint32_t n_in_rows = (uint32_t)p.n_in_rows;
   const uint32_t tiles_addr = smem_u32(s.tiles);
-  const int ids_per_tile = p.kvol * kTileRows;
-  static_assert(kGroup * kPasses <= 16 && kMaxStages <= 8, "zero_rows keeps 8 or 16 bits per stage (then <= 4 stages)");
-  uint64_t zero_rows = 0;  // bit kBits * stage + e * kPasses + i: this thread's last copy to that position was a zero fill
-  int stage = 0;
-  uint32_t phase = 0, idx_phase = 0;  // idx_phase bit b: parity to wait for on idx_full[b]
-  int buf = 0;
-  bool ok = true;
+  uint32_t* const my_flags = &sh->zero_flags[0][quarter * 32 + lane];
+
+  auto load_ids = [&](const StageIter& it, int (&ids)[kGroup][kPasses]) {
+    const int32_t* base = p.table + ((int64_t)it.tile * p.kvol + it.base) * kTileRows + row0;
+#pragma unroll
+    for (int e = 0; e < kGroup; ++e)
+#pragma unroll
+      for (int i = 0; i < kPasses; ++i)
+        ids[e][i] = ((it.take >> e) & 1u) ? __ldg(base + e * kTileRows + i * kRowsPerPass) : -1;
+  };
+  // the neighbour ids of a tile are kvol * 512 contiguous bytes: one 128-byte line per lane of a team
+  auto prefetch_ids = [&](int tile) {
+    const int line = quarter * 32 + lane;
+    if (tile < p.num_tiles && line < p.kvol * 4) {
+      const int32_t* a = p.table + (int64_t)tile * p.kvol * kTileRows + line * 32;
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(a));
+    }
+  };
+  // the team's next stage: kTeams stages further in the sequence
+  auto next_own = [&](StageIter& it) -> bool {
+#pragma unroll
+    for (int t = 0; t < kTeams; ++t)
+      if (!next_stage<kGroup>(p, it)) return false;
+    return true;
+  };
   pdl_wait();  // masks, ids and features may come from the preceding kernels
-  uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
-  for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-    const int next = tile + gridDim.x;
-    const uint32_t next_mask = next < p.num_tiles ? __ldg(p.tile_mask + next) : 0u;
-    ok = mbar_wait(&sh->idx_full[buf], (idx_phase >> buf) & 1u, abort_flag, 13);
-    if (!ok) break;
-    idx_phase ^= 1u << buf;
-    const int32_t* ids = s.idx + (size_t)buf * ids_per_tile + rsub;
-    for (int base = 0; base < p.kvol && ok; base += kGroup) {
-      const uint32_t take = (mask >> base) & gmask;
-      if (!take) continue;
-      for (int part = 0; part < p.kparts; ++part) {
-        ok = mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag, 12);
-        if (!ok) break;
-        const unsigned char* src_part = src_j + (size_t)part * p.kchunk * 2;
-        const uint32_t dst = tiles_addr + (uint32_t)stage * s.stage_bytes + dst_lane;
-        const int32_t* idp = ids + base * kTileRows;
-        int id[kGroup][kPasses];
+  prefetch_ids((int)blockIdx.x + (int)gridDim.x);
+  int stage = team;  // slot of the team's current stage (at least two stages exist)
+  uint32_t phase = 0;
+  PROF_DECL
+  // One stage: find the team's stage after `cur` and start the loads of its ids, then wait for the slot and copy
+  // `cur`.  Returns false when `cur` was the team's last stage or a wait gave up.
+  auto step = [&](const StageIter& cur, const int (&ids)[kGroup][kPasses], StageIter& nxt,
+                  int (&ids_next)[kGroup][kPasses]) -> bool {
+    PROF(0);
+    nxt = cur;
+    const bool have_next = next_own(nxt);
+    if (have_next) load_ids(nxt, ids_next);
+    // on entering a tile, pull the ids of the CTA's next tile towards the SM: they may come from DRAM, which takes
+    // longer than the one stage the loads above run ahead
+    if (have_next && nxt.tile != cur.tile) prefetch_ids(nxt.tile + (int)gridDim.x);
+    PROF(1);
+    if (!mbar_wait_warp(&sh->empty[stage], phase ^ 1, abort_flag, 12)) return false;
+    PROF(2);
+    const unsigned char* src_part = src_j + (size_t)cur.part * p.kchunk * 2;
+    const uint32_t dst = tiles_addr + (uint32_t)stage * s.stage_bytes + dst_lane;
+    // A lone warp issues a dependent instruction every four cycles or so, and the copies (volatile asm) keep their
+    // order: so everything a copy needs is computed first, for all copies of the stage at once -- independent chains
+    // the scheduler can interleave -- and the copies themselves follow as short, independent instruction groups.
+    uint32_t valid_bits = 0, run_bits = 0;  // bit e * kPasses + i
+    const unsigned char* src[kGroup][kPasses];
 #pragma unroll
-        for (int e = 0; e < kGroup; ++e)
+    for (int e = 0; e < kGroup; ++e) {
+      if ((cur.take >> e) & 1u) run_bits |= (uint32_t)((1ull << kPasses) - 1ull) << (e * kPasses);
 #pragma unroll
-          for (int i = 0; i < kPasses; ++i)
-            id[e][i] = ((take >> e) & 1u) ? idp[e * kTileRows + i * kRowsPerPass] : -1;
-        // Most rows of a block have no neighbour (LiDAR: about 5 of 27 offsets per voxel).  A position this thread
-        // zero-filled the last time it wrote the stage is still zero (nobody else writes it), so a zero row over a
-        // zero row is skipped: it would only spend shared-memory bandwidth the tensor core needs.
-        const uint32_t was_zero = (uint32_t)(zero_rows >> (stage * kBits)) & ((1u << kBits) - 1u);
-        uint32_t now_zero = was_zero;
-#pragma unroll
-        for (int e = 0; e < kGroup; ++e)
-#pragma unroll
-          for (int i = 0; i < kPasses; ++i) {
-            constexpr uint32_t kNone = 0u;
-            const uint32_t bit = 1u << (e * kPasses + i);
-            const uint32_t run = (take >> e) & 1u;
-            const bool valid = (uint32_t)id[e][i] < n_in_rows;  // negative = no neighbour
-            const unsigned char* src = src_part + (uint64_t)(valid ? (uint32_t)id[e][i] : 0u) * row_src_bytes;
-            const uint32_t redundant = (!valid && (was_zero & bit)) ? 1u : kNone;
-            cp_async_16_if(run & (redundant ^ 1u), dst + (uint32_t)(e * kBlockBytes + i * kRowsPerPass * kRowBytes),
-                           src, valid ? 16u : 0u);
-            if (run) now_zero = valid ? (now_zero & ~bit) : (now_zero | bit);
-          }
-        zero_rows = (zero_rows & ~((unsigned long long)((1u << kBits) - 1u) << (stage * kBits))) |
-                    ((uint64_t)now_zero << (stage * kBits));
-        cp_async_arrive(&sh->full[stage]);  // one arrival per producer thread once its copies have landed
-        if (++stage == p.stages) stage = 0, phase ^= 1;
+      for (int i = 0; i < kPasses; ++i) {
+        const bool valid = (uint32_t)ids[e][i] < n_in_rows;  // negative = no neighbour
+        valid_bits |= (valid ? 1u : 0u) << (e * kPasses + i);
+        src[e][i] = src_part + (uint64_t)(valid ? (uint32_t)ids[e][i] : 0u) * row_src_bytes;
       }
     }
-    __syncwarp();
-    if (lane == 0) mbar_arrive(&sh->idx_free[buf]);  // this warp has read all the ids it needs
-    buf ^= 1;
-    mask = next_mask;
+    // Most rows of a block have no neighbour (LiDAR: about 5 of 27 offsets per voxel).  A position that was
+    // zero-filled the last time the slot was written is still zero, so a zero row over a zero row is skipped: it
+    // would only spend shared-memory bandwidth the tensor core needs.
+    uint32_t* flags = my_flags + stage * kTileRows;
+    const uint32_t was_zero = *flags;
+    const uint32_t copy_bits = (valid_bits | ~was_zero) & run_bits;
+    *flags = (was_zero & ~run_bits) | (~valid_bits & run_bits);
+#pragma unroll
+    for (int e = 0; e < kGroup; ++e)
+#pragma unroll
+      for (int i = 0; i < kPasses; ++i) {
+        const uint32_t bit = 1u << (e * kPasses + i);
+        const uint32_t d = (kRowBytes == 128 ? (dst ^ (uint32_t)((i & 1) << 6)) : dst) +
+                           (uint32_t)(e * kBlockBytes + i * kRowsPerPass * kRowBytes);
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c)
+          cp_async_16_if(copy_bits & bit, d + c * kChunkBytes, src[e][i] + c * 128, ~valid_bits & bit);
+      }
+    cp_async_arrive(&sh->full[stage]);  // one arrival per producer thread once its copies have landed
+    PROF(3);
+#pragma unroll
+    for (int t = 0; t < kTeams; ++t)
+      if (++stage == p.stages) stage = 0, phase ^= 1;
+    return have_next;
+  };
+  // two id buffers used in turn: the loaded ids are first touched a whole stage after their loads were issued
+  StageIter it_a, it_b;
+  int ids_a[kGroup][kPasses], ids_b[kGroup][kPasses];
+  first_tile<kGroup>(p, it_a);
+  bool have = true;
+  for (int t = 0; t <= team && have; ++t) have = next_stage<kGroup>(p, it_a);
+  if (have) {
+    load_ids(it_a, ids_a);
+    while (step(it_a, ids_a, it_b, ids_b) && step(it_b, ids_b, it_a, ids_a)) {
+    }
   }
+  PROF_STORE(0, warp == 0 && lane == 0)
 }
 
 // ---- control warp (one lane) ---------------------------------------------------------------------------------------
-// Keeps the two id buffers filled one tile ahead and brings in the weights: all of them once when they are
-// resident, else the blocks of every stage as soon as the stage is free.
+// Brings in the weights: all of them once when they are resident, else the blocks of every stage as soon as the
+// stage is free.
+template <int kGroup>
 __device__ __forceinline__ void control_role(const TcParams& p, const Smem& s, const CUtensorMap* map_b) {
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
   const uint32_t b_tx = (uint32_t)p.cout * p.kchunk * 2;
-  const int ids_per_tile = p.kvol * kTileRows;
-  const uint32_t gmask = (1u << p.group) - 1u;
   if ((int)blockIdx.x >= p.num_tiles) return;
   // the weights are constants of the layer: their load does not wait for the preceding kernel
   if (p.b_resident) {  // in the layout the per-stage loads would have produced
@@ -443,65 +557,43 @@ __device__ __forceinline__ void control_role(const TcParams& p, const Smem& s, c
       for (int c = 0; c < p.chunks; ++c)
         tma_load_2d(map_b, &sh->b_ready, s.bres + (size_t)k * p.b_bytes + (size_t)c * p.cout * p.row_bytes, c * 64,
                     k * p.cout);
+    return;
   }
-  pdl_wait();
-  mbar_arrive_expect_tx(&sh->idx_full[0], p.idx_bytes);
-  bulk_load_1d(&sh->idx_full[0], s.idx, p.table + (int64_t)blockIdx.x * ids_per_tile, p.idx_bytes);
-  int stage = 0, buf = 0;
-  uint32_t phase = 0, free_phase = 0;  // free_phase bit b: parity to wait for on idx_free[b]
-  bool first_tile = true;
-  uint32_t mask = __ldg(p.tile_mask + blockIdx.x);
-  for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-    const int next = tile + gridDim.x;
-    uint32_t next_mask = 0;
-    if (next < p.num_tiles) {
-      next_mask = __ldg(p.tile_mask + next);
-      // the other buffer held the previous tile's ids: wait until every producer warp has released it
-      if (!first_tile) {
-        if (!mbar_wait(&sh->idx_free[buf ^ 1], (free_phase >> (buf ^ 1)) & 1u, abort_flag, 14)) return;
-        free_phase ^= 1u << (buf ^ 1);
-      }
-      mbar_arrive_expect_tx(&sh->idx_full[buf ^ 1], p.idx_bytes);
-      bulk_load_1d(&sh->idx_full[buf ^ 1], s.idx + (size_t)(buf ^ 1) * ids_per_tile,
-                   p.table + (int64_t)next * ids_per_tile, p.idx_bytes);
+  pdl_wait();  // the offset masks come from the preceding kernels
+  StageIter it;
+  first_tile<kGroup>(p, it);
+  int stage = 0;
+  uint32_t phase = 0;
+  while (next_stage<kGroup>(p, it)) {
+    if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag, 11)) return;
+    mbar_arrive_expect_tx(&sh->full[stage], (uint32_t)__popc(it.take) * b_tx);
+    unsigned char* b_dst = s.tiles + (size_t)stage * s.stage_bytes + (size_t)kGroup * p.a_bytes;
+#pragma unroll
+    for (int e = 0; e < kGroup; ++e, b_dst += p.b_bytes) {
+      if (!((it.take >> e) & 1u)) continue;
+      for (int c = 0; c < p.chunks; ++c)
+        tma_load_2d(map_b, &sh->full[stage], b_dst + (size_t)c * p.cout * p.row_bytes,
+                    it.part * p.kchunk + c * 64, (it.base + e) * p.cout);
     }
-    if (!p.b_resident) {
-      for (int base = 0; base < p.kvol; base += p.group) {
-        const uint32_t take = (mask >> base) & gmask;
-        if (!take) continue;
-        for (int part = 0; part < p.kparts; ++part) {
-          if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag, 11)) return;
-          mbar_arrive_expect_tx(&sh->full[stage], (uint32_t)__popc(take) * b_tx);
-          unsigned char* b_dst = s.tiles + (size_t)stage * s.stage_bytes + (size_t)p.group * p.a_bytes;
-          for (int e = 0; e < p.group; ++e, b_dst += p.b_bytes) {
-            if (!((take >> e) & 1u)) continue;
-            for (int c = 0; c < p.chunks; ++c)
-              tma_load_2d(map_b, &sh->full[stage], b_dst + (size_t)c * p.cout * p.row_bytes,
-                          part * p.kchunk + c * 64, (base + e) * p.cout);
-          }
-          if (++stage == p.stages) stage = 0, phase ^= 1;
-        }
-      }
-    }
-    first_tile = false;
-    buf ^= 1;
-    mask = next_mask;
+    if (++stage == p.stages) stage = 0, phase ^= 1;
   }
 }
 
-// ---- MMA issuer (one lane) ---------------------------------------------------------------------------------------
+// ---- MMA warp ----------------------------------------------------------------------------------------------------
 // Low word of a K-major operand descriptor: start address in 16-byte units, leading byte offset 1 (unused for the
 // swizzled K-major layouts).  Advancing the operand by `d` bytes adds d / 16 to this word.
 __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16); }
 
-// kSteps = tcgen05.mma instructions (K = 16 each) per (offset, K part) block.
-// The body of a stage is branch-free: all kGroup block slots are unrolled and absent offsets predicated off, so
-// the issuing thread runs a straight line of descriptor adds and MMAs (a taken branch would cost it more than an MMA).
-template <int kSteps, int kGroup>
+// The whole warp walks the stage sequence; everything an MMA depends on (offset mask, stage slot, accumulate flag)
+// is kept warp-uniform in a form the compiler can see -- the mask goes through a shuffle from lane 0 -- so that
+// descriptor arithmetic stays in the uniform datapath; one elected lane issues the straight line of predicated
+// MMAs of a stage and the commit.
+template <int kPieces, int kChunks, int kGroup>
 __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint32_t tmem_base) {
-  constexpr uint32_t kRowBytes = kSteps >= 4 ? 128 : kSteps * 32;
-  constexpr uint32_t a_step = (kTileRows * kSteps * 32) >> 4;  // = p.a_bytes / 16
-  constexpr uint32_t cs_a = (kTileRows * kRowBytes) >> 4;      // between the 64-column blocks of A, 16-byte units
+  constexpr int kSteps = kPieces * kChunks / 2;  // tcgen05.mma instructions (K = 16 each) per block
+  constexpr uint32_t kRowBytes = kPieces * 16;
+  constexpr uint32_t a_step = (kTileRows * kRowBytes * kChunks) >> 4;  // = p.a_bytes / 16
+  constexpr uint32_t cs_a = (kTileRows * kRowBytes) >> 4;              // between the 64-column blocks of A
   constexpr uint32_t gmask = (1u << kGroup) - 1u;
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
@@ -510,62 +602,81 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
   const uint32_t cs_b = (uint32_t)(p.cout * kRowBytes) >> 4;
   const uint32_t b_step = p.b_bytes >> 4, stage_step = s.stage_bytes >> 4;
   const uint32_t tiles_lo = desc_lo(smem_u32(s.tiles)), bres_lo = desc_lo(smem_u32(s.bres));
-  const uint32_t b_in_stage = (uint32_t)kGroup * a_step;
   const uint32_t idesc = p.idesc;
   const bool resident = p.b_resident != 0;
-  if (resident && !mbar_wait(&sh->b_ready, 0, abort_flag, 23)) return;
+  if (resident && !__all_sync(0xffffffffu, mbar_wait(&sh->b_ready, 0, abort_flag, 23))) return;
   int stage = 0, acc = 0;
   uint32_t phase = 0, acc_phase = 0;
   const int num_stages = p.stages, kvol = p.kvol, kparts = p.kparts;
-  const uint32_t lane0 = (threadIdx.x & 31) == 0 ? 1u : 0u;  // the lane that issues; the others keep it company
+  bool landed = false;  // the stage about to be waited for was already seen full by the probe below
   pdl_wait();
-  uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
+  PROF_DECL
+  uint32_t mask_ahead = load_mask(p, blockIdx.x);
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-    const int next = tile + gridDim.x;
-    const uint32_t next_mask = next < p.num_tiles ? __ldg(p.tile_mask + next) : 0u;
-    if (mask) {  // a tile no offset feeds uses no accumulator: the epilogue writes its bias rows on its own
-      if (!mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1, abort_flag, 22)) return;
-      tc_fence_after();
-      const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.cout);
-      uint32_t accumulate = 0;
-      int part = 0;
-      for (int base = 0; base < kvol;) {
-        const uint32_t take = (mask >> base) & gmask;
-        if (take) {
-          // the full barrier guards shared memory only: no tcgen05 fence is needed, but the rows written by
-          // cp.async (generic proxy) must be made visible to the tensor core's reads (async proxy)
-          if (!mbar_wait(&sh->full[stage], phase, abort_flag, 21)) return;
-          fence_proxy_async();
-          const uint32_t a_lo = tiles_lo + (uint32_t)stage * stage_step;
-          uint32_t b_lo = resident ? bres_lo + (uint32_t)base * b_step : a_lo + b_in_stage;
+    const uint32_t mask = __shfl_sync(0xffffffffu, mask_ahead, 0);
+    mask_ahead = load_mask(p, tile + gridDim.x);  // a round trip to L2: in flight while this tile is issued
+    if (mask == 0) continue;  // a tile no offset feeds uses no accumulator: the epilogue writes its bias rows alone
+    PROF(0);
+    if (!__all_sync(0xffffffffu, mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1, abort_flag, 22))) return;
+    tc_fence_after();
+    PROF(4);
+    const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.cout);
+    uint32_t done = 0;  // nonzero once the accumulator holds a product
+    for (int base = 0; base < kvol; base += kGroup) {
+      const uint32_t take = (mask >> base) & gmask;
+      if (take == 0) continue;
+      for (int part = 0; part < kparts; ++part) {
+        // the full barrier guards shared memory only: no tcgen05 fence is needed, but the rows written by
+        // cp.async (generic proxy) must be made visible to the tensor core's reads (async proxy)
+        PROF(0);
+        if (!__all_sync(0xffffffffu, landed || mbar_wait(&sh->full[stage], phase, abort_flag, 21))) return;
+        PROF(1);
+        fence_proxy_async();
+        PROF(2);
+        // look at the following stage's barrier now: the answer (a round trip to shared memory) arrives while
+        // this stage's MMAs are issued, and a stage that has already landed then costs no wait at all
+        const bool wrap = stage + 1 == num_stages;
+        const int stage_next = wrap ? 0 : stage + 1;
+        const uint32_t phase_next = phase ^ (wrap ? 1u : 0u);
+        const bool landed_next = mbar_test(&sh->full[stage_next], phase_next);
+        const uint32_t a_lo = tiles_lo + (uint32_t)stage * stage_step;
+        const uint32_t b_lo = resident ? bres_lo + (uint32_t)base * b_step : a_lo + (uint32_t)kGroup * a_step;
+        const uint32_t before = done | (uint32_t)part;
+        // descriptors and flags of all MMAs of the stage first (independent, warp-uniform arithmetic), then the
+        // straight line of MMAs: the issuing lane runs no dependent chain between two of them
+        uint64_t desc_a[kGroup][kSteps], desc_b[kGroup][kSteps];
+        uint32_t earlier[kGroup];
 #pragma unroll
-          for (int e = 0; e < kGroup; ++e, b_lo += b_step) {
-            const uint32_t present = (take >> e) & 1u, run = present & lane0;
+        for (int e = 0; e < kGroup; ++e) {
+          earlier[e] = before | (take & ((1u << e) - 1u));
 #pragma unroll
-            for (int ks = 0; ks < kSteps; ++ks) {
-              // 32 bytes per K step inside the swizzle span, the next 64-column block every 4 steps
-              const uint32_t adv_a = (uint32_t)e * a_step + (uint32_t)(ks >> 2) * cs_a + (uint32_t)(ks & 3) * 2u;
-              const uint32_t adv_b = (uint32_t)(ks >> 2) * cs_b + (uint32_t)(ks & 3) * 2u;
-              umma_f16_if(run, d_addr, desc_hi | (a_lo + adv_a), desc_hi | (b_lo + adv_b), idesc, accumulate);
-              accumulate |= present;
-            }
+          for (int ks = 0; ks < kSteps; ++ks) {
+            // 32 bytes per K step inside the swizzle span, the next 64-column block every 4 steps
+            const uint32_t adv_a = (uint32_t)e * a_step + (uint32_t)(ks >> 2) * cs_a + (uint32_t)(ks & 3) * 2u;
+            const uint32_t adv_b = (uint32_t)e * b_step + (uint32_t)(ks >> 2) * cs_b + (uint32_t)(ks & 3) * 2u;
+            desc_a[e][ks] = desc_hi | (a_lo + adv_a);
+            desc_b[e][ks] = desc_hi | (b_lo + adv_b);
           }
-          umma_commit_if(lane0, &sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
-          const bool wrap = stage + 1 == num_stages;
-          stage = wrap ? 0 : stage + 1;
-          phase ^= wrap ? 1u : 0u;
-          ++part;
         }
-        // next K part of the same window, or the next window (one loop, one back edge: branches are what costs)
-        const bool window_done = !take || part == kparts;
-        base += window_done ? kGroup : 0;
-        part = window_done ? 0 : part;
+        if (elect_one()) {
+#pragma unroll
+          for (int e = 0; e < kGroup; ++e)
+#pragma unroll
+            for (int ks = 0; ks < kSteps; ++ks)
+              umma_f16_if((take >> e) & 1u, d_addr, desc_a[e][ks], desc_b[e][ks], idesc, ks > 0 ? 1u : earlier[e]);
+          umma_commit(&sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
+        }
+        __syncwarp();
+        PROF(3);
+        stage = stage_next, phase = phase_next, landed = landed_next;
       }
-      umma_commit_if(lane0, &sh->acc_full[acc]);
-      if (++acc == kNumAcc) acc = 0, acc_phase ^= 1;
+      done |= take;
     }
-    mask = next_mask;
+    if (elect_one()) umma_commit(&sh->acc_full[acc]);
+    __syncwarp();
+    if (++acc == kNumAcc) acc = 0, acc_phase ^= 1;
   }
+  PROF_STORE(1, (threadIdx.x & 31) == 0)
 }
 
 // ---- epilogue ----------------------------------------------------------------------------------------------------
@@ -578,34 +689,35 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
   uint32_t acc_phase = 0;
   pdl_wait();  // residual rows come from an earlier layer; output rows may still be read by the preceding kernel
   uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
+  PROF_DECL
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
     const int next = tile + gridDim.x;
     const uint32_t next_mask = next < p.num_tiles ? __ldg(p.tile_mask + next) : 0u;
     const bool empty_tile = mask == 0;  // bias (+ residual) only, no accumulator involved
+    PROF(0);
     if (!empty_tile) {
       if (!mbar_wait(&sh->acc_full[acc], acc_phase, abort_flag, 31)) return;
       tc_fence_after();
     }
+    PROF(1);
     const int64_t row = (int64_t)tile * kTileRows + quad * 32 + lane;
     const bool row_ok = row < p.m_max;
     unsigned short* out_row = reinterpret_cast<unsigned short*>(p.out) + row * p.cout;
     const unsigned short* res_row =
         (p.residual && row_ok) ? reinterpret_cast<const unsigned short*>(p.residual) + row * p.cout : nullptr;
     const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.cout);
-    for (int c0 = 0; c0 < p.cout; c0 += 32) {
-      const int n = p.cout - c0 >= 32 ? 32 : 16;
-      uint32_t v[32];
+    for (int c0 = 0; c0 < p.cout; c0 += 16) {
+      uint32_t v[16];
       if (empty_tile) {
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = 0u;
+        for (int j = 0; j < 16; ++j) v[j] = 0u;
       } else {
-        if (n == 32) tmem_ld32(taddr + c0, v);
-        else tmem_ld16(taddr + c0, v);
+        tmem_ld16(taddr + c0, v);
         tmem_ld_wait();
       }
       if (row_ok) {
-        if (p.is_bf16) store_chunk<true>(v, n, s.bias, c0, out_row, res_row, p.relu);
-        else store_chunk<false>(v, n, s.bias, c0, out_row, res_row, p.relu);
+        if (p.is_bf16) store_chunk<true>(v, s.bias, c0, out_row, res_row, p.relu);
+        else store_chunk<false>(v, s.bias, c0, out_row, res_row, p.relu);
       }
     }
     if (!empty_tile) {
@@ -614,31 +726,34 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
       if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
       if (++acc == kNumAcc) acc = 0, acc_phase ^= 1;
     }
+    PROF(2);
     mask = next_mask;
   }
+  PROF_STORE(2, quad == 0 && lane == 0)
 }
 
-// kSteps = kchunk / 16 (1, 2, 4, 8), kGroup = offsets per stage (1, 2, 4, 8), kProd = producer threads (256 or 128).
-template <int kSteps, int kGroup, int kProd>
-__global__ void __launch_bounds__(threads_of(kProd), kProd == 256 ? 1 : 2)
+// kPieces x kChunks = 16-byte pieces per A row (2, 4, 8, 16), kGroup = offsets per stage, kProdWarps = 4 or 8,
+// kCtas = CTAs per SM the launch is planned for (1 or 2).
+template <int kPieces, int kChunks, int kGroup, int kProdWarps, int kCtas>
+__global__ void __launch_bounds__(threads_of(kProdWarps), kCtas)
 spconv_mm_tc_kernel(const __grid_constant__ CUtensorMap map_b, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
-  const Smem s = carve_smem(smem_raw, p);
+  const Smem s = carve_smem<kGroup>(smem_raw, p);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const uint32_t tmem_base = cta_setup<kProd>(p, s);
+  const uint32_t tmem_base = cta_setup<kProdWarps>(p, s);
   pdl_release();
-  if (warp < kProd / 32) {
-    producer_role<2 * kSteps, kGroup, kProd>(p, s, threadIdx.x);
-  } else if (warp == mma_warp_of(kProd)) {
-    mma_role<kSteps, kGroup>(p, s, tmem_base);
+  if (warp < kProdWarps) {
+    producer_role<kPieces, kChunks, kGroup, kProdWarps>(p, s, warp, lane);
+  } else if (warp == kProdWarps) {
+    mma_role<kPieces, kChunks, kGroup>(p, s, tmem_base);
     __syncwarp();
-  } else if (warp == mma_warp_of(kProd) + 1) {
-    if (lane == 0) control_role(p, s, &map_b);
+  } else if (warp == kProdWarps + 1) {
+    if (lane == 0) control_role<kGroup>(p, s, &map_b);
     __syncwarp();
   } else {
     epilogue_role(p, s, tmem_base, warp & 3);
   }
-  cta_teardown<kProd>(p, tmem_base);
+  cta_teardown<kProdWarps>(p, tmem_base);
 }
 
 // ---- host --------------------------------------------------------------------------------------------------------
@@ -647,14 +762,14 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
+  static EncodeTiledFn fn = [] {
     void* ptr = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
         q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(ptr);
-  }
+      return reinterpret_cast<EncodeTiledFn>(ptr);
+    return static_cast<EncodeTiledFn>(nullptr);
+  }();  // initialised once, thread-safe
   return fn;
 }
 
@@ -680,6 +795,36 @@ struct TcState {
   bool map_b_ok = false;
 };
 
+// Tuning override for experiments (0 = automatic): offsets per stage and pipeline stages.
+int g_plan_group = 0, g_plan_stages = 0, g_plan_prod_warps = 0;
+
+typedef void (*KernelFn)(const CUtensorMap, const TcParams);
+struct KernelEntry {
+  int pieces, chunks, group, prod_warps, ctas;
+  KernelFn fn;
+};
+#define D3D_TC_K(P, C, G, W, N) {P, C, G, W, N, spconv_mm_tc_kernel<P, C, G, W, N>}
+// One kernel instance per (row width of a block, offsets per stage, CTAs per SM).
+const KernelEntry kKernels[] = {
+    D3D_TC_K(2, 1, 8, 8, 2), D3D_TC_K(2, 1, 4, 8, 2), D3D_TC_K(2, 1, 2, 8, 2), D3D_TC_K(2, 1, 1, 8, 2),
+    D3D_TC_K(4, 1, 4, 8, 2), D3D_TC_K(4, 1, 3, 8, 2), D3D_TC_K(4, 1, 2, 8, 2), D3D_TC_K(4, 1, 1, 8, 2),
+    D3D_TC_K(8, 1, 2, 8, 2), D3D_TC_K(8, 1, 1, 8, 2),
+    D3D_TC_K(2, 1, 8, 4, 2), D3D_TC_K(4, 1, 3, 4, 2), D3D_TC_K(8, 1, 1, 4, 2),
+    D3D_TC_K(2, 1, 8, 8, 1), D3D_TC_K(2, 1, 4, 8, 1), D3D_TC_K(2, 1, 2, 8, 1), D3D_TC_K(2, 1, 1, 8, 1),
+    D3D_TC_K(4, 1, 4, 8, 1), D3D_TC_K(4, 1, 3, 8, 1), D3D_TC_K(4, 1, 2, 8, 1), D3D_TC_K(4, 1, 1, 8, 1),
+    D3D_TC_K(8, 1, 2, 8, 1), D3D_TC_K(8, 1, 1, 8, 1), D3D_TC_K(8, 2, 1, 8, 1),
+};
+#undef D3D_TC_K
+constexpr int kNumKernels = sizeof(kKernels) / sizeof(kKernels[0]);
+
+const KernelEntry* find_kernel(int pieces, int chunks, int group, int prod_warps, int ctas) {
+  for (int i = 0; i < kNumKernels; ++i)
+    if (kKernels[i].pieces == pieces && kKernels[i].chunks == chunks && kKernels[i].group == group &&
+        kKernels[i].prod_warps == prod_warps && kKernels[i].ctas == ctas)
+      return &kKernels[i];
+  return nullptr;
+}
+
 }  // namespace
 
 bool spconv_mm_tc_eligible(const d3d_spconv_mm_s* h, int dtype) {
@@ -696,6 +841,19 @@ void spconv_mm_tc_release(d3d_spconv_mm_s* h) {
   h->tc_state = nullptr;
 }
 
+// Creates the per-handle state of the tensor-core path (the tensor map over the transposed weights).  Called from
+// d3d_spconv_mm_configure, so that an enqueue neither allocates nor encodes.
+int spconv_mm_tc_prepare(d3d_spconv_mm_s* h, int dtype) {
+  if (!spconv_mm_tc_eligible(h, dtype)) return D3D_OK;
+  const int cin = h->p.in_channels, cout = h->p.out_channels, kvol = h->p.kernel_vol;
+  TcState* st = new (std::nothrow) TcState();
+  D3D_REQUIRE(st, D3D_ERR_INVALID_ARGUMENT);
+  const uint32_t box_cols = cin < 64 ? cin : 64;
+  st->map_b_ok = make_map(&st->map_b, dtype, h->wt_dev, cin, (uint64_t)kvol * cout, box_cols, cout);
+  h->tc_state = st;
+  return st->map_b_ok ? D3D_OK : D3D_ERR_CUDA;
+}
+
 int launch_spconv_mm_tc(const MmLaunch& a) {
   d3d_spconv_mm_s* h = const_cast<d3d_spconv_mm_s*>(a.h);
   const int cin = h->p.in_channels, cout = h->p.out_channels, kvol = h->p.kernel_vol;
@@ -705,13 +863,8 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   D3D_REQUIRE(reinterpret_cast<uintptr_t>(a.in_feats) % 16 == 0 && reinterpret_cast<uintptr_t>(a.out_feats) % 16 == 0,
               D3D_ERR_INVALID_ARGUMENT);
   D3D_REQUIRE(!a.residual || reinterpret_cast<uintptr_t>(a.residual) % 16 == 0, D3D_ERR_INVALID_ARGUMENT);
-  if (!h->tc_state) h->tc_state = new TcState();
   TcState* st = reinterpret_cast<TcState*>(h->tc_state);
-  const uint32_t box_cols = cin < 64 ? cin : 64;
-  if (!st->map_b_ok) {
-    st->map_b_ok = make_map(&st->map_b, a.dtype, h->wt_dev, cin, (uint64_t)kvol * cout, box_cols, cout);
-    D3D_REQUIRE(st->map_b_ok, D3D_ERR_CUDA);
-  }
+  D3D_REQUIRE(st && st->map_b_ok, D3D_ERR_INVALID_ARGUMENT);  // configure() creates it
 
   TcParams p;
   p.table = a.table;
@@ -722,27 +875,8 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.n_in_rows = (int32_t)a.max_num_act_in;
   p.kvol = kvol, p.cin = cin, p.cout = cout;
   p.num_tiles = (int)((m_max + kTileRows - 1) / kTileRows);
-  p.row_bytes = (int)box_cols * 2;
-  p.idx_bytes = (uint32_t)kvol * kTileRows * 4;
-  // control data of a CTA: alignment slack, the two neighbour-id buffers, bias, barriers
-  const size_t ctrl = 1024 + 2 * (size_t)p.idx_bytes + align_up((size_t)cout * 4 + 8, 16) + sizeof(Shared);
-  const size_t budget_one = 227 * 1024 - ctrl;  // one CTA per SM
-  // a block holds `kchunk` <= 128 input channels of one kernel offset; split further until two stages fit
-  int kchunk = cin > 128 ? 128 : cin;
-  while (kchunk > 64 &&
-         2 * (align_up((size_t)kTileRows * kchunk * 2, 1024) + align_up((size_t)cout * kchunk * 2, 1024)) > budget_one)
-    kchunk /= 2;
-  int ksteps = 0;
-  auto set_chunk = [&](int kc) {
-    kchunk = kc, ksteps = kc / 16;
-    p.kchunk = kc;
-    p.kparts = cin / kc;
-    p.chunks = kc <= 64 ? 1 : kc / 64;
-    p.a_bytes = (uint32_t)align_up((size_t)kTileRows * kc * 2, 1024);
-    p.b_bytes = (uint32_t)align_up((size_t)cout * kc * 2, 1024);
-  };
-  const int kchunk_one = kchunk;  // block width with one CTA per SM; two per SM use at most 64 channels per block
-  set_chunk(kchunk_one);
+  const int box_cols = cin < 64 ? cin : 64;
+  p.row_bytes = box_cols * 2;
   p.layout_type = p.row_bytes == 32 ? 6u : p.row_bytes == 64 ? 4u : 2u;
   const uint32_t fmt = a.dtype == D3D_BF16 ? 1u : 0u;
   p.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(cout >> 3) << 17) | ((uint32_t)(kTileRows >> 4) << 24);
@@ -754,81 +888,94 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.residual = a.residual;
   p.relu = a.relu;
   p.is_bf16 = a.dtype == D3D_BF16;
-  // Shared-memory plan for one CTA per SM (256 producer threads) or two (128 each, half the memory).  Small layers
-  // keep all weight blocks resident instead of reloading one per stage; several offsets share a stage when their
-  // blocks are small, so that the per-stage hand-over cost is amortised (a stage holds at most 8 K-step blocks).
+
+  // Shared-memory plan.  Control data of a CTA: alignment slack, bias, barriers and row flags.
+  const size_t ctrl = 1024 + align_up((size_t)cout * 4 + 8, 16) + sizeof(Shared);
+  const size_t swizzle_repeat = (size_t)8 * p.row_bytes;  // operand blocks start on a multiple of it
   struct Plan {
-    int resident, group, stages;
+    int kchunk, resident, group, stages;
     size_t smem;
+    const KernelEntry* kernel;
   };
-  auto make_plan = [&](bool two_per_sm, Plan* out) -> bool {
-    if (two_per_sm && (kchunk > 64 || ctrl + 2048 > 113 * 1024)) return false;
-    const size_t bres_bytes = (size_t)kvol * p.b_bytes;
-    const size_t budget = (two_per_sm ? 113 * 1024 : 227 * 1024) - ctrl;
-    const size_t resident_limit = two_per_sm ? 32 * 1024 : 64 * 1024;
-    Plan pl;
-    pl.resident = (p.kparts == 1 && bres_bytes <= resident_limit) ? 1 : 0;
-    if (pl.resident && bres_bytes + 2 * (size_t)p.a_bytes > budget) pl.resident = 0;
-    const size_t ring = budget - (pl.resident ? bres_bytes : 0);
-    const size_t blk = (size_t)p.a_bytes + (pl.resident ? 0 : p.b_bytes);
-    const size_t stage_target = two_per_sm ? ring / 2 : 48 * 1024;
-    pl.group = 1;
-    if (p.kparts == 1)
-      while (pl.group < kMaxGroup && (size_t)(2 * pl.group) * blk <= stage_target && 2 * pl.group * ksteps <= 8)
-        pl.group *= 2;
-    const size_t stage_bytes = (size_t)pl.group * blk;
-    pl.stages = (int)(ring / stage_bytes);
-    // the producers keep per-stage zero-row flags in one 64-bit word: 8 bits per stage, 16 when a thread owns more
-    const int flag_bits = pl.group * ksteps * (two_per_sm ? 2 : 1) <= 8 ? 8 : 16;
-    const int max_stages = 64 / flag_bits < kMaxStages ? 64 / flag_bits : kMaxStages;
-    pl.stages = pl.stages > max_stages ? max_stages : pl.stages;
-    if (pl.stages < 2) return false;
-    pl.smem = ctrl + (size_t)pl.stages * stage_bytes + (pl.resident ? bres_bytes : 0);
-    // pin the number of CTAs per SM through the request: more than half (a third) of the SM's shared memory
+  // `two_per_sm`: 4 producer warps and half the SM's shared memory and tensor-memory columns per CTA.
+  auto make_plan = [&](bool two_per_sm, int kchunk, Plan* out) -> bool {
+    if (two_per_sm && (kchunk > 64 || cols > 256)) return false;
+    const int pieces = kchunk >= 64 ? 8 : kchunk / 8, chunks = kchunk > 64 ? kchunk / 64 : 1;
+    const int ksteps = kchunk / 16, kparts = cin / kchunk;
+    const size_t a_bytes = (size_t)kTileRows * kchunk * 2;
+    const size_t b_bytes = align_up((size_t)cout * kchunk * 2, swizzle_repeat);
+    const size_t limit = two_per_sm ? 113 * 1024 : 227 * 1024;
+    if (ctrl + 2 * (a_bytes + b_bytes) > limit) return false;
+    // two producer teams, except for 32-channel blocks, which measured better with one (B200: 94 vs 102 us at
+    // 463 k voxels; 64 channels: 102 vs 116 us, 128: 68 vs 73 us the other way round)
+    const int prod_warps = g_plan_prod_warps ? g_plan_prod_warps : (two_per_sm && kchunk == 32 ? 4 : 8);
+    const size_t budget = limit - ctrl;
+    const size_t bres_bytes = (size_t)kvol * b_bytes;
+    Plan best;
+    best.stages = 0, best.group = 0, best.kernel = nullptr;
+    int best_score = -1;
+    for (int resident = 1; resident >= 0; --resident) {
+      // resident weights: only while they leave the ring at least three quarters of the memory
+      if (resident && (kparts != 1 || bres_bytes * 4 > budget)) continue;
+      const size_t ring = budget - (resident ? bres_bytes : 0);
+      const size_t blk = a_bytes + (resident ? 0 : b_bytes);
+      for (int group = kMaxGroup; group >= 1; --group) {
+        const KernelEntry* k = find_kernel(pieces, chunks, group, prod_warps, two_per_sm ? 2 : 1);
+        if (!k) continue;
+        if (g_plan_group && group != g_plan_group) continue;
+        if (group > 1 && (group * ksteps > 8 || group > kvol)) continue;
+        int stages = (int)(ring / ((size_t)group * blk));
+        if (stages > kMaxStages) stages = kMaxStages;
+        if (g_plan_stages && stages > g_plan_stages) stages = g_plan_stages;
+        if (stages < 2) continue;
+        // three stages hide the gather latency, more add little; then as many MMAs per hand-over as possible
+        const int depth = stages >= 3 ? 3 : stages;
+        const int score = depth * 1000 + group * ksteps * 10 + (stages > 4 ? 4 : stages) + resident * 5;
+        if (score > best_score) {
+          best_score = score;
+          best.kchunk = kchunk, best.resident = resident, best.group = group, best.stages = stages, best.kernel = k;
+          best.smem = ctrl + (size_t)stages * group * blk + (resident ? bres_bytes : 0);
+        }
+      }
+    }
+    if (best_score < 0) return false;
+    // pin the number of CTAs per SM through the request: more than a third (half) of the SM's shared memory
     const size_t floor_bytes = two_per_sm ? 80 * 1024 : 120 * 1024;
-    if (pl.smem < floor_bytes) pl.smem = floor_bytes;
-    *out = pl;
+    if (best.smem < floor_bytes) best.smem = floor_bytes;
+    *out = best;
     return true;
   };
   Plan pl;
   bool two_per_sm = false;
-  // 128 input channels: two CTAs per SM (K split in two) measure about even with one; they win for few tiles per
-  // SM, where twice as many CTAs quantise the tile count better
-  if (h->kernel_choice != 3 && (cin < 128 || (cin == 128 && p.num_tiles <= 8 * kNumSMs))) {
-    set_chunk(kchunk_one < 64 ? kchunk_one : 64);
-    two_per_sm = make_plan(true, &pl);
-  }
+  if (h->kernel_choice != 3) two_per_sm = make_plan(true, cin < 64 ? cin : 64, &pl) && pl.stages >= 2;
   if (!two_per_sm) {
-    set_chunk(kchunk_one);
-    D3D_REQUIRE(make_plan(false, &pl), D3D_ERR_TOO_LARGE);
+    Plan wide, narrow;
+    const bool have_wide = cin >= 128 && make_plan(false, 128, &wide);
+    const bool have_narrow = make_plan(false, cin < 64 ? cin : 64, &narrow);
+    D3D_REQUIRE(have_wide || have_narrow, D3D_ERR_TOO_LARGE);
+    // 128-channel blocks (eight MMAs per hand-over) when three of them fit, else 64-channel K parts
+    pl = (have_wide && (wide.stages >= 3 || !have_narrow)) ? wide : narrow;
   }
-  p.b_resident = pl.resident, p.group = pl.group, p.stages = pl.stages;
-  const size_t smem = pl.smem;
-  // one kernel instance per (MMAs per block, offsets per stage, producer threads)
-  typedef void (*KernelFn)(const CUtensorMap, const TcParams);
-  static const KernelFn kernels[2][4][4] = {
-      {{spconv_mm_tc_kernel<1, 1, 256>, spconv_mm_tc_kernel<1, 2, 256>, spconv_mm_tc_kernel<1, 4, 256>,
-        spconv_mm_tc_kernel<1, 8, 256>},
-       {spconv_mm_tc_kernel<2, 1, 256>, spconv_mm_tc_kernel<2, 2, 256>, spconv_mm_tc_kernel<2, 4, 256>, nullptr},
-       {spconv_mm_tc_kernel<4, 1, 256>, spconv_mm_tc_kernel<4, 2, 256>, nullptr, nullptr},
-       {spconv_mm_tc_kernel<8, 1, 256>, nullptr, nullptr, nullptr}},
-      {{spconv_mm_tc_kernel<1, 1, 128>, spconv_mm_tc_kernel<1, 2, 128>, spconv_mm_tc_kernel<1, 4, 128>,
-        spconv_mm_tc_kernel<1, 8, 128>},
-       {spconv_mm_tc_kernel<2, 1, 128>, spconv_mm_tc_kernel<2, 2, 128>, spconv_mm_tc_kernel<2, 4, 128>, nullptr},
-       {spconv_mm_tc_kernel<4, 1, 128>, spconv_mm_tc_kernel<4, 2, 128>, nullptr, nullptr},
-       {nullptr, nullptr, nullptr, nullptr}}};
-  const int si = kchunk == 16 ? 0 : kchunk == 32 ? 1 : kchunk == 64 ? 2 : 3;
-  const int gi = pl.group == 1 ? 0 : pl.group == 2 ? 1 : pl.group == 4 ? 2 : 3;
-  const int di = two_per_sm ? 1 : 0;
-  D3D_REQUIRE(kernels[di][si][gi] != nullptr, D3D_ERR_TOO_LARGE);
-  static bool attr_set[64][2][4][4] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return D3D_ERR_CUDA;
-  if (!attr_set[dev][di][si][gi]) {
-    if (cudaFuncSetAttribute(kernels[di][si][gi], cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) !=
-        cudaSuccess)
-      return D3D_ERR_CUDA;
-    attr_set[dev][di][si][gi] = true;
+  p.kchunk = pl.kchunk;
+  p.kparts = cin / pl.kchunk;
+  p.chunks = pl.kchunk <= 64 ? 1 : pl.kchunk / 64;
+  p.a_bytes = (uint32_t)((size_t)kTileRows * pl.kchunk * 2);
+  p.b_bytes = (uint32_t)align_up((size_t)cout * pl.kchunk * 2, swizzle_repeat);
+  p.b_resident = pl.resident, p.stages = pl.stages;
+  const KernelFn kernel = pl.kernel->fn;
+  {
+    // raising the dynamic shared memory limit is per function and per device; once each, under a lock
+    static std::mutex attr_lock;
+    static bool attr_set[64][kNumKernels] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return D3D_ERR_CUDA;
+    const int ki = (int)(pl.kernel - kKernels);
+    std::lock_guard<std::mutex> guard(attr_lock);
+    if (!attr_set[dev][ki]) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
+        return D3D_ERR_CUDA;
+      attr_set[dev][ki] = true;
+    }
   }
   const int ctas = kNumSMs * (two_per_sm ? 2 : 1);
   const int grid = p.num_tiles < ctas ? p.num_tiles : ctas;
@@ -837,13 +984,13 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   // it touches its data.  Measured on B200: 3-4 us less per launch for layers run back to back on one stream; a
   // loss where other streams have kernels that would otherwise fill the tail of the preceding kernel.
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(threads_of(two_per_sm ? 128 : 256));
-  cfg.dynamicSmemBytes = smem, cfg.stream = reinterpret_cast<cudaStream_t>(a.stream);
+  cfg.gridDim = dim3(grid), cfg.blockDim = dim3(threads_of(pl.kernel->prod_warps));
+  cfg.dynamicSmemBytes = pl.smem, cfg.stream = reinterpret_cast<cudaStream_t>(a.stream);
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr, cfg.numAttrs = h->dependent_launch ? 1 : 0;
-  if (cudaLaunchKernelEx(&cfg, kernels[di][si][gi], st->map_b, p) != cudaSuccess) return D3D_ERR_CUDA;
+  if (cudaLaunchKernelEx(&cfg, kernel, st->map_b, p) != cudaSuccess) return D3D_ERR_CUDA;
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }
@@ -859,5 +1006,22 @@ extern "C" int d3d_debug_take_kernel_error(int* code) {
   if (cudaDeviceSynchronize() != cudaSuccess) return D3D_ERR_CUDA;
   if (cudaMemcpyFromSymbol(code, d3d::g_tc_error, sizeof(int)) != cudaSuccess) return D3D_ERR_CUDA;
   if (cudaMemcpyToSymbol(d3d::g_tc_error, &zero, sizeof(int)) != cudaSuccess) return D3D_ERR_CUDA;
+  return D3D_OK;
+}
+
+#ifdef D3D_TC_PROFILE
+extern "C" int d3d_debug_copy_prof(long long* dst) {
+  cudaDeviceSynchronize();
+  return (int)cudaMemcpyFromSymbol(dst, d3d::g_prof, sizeof(long long) * 24);
+}
+#endif
+
+// Tuning aid without a reference counterpart: overrides the pipeline plan of the tensor-core kernel for every later
+// launch of this process (kernel offsets per stage, maximum number of stages, producer warps; 0 = automatic).  Not thread-safe.
+extern "C" int d3d_debug_set_tc_plan(int group, int max_stages, int prod_warps) {
+  if (group < 0 || group > d3d::kMaxGroup || max_stages < 0 || max_stages > d3d::kMaxStages ||
+      !(prod_warps == 0 || prod_warps == 4 || prod_warps == 8))
+    return D3D_ERR_INVALID_ARGUMENT;
+  d3d::g_plan_group = group, d3d::g_plan_stages = max_stages, d3d::g_plan_prod_warps = prod_warps;
   return D3D_OK;
 }

@@ -30,7 +30,12 @@ def main():
     ap.add_argument("--reps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--index-reps", type=int, default=0, help="also time the rulebook + table build this many times")
+    ap.add_argument("--plan", type=int, nargs=3, default=None, metavar=("GROUP", "STAGES", "PRODUCER_WARPS"),
+                    help="override the tensor-core kernel's pipeline plan (0 = automatic)")
     args = ap.parse_args()
+    if args.plan:
+        from . import _lib
+        _lib.check("d3d_debug_set_tc_plan", _lib.lib().d3d_debug_set_tc_plan(*args.plan))
     dev = "cuda:0"
     rng = np.random.Generator(np.random.PCG64(77))
     vox = synth.lidar_like_voxels(rng, args.voxels, tuple(args.grid), sigma=6.0)

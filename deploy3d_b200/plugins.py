@@ -152,6 +152,13 @@ class SPConvMMPlugin(_Plugin):
     def output_descs(self, in_descs):
         return [make_desc(in_descs[0].dtype, (self.p.max_num_act_out, self.p.out_channels))]
 
+    def enqueue(self, *inputs, outputs=None, stream=None):
+        """configurePlugin for the dtype of ``inFeats`` (a no-op when already done), then enqueue: the C entry
+        point itself refuses a handle that was not configured, as it may not allocate."""
+        with torch.cuda.device(inputs[0].device):
+            self.configure(inputs[0].dtype)
+        return super().enqueue(*inputs, outputs=outputs, stream=stream)
+
     def configure(self, torch_dtype):
         """configurePlugin: upload the weights in the compute dtype (trt/spconv/mm_trt.cu:127-142)."""
         check("d3d_spconv_mm_configure", lib().d3d_spconv_mm_configure(self.handle, _TORCH2D3D[torch_dtype]))

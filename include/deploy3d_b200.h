@@ -63,6 +63,10 @@ const char* d3d_status_string(int status);
  * synchronises the device, returns in *code the error word a kernel of this library raised when one of its bounded
  * waits expired (0 = none) and clears it. */
 int d3d_debug_take_kernel_error(int* code);
+/* Tuning aid (no reference counterpart): overrides the pipeline plan of the tensor-core SPConvMM kernel for every
+ * later launch of the process: kernel offsets per pipeline stage, maximum number of stages, producer warps (4 or 8);
+ * 0 = automatic.  Not thread-safe; results do not depend on the plan. */
+int d3d_debug_set_tc_plan(int group, int max_stages, int prod_warps);
 
 /* ---------------------------------------------------------------------------------------------
  * SPConvIdx{1,2,3,4}d -- rulebook generation.
