@@ -4,9 +4,9 @@
     python bench.py [--gpus N] [--steps K] [--warmup W]            this implementation (one process per GPU)
     python bench.py --impl reference [--steps K] [--warmup W]      the CPU restatement of the reference on host cores
 
-One step = one frame of benchmark config 4 (300 000 points x 5 channels -> mean voxel encoder -> VoxelResBackBone8x
-16/32/64/128 in fp16 -> BEV densify, plus rotated-BEV NMS over 10 x 1000 boxes at IoU 0.2) on synthetic, seeded
-data.  Prints ONE JSON line (rank 0).  `value` is measured with the inputs resident in HBM (CUDA-graph replay,
+One step = FRAMES_PER_STEP frames of benchmark config 4 (300 000 points x 5 channels -> mean voxel encoder ->
+VoxelResBackBone8x 16/32/64/128 in fp16 -> BEV densify, plus rotated-BEV NMS over 10 x 1000 boxes at IoU 0.2) on
+synthetic, seeded data.  Prints ONE JSON line (rank 0).  `value` is measured with the inputs resident in HBM (CUDA-graph replay,
 CUDA events); `e2e` drives the same frames from pinned host memory through the public pipeline object, with the
 H2D copy of every frame's inputs and the D2H read of its results inside the timed region.
 """
@@ -28,6 +28,8 @@ METRIC = "sparse backbone frames/s (CenterPoint-shaped frame, fp16)"
 UNIT = "frames/s"
 WORKLOAD = "config4: 300000 pts x5 -> mean VFE -> VoxelResBackBone8x 16/32/64/128 fp16 -> BEVDensify + NMS3d 10x1000 @0.2"
 N_ROTATE = 4  # distinct synthetic frames cycled through the input buffers
+FRAMES_PER_STEP = 10  # frames per GPU and step: 20 steps time 200 frames per GPU, about half a second
+REFERENCE_BUDGET_S = 150.0  # the CPU arm stops adding timed steps once this much time has been spent
 CPU_FRACTION = 1.0 / 16  # share of one frame (an azimuth sector) the CPU arm processes per thread and step
 CPU_DENOM = 16
 
@@ -104,8 +106,9 @@ def sector_sample(frame, fraction, which=0):
     return pts[m], frame["batch"][m]
 
 
-def cpu_frames_per_second(threads, fraction, steps, warmup):
-    """Runs `threads` sector samples concurrently per step; returns (frames/s, seconds per step)."""
+def cpu_frames_per_second(threads, fraction, steps, warmup, budget_s=None):
+    """Runs `threads` sector samples concurrently per step; returns (frames/s, seconds per step, steps run).
+    With `budget_s`, no further step is started once the timed steps have used that much time."""
     from concurrent.futures import ThreadPoolExecutor
     from deploy3d_b200 import synth
     from oracle import pipeline_cpu
@@ -126,23 +129,28 @@ def cpu_frames_per_second(threads, fraction, steps, warmup):
     for _ in range(warmup):
         step()
     t0 = time.perf_counter()
-    for _ in range(steps):
+    done = 0
+    while done < steps:
         step()
-    dt = (time.perf_counter() - t0) / steps
-    return threads * fraction / dt, dt
+        done += 1
+        if budget_s is not None and time.perf_counter() - t0 > budget_s:
+            break
+    dt = (time.perf_counter() - t0) / done
+    return threads * fraction / dt, dt, done
 
 
 def run_reference(args):
+    """The reference has no CPU implementation of its own; this arm times the CPU restatement of its algorithm
+    (oracle/: scalar C, one thread per azimuth sector, one sector per host core and step).  It loads neither the
+    product library nor a GPU."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     cores = len(os.sched_getaffinity(0))
     fraction = CPU_FRACTION
-    # keep the whole run within a few minutes whatever K and W are: one step of a 1/16 sector costs some 15 s
-    # of single-core work per thread, so clamp the number of timed steps the arm actually executes
-    steps = max(1, min(args.steps, 3))
     warmup = 1 if args.warmup > 0 else 0
-    fps, dt = cpu_frames_per_second(cores, fraction, steps, warmup)
+    # every requested step is run unless the budget runs out first (a step is some 2-20 s, depending on the host)
+    fps, dt, steps = cpu_frames_per_second(cores, fraction, max(1, args.steps), warmup, REFERENCE_BUDGET_S)
     line = {
         "impl": "reference", "metric": METRIC, "value": fps, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -150,35 +158,30 @@ def run_reference(args):
         "config": {"workload": WORKLOAD, "sample": "1/%d azimuth sector of the frame per thread" % CPU_DENOM},
         "cpu_baseline": {"value": fps, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": "%d threads x (1/%d azimuth sector of one config-4 frame, 1 of the 10 NMS rows) "
-                                   "per step, frames/s = threads/%d/t; requested steps %d clamped to %d"
-                                   % (cores, CPU_DENOM, CPU_DENOM, args.steps, steps)},
+                                   "per step, frames/s = threads/%d/t; %d of %d requested steps fit the %d s budget"
+                                   % (cores, CPU_DENOM, CPU_DENOM, steps, args.steps, int(REFERENCE_BUDGET_S))},
         "e2e": {"value": fps, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    gpu = reference_gpu_kernels()
-    if gpu is not None:
-        line["reference_gpu"] = gpu
     print(json.dumps(line))
 
 
 def reference_gpu_kernels():
-    """Extra, informational key of the reference arm: the reference has no CPU implementation (the value of this arm
-    is the CPU port of its algorithm), but its own CUDA kernels compile for sm_100a (oracle/_ref/libref_spconv.so).
-    When that library and a GPU are present, time its rulebook builders and convolution launches on the benchmark
-    frame, one after the other with CUDA events.  Not a frames/s figure of a complete reference pipeline: its ReLU /
-    add graph ops, encoder, densify, NMS and host synchronisations are not included, so 1 / (sum) bounds it from above."""
+    """Informational key of this implementation's line (`config.reference_gpu`): the reference's own CUDA kernels
+    compile for sm_100a (oracle/_ref/libref_spconv.so).  When that library is present, its rulebook builders and
+    convolution launches are timed on the benchmark frame, one after the other with CUDA events, after the timed
+    regions of the benchmark.  Not a frames/s figure of a complete reference pipeline: its ReLU / add graph ops,
+    encoder, densify, NMS and host synchronisations are not included, so 1 / (sum) bounds it from above."""
     try:
-        import torch
-        if not torch.cuda.is_available():
-            return None
         from oracle import ref_gpu_timing
         r = ref_gpu_timing.measure(reps=5)
         ref_ms = (r["rulebook_us"][0] + r["conv_us"][0]) * 1e-3
         return {"rulebook_ms_per_frame": r["rulebook_us"][0] * 1e-3, "conv_ms_per_frame": r["conv_us"][0] * 1e-3,
                 "frames_per_s_upper_bound": 1e3 / ref_ms,
+                "product_rulebook_ms_per_frame": r["rulebook_us"][1] * 1e-3,
                 "what": "reference CUDA kernels (trt/spconv/index.cu, trt/spconv/mm.h) recompiled for sm_100a, "
                         "rulebooks + 21 convolution launches of one config-4 frame, back to back on one B200"}
-    except Exception as e:  # the arm's value does not depend on this
+    except Exception as e:  # informational only
         sys.stderr.write("reference_gpu skipped: %s\n" % e)
         return None
 
@@ -186,11 +189,21 @@ def reference_gpu_kernels():
 # ------------------------------------------------------------------------------------------------------------------
 # GPU arm
 # ------------------------------------------------------------------------------------------------------------------
-# dram__bytes_read.sum + dram__bytes_write.sum over the 21 SPConvMM launches of one config-4 frame, from the ncu capture
-# summarised in profiles/spconv_mm_tc_bench_layers_dram.md (L2 flushed before every launch; outputs still in L2 at the
-# end of a launch are written back later and not counted)
-CONV_DRAM_BYTES_PER_FRAME = 1.43e9
+DRAM_PROFILE = os.path.join(ROOT, "profiles", "spconv_mm_tc_bench_layers_dram.md")
 INNER_LAUNCHES = 4  # timed launches per layer and frame in the per-layer pass
+
+
+def conv_dram_bytes_per_frame():
+    """dram__bytes_read.sum + dram__bytes_write.sum over the 21 SPConvMM launches of one config-4 frame, from the ncu
+    capture summarised in profiles/spconv_mm_tc_bench_layers_dram.md (its `dram_bytes_per_frame:` line, which also
+    names the kernel source revision it was captured at).  None when the summary is missing."""
+    import re
+    try:
+        with open(DRAM_PROFILE) as f:
+            m = re.search(r"^dram_bytes_per_frame:\s*([0-9.eE+]+)\s*\((.*)\)\s*$", f.read(), re.M)
+        return (float(m.group(1)), m.group(2)) if m else None
+    except OSError:
+        return None
 
 
 def conv_launch_times(pipe, frames, reps):
@@ -258,19 +271,10 @@ def run_ours(args):
     dev = "cuda:%d" % local
     dist = None
     if world > 1:
+        # The frames are independent replicas: no data crosses GPUs.  The ranks only meet at the barriers around the
+        # timed regions and to exchange their elapsed times, which a host-side (gloo) group does.
         import torch.distributed as dist
-        # NCCL prints its version banner to stdout when the communicator comes up; stdout must carry exactly one
-        # JSON line, so file descriptor 1 points at stderr until the first collective has run
-        sys.stdout.flush()
-        saved_stdout = os.dup(1)
-        os.dup2(2, 1)
-        try:
-            dist.init_process_group("nccl", device_id=torch.device(dev))
-            dist.barrier()
-            torch.cuda.synchronize()
-        finally:
-            os.dup2(saved_stdout, 1)
-            os.close(saved_stdout)
+        dist.init_process_group("gloo")
 
     frames = [synth.config4_points(i) for i in range(N_ROTATE)]
     boxes = synth.config4_boxes()
@@ -294,11 +298,12 @@ def run_ours(args):
     torch.cuda.synchronize()
     dev_pts = [torch.from_numpy(f["points"]).to(dev) for f in frames]
     working_set = pipe.buffer_bytes()
+    fps_step = FRAMES_PER_STEP
 
     def barrier():
+        torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
-        torch.cuda.synchronize()
 
     # ---- device-resident throughput: graph replay, inputs already in HBM ------------------------------------------
     main_stream = torch.cuda.current_stream()
@@ -324,7 +329,7 @@ def run_ours(args):
                     marks[-1][1].record(run_streams[k])
 
     fork()
-    device_loop(args.warmup)
+    device_loop(args.warmup * fps_step)
     join()
     barrier()
     sampler = ClockSampler(local)
@@ -333,7 +338,7 @@ def run_ours(args):
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()  # on the launching stream; the run streams start after it and are joined before e1
     fork()
-    device_loop(args.steps)
+    device_loop(args.steps * fps_step)
     join()
     e1.record()
     barrier()
@@ -393,26 +398,27 @@ def run_ours(args):
             frame_done[s].synchronize()
 
     fork()
-    e2e_loop(args.warmup)
+    e2e_loop(args.warmup * fps_step)
     join()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     f0.record()
     fork()
-    e2e_loop(args.steps)
+    e2e_loop(args.steps * fps_step)
     join()
     f1.record()
     barrier()
     e2e_elapsed = f0.elapsed_time(f1) * 1e-3
     # the results that came back are real: both slots ran the same candidate boxes (same NMS verdicts, some boxes
     # suppressed, some kept) and every voxel set of the last two frames is populated
-    if args.steps >= 2:
-        a, b = out_scores[0].numpy(), out_scores[1].numpy()
-        if not ((a == b).all() and (a < 0).any() and (a > 0).any() and (out_counts[0][:len(count_tensors[0])] > 0).all()
-                and (out_counts[1][:len(count_tensors[0])] > 0).all()):
-            raise RuntimeError("end-to-end results look wrong: NMS scores or voxel counts of the last frames")
+    a, b = out_scores[0].numpy(), out_scores[1].numpy()
+    if not ((a == b).all() and (a < 0).any() and (a > 0).any() and (out_counts[0][:len(count_tensors[0])] > 0).all()
+            and (out_counts[1][:len(count_tensors[0])] > 0).all()):
+        raise RuntimeError("end-to-end results look wrong: NMS scores or voxel counts of the last frames")
 
-    elapsed, e2e_elapsed = max_over_ranks([elapsed, e2e_elapsed], dist, dev)
+    per_rank = gather_ranks([elapsed, e2e_elapsed], dist)  # [rank][which]
+    elapsed_all = [r[0] for r in per_rank]
+    elapsed, e2e_elapsed = max(elapsed_all), max(r[1] for r in per_rank)
 
     line = None
     if rank == 0:
@@ -423,33 +429,50 @@ def run_ours(args):
         f_dense = sum(l["flops_dense"] for l in tc)
         achieved = f_dense / t_conv / 1e12
         launches_per_frame = count_launches(pipe)
+        traffic = conv_dram_bytes_per_frame()
+        plugin_order = None
+        if world == 1 and not args.no_plugin_order:
+            plugin_order = plugin_order_rate(dev, caps, frames, boxes, dev_pts, args)
+        ref_gpu = None
+        if world == 1 and not args.no_reference_gpu and os.path.exists(os.path.join(ROOT, "oracle", "_ref",
+                                                                                  "libref_spconv.so")):
+            ref_gpu = reference_gpu_kernels()
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
             # a quarter of a frame: some 10-20 s of single-core work, enough to time, short enough for a default run
-            fps, dt = cpu_frames_per_second(1, 0.25, 1, 0)
+            fps, dt, _ = cpu_frames_per_second(1, 0.25, 1, 0)
             cpu = {"value": fps, "unit": UNIT, "cores": 1, "kind": "port",
                    "sample": "one 1/4 azimuth sector of a config-4 frame (and 2 of the 10 NMS rows) on one core, "
                              "frames/s = (1/4)/t, t = %.1f s" % dt}
+        frames_timed = args.steps * fps_step
         line = {
-            "metric": METRIC, "value": world * args.steps / elapsed, "unit": UNIT, "n_gpus": world,
+            "metric": METRIC, "value": aggregate_frames_per_second(world, args.steps, fps_step, elapsed),
+            "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
             "data": "synthetic",
-            "config": {"workload": WORKLOAD, "frames_per_gpu_per_step": 1, "parallelism": "frame replicas x%d" % world,
+            "config": {"workload": WORKLOAD, "frames_per_gpu_per_step": fps_step,
+                       "ms_per_frame": elapsed / frames_timed * 1e3,
+                       "parallelism": "frame replicas x%d (no collective; ranks meet at host-side barriers only)" % world,
                        "frames_in_flight_per_gpu": n_pipes, "frame_latency_ms": frame_latency_ms,
                        "voxels": {k: int(v) for k, v in pipe.net.counts().items()},
                        "l2": "no flush: a frame rewrites %.0f MB of rulebooks/tables/activations (> 126 MB L2) and "
                              "inputs rotate over %d frames" % (working_set / 1e6, N_ROTATE),
-                       "kernel": {0: "auto", 1: "simt", 2: "tcgen05"}[args.kernel]},
+                       "kernel": {0: "auto", 1: "simt", 2: "tcgen05"}[args.kernel],
+                       "rank_seconds": {"min": min(elapsed_all), "median": float(np.median(elapsed_all)),
+                                        "max": max(elapsed_all)},
+                       "outputs": "NMS scores and voxel counts return to the host; the BEV map stays on the device, "
+                                  "where the dense head of the engine reads it",
+                       "plugin_order": plugin_order, "reference_gpu": ref_gpu},
             "clocks": clocks,
-            "e2e": {"value": world * args.steps / e2e_elapsed, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_elapsed / args.steps * 1e3},
-            "gpu_launches": launches_per_frame * args.steps,
+            "e2e": {"value": world * frames_timed / e2e_elapsed, "unit": UNIT, "h2d_bytes_per_step": h2d * fps_step,
+                    "d2h_bytes_per_step": d2h * fps_step, "ms_per_step": e2e_elapsed / args.steps * 1e3},
+            "gpu_launches": launches_per_frame * frames_timed,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_tflops"],
-                         "traffic": CONV_DRAM_BYTES_PER_FRAME / len(tc),
-                         "traffic_unit": "bytes per launch (mean of the %d launches of a frame; ncu, L2 flushed before "
-                                         "every launch)" % len(tc),
+                         "traffic": traffic[0] / len(tc) if traffic else None,
+                         "traffic_unit": ("bytes per launch (mean of the %d launches of a frame; ncu, L2 flushed before "
+                                          "every launch; captured at %s)" % (len(tc), traffic[1])) if traffic else None,
                          "algorithmic_bytes": sum(l["bytes"] for l in tc) / len(tc),
                          "kernel": "SPConvMM (tcgen05) over all %d layers of the backbone, dense-equivalent FLOPs "
                                    "2*M*kVol*Cin*Cout per launch, time = sum of per-launch CUDA-event durations (each layer launched back to back)"
@@ -471,15 +494,47 @@ def run_ours(args):
     return line
 
 
-def max_over_ranks(values, dist, device):
-    """Slowest rank decides: element-wise maximum of `values` over all ranks (identity without a process group).
-    The frames are independent replicas, so this reduction of the timings is the only inter-rank exchange."""
-    if dist is None:
-        return [float(v) for v in values]
+def plugin_order_rate(dev, caps, frames, boxes, dev_pts, args):
+    """What a TensorRT engine built from the reference's graph would get from this library: ONE pipeline on ONE
+    stream, every node in ONNX order through the plugin-level entry points only (d3d_spconv_index_enqueue once per
+    rulebook, d3d_spconv_mm_enqueue per layer -- which rebuilds its neighbour table in its own workspace every
+    time --, ReLU / residual add as separate element-wise kernels, NMS after the backbone), captured in a CUDA graph
+    with programmatic dependent launch on.  Frames per second with the inputs resident in HBM."""
     import torch
-    t = torch.tensor([float(v) for v in values], dtype=torch.float64, device=device)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return [float(v) for v in t]
+    from deploy3d_b200.pipeline import DetectionPipeline
+    q = DetectionPipeline("centerpoint", dev, caps=caps, kernel=args.kernel, plugin_order=True)
+    q.load_frame(frames[0], boxes)
+    q.capture()
+    n = max(20, min(args.steps * FRAMES_PER_STEP, 100))
+    for i in range(5):
+        q.points.copy_(dev_pts[i % N_ROTATE], non_blocking=True)
+        q.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(n):
+        q.points.copy_(dev_pts[i % N_ROTATE], non_blocking=True)
+        q.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / n
+    del q
+    torch.cuda.empty_cache()
+    return {"frames_per_s": 1e3 / ms, "ms_per_frame": ms, "frames": n,
+            "what": "one pipeline, one stream, plugin-level enqueue of every node in graph order (neighbour table "
+                    "rebuilt by each of the 21 SPConvMM nodes), separate ReLU / add kernels, CUDA graph, dependent launch"}
+
+
+def gather_ranks(values, dist):
+    """[rank][i] of `values` from every rank (identity without a process group).  The frames are independent
+    replicas: this exchange of timings is the only inter-rank traffic, and it goes over the host."""
+    if dist is None:
+        return [[float(v) for v in values]]
+    import torch
+    mine = torch.tensor([float(v) for v in values], dtype=torch.float64)
+    out = [torch.zeros_like(mine) for _ in range(dist.get_world_size())]
+    dist.all_gather(out, mine)
+    return [[float(v) for v in t] for t in out]
 
 
 def aggregate_frames_per_second(world, steps, frames_per_step, elapsed_max):
@@ -504,7 +559,7 @@ def count_launches(pipe):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20, help="timed steps of %d frames per GPU each" % FRAMES_PER_STEP)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--kernel", type=int, default=0, help="SPConvMM kernel: 0 auto, 1 SIMT, 2 tcgen05")
@@ -512,6 +567,9 @@ def main():
                     help="pipelines (buffers + CUDA graph + stream each) that take the frames in turn")
     ap.add_argument("--layers", action="store_true", help="print the per-layer SPConvMM table to stderr")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-plugin-order", action="store_true", help="skip the single-stream plugin-order figure")
+    ap.add_argument("--no-reference-gpu", action="store_true",
+                    help="skip timing the reference's CUDA kernels (oracle/_ref) beside this library's")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -115,8 +115,14 @@ class SparseNet:
     """
 
     def __init__(self, layers, spatial, caps, dtype=torch.float16, device="cuda:0", seed=0, kernel=0,
-                 pad_input=True, overlap_rulebooks=False):
+                 pad_input=True, overlap_rulebooks=False, plugin_order=False):
         self.layers, self.device, self.dtype = layers, torch.device(device), dtype
+        # plugin order: what a TensorRT engine built from the reference's ONNX graph executes -- one stream, every
+        # SPConvMM node through the plugin-level enqueue (which rebuilds its neighbour table in its own workspace,
+        # trt/spconv/mm_trt.cu:149-205 has no state shared between nodes), ReLU / residual add as separate
+        # element-wise layers after the plugin (tests/cylinder/test_cylinder3d.py:91-92)
+        self.plugin_order = plugin_order
+        overlap_rulebooks = overlap_rulebooks and not plugin_order
         self.overlap_rulebooks = overlap_rulebooks
         self.side = torch.cuda.Stream(device=self.device) if overlap_rulebooks else None
         self.side_subm = torch.cuda.Stream(device=self.device) if overlap_rulebooks else None
@@ -164,14 +170,15 @@ class SparseNet:
                     if not subm:
                         out["coors"] = torch.zeros((out["cap"], 4), dtype=torch.int32, device=self.device)
                         out["num"] = torch.zeros(1, dtype=torch.int32, device=self.device)
-                    rb.table_fwd = torch.empty(max(SPConvMMPlugin.table_bytes(rb.kvol, out["cap"]), 16),
-                                               dtype=torch.uint8, device=self.device)
+                    rb.table_fwd = None if plugin_order else torch.empty(
+                        max(SPConvMMPlugin.table_bytes(rb.kvol, out["cap"]), 16), dtype=torch.uint8,
+                        device=self.device)
                     rb.table_inv = None
                     self.rulebooks[L.key] = rb
                 rb = self.rulebooks[L.key]
                 if L.kind == "inverse":
                     out_set, in_set = rb.in_set, rb.out_set
-                    if rb.table_inv is None:
+                    if rb.table_inv is None and not plugin_order:
                         rb.table_inv = torch.empty(
                             max(SPConvMMPlugin.table_bytes(rb.kvol, self.sets[out_set]["cap"]), 16),
                             dtype=torch.uint8, device=self.device)
@@ -213,6 +220,8 @@ class SparseNet:
         else:
             rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor,
                               outputs=[rb.index, rb.num_index, dst["coors"], dst["num"], rb.out_shape_tensor])
+        if self.plugin_order:
+            return  # every SPConvMM node builds its own table inside its enqueue
         SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd,
                                mirror=rb.mirror)
         if rb.table_inv is not None:
@@ -261,9 +270,19 @@ class SparseNet:
                 else:
                     self._build_rulebook(rb)
                 built.add(L.key)
-            table = rb.table_inv if L.kind == "inverse" else rb.table_fwd
             res = saved[L.residual] if L.residual else None
-            x = plug.run(x, self.sets[out_set]["num"], table, out=out_buf, relu=L.relu, residual=res)
+            if self.plugin_order:
+                in_set = rb.out_set if L.kind == "inverse" else rb.in_set
+                plug.enqueue(x, self.sets[in_set]["num"], self.sets[out_set]["num"], rb.index, rb.num_index,
+                             outputs=[out_buf])
+                if res is not None:
+                    out_buf.add_(res)
+                if L.relu:
+                    out_buf.relu_()
+                x = out_buf
+            else:
+                table = rb.table_inv if L.kind == "inverse" else rb.table_fwd
+                x = plug.run(x, self.sets[out_set]["num"], table, out=out_buf, relu=L.relu, residual=res)
             if L.save:
                 saved[L.save] = x
         if self.overlap_rulebooks:

@@ -20,8 +20,10 @@ class DetectionPipeline:
     """CenterPoint-shaped (``kind='centerpoint'``) or SECOND-shaped (``kind='second'``) frame pipeline."""
 
     def __init__(self, kind="centerpoint", device="cuda:0", caps=None, kernel=0, n_class=10, topk=1000,
-                 iou_threshold=0.2, dtype=torch.float16, n_pts=None, overlap_rulebooks=True):
+                 iou_threshold=0.2, dtype=torch.float16, n_pts=None, overlap_rulebooks=True, plugin_order=False):
         self.kind, self.device, self.dtype = kind, torch.device(device), dtype
+        # plugin order: one stream, nodes in ONNX order through the plugin-level entry points only (see SparseNet)
+        self.plugin_order = plugin_order
         if kind == "centerpoint":
             frame = synth.config4_points()
             self.layers = backbone.voxel_res_backbone_8x(5)
@@ -49,7 +51,7 @@ class DetectionPipeline:
             self.vox_num = torch.zeros(1, dtype=torch.int32, device=dev)
             spatial_b = [self.spatial[0]] + list(self.spatial[2:])
             self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel,
-                                          overlap_rulebooks=overlap_rulebooks)
+                                          overlap_rulebooks=overlap_rulebooks, plugin_order=plugin_order)
             # low-precision copy of the voxel features, zero-padded to the channel count the first layer runs with
             self.vox_feats_lp = torch.zeros((cap_in, self.net.in_channels), dtype=dtype, device=dev)
             self.net.set_input(self.vox_coors, self.vox_num)
@@ -107,16 +109,20 @@ class DetectionPipeline:
         NMS of frame i beside the backbone of frame i+1.)  The branch joins before enqueue returns, so the caller
         still sees one stream; inside a CUDA graph capture it becomes a fork / join of the graph."""
         main = torch.cuda.current_stream(self.device)
-        self.side.wait_stream(main)
-        with torch.cuda.stream(self.side):
-            self.nms.enqueue(self.scores, self.boxes, outputs=[self.nms_scores])
+        if not self.plugin_order:
+            self.side.wait_stream(main)
+            with torch.cuda.stream(self.side):
+                self.nms.enqueue(self.scores, self.boxes, outputs=[self.nms_scores])
         self.vfe.enqueue(self.points, self.batch, self.cfg, self.shape_tensor,
                          outputs=[self.vox_feats, self.vox_coors, self.vox_num])
         # fp32 -> fp16 reformat (TensorRT inserts this layer itself); padding columns stay zero
         self.vox_feats_lp[:, :self.c_pts].copy_(self.vox_feats)
         feats, coors, num = self.net.forward(self.vox_feats_lp)
         self.densify.enqueue(feats, coors, num, self.out_shape_tensor, outputs=[self.bev])
-        main.wait_stream(self.side)
+        if self.plugin_order:
+            self.nms.enqueue(self.scores, self.boxes, outputs=[self.nms_scores])
+        else:
+            main.wait_stream(self.side)
         return feats, coors, num
 
     def capture(self):

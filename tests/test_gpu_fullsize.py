@@ -1,0 +1,211 @@
+"""Full-size parity on the benchmark frames: every rulebook and every convolution layer of the CenterPoint-shaped
+(config 4: 300 000 points -> about 281 000 voxels, 21 layers, fp16) and SECOND-shaped (config 3) backbones against
+the reference's own GPU code (trt/spconv/index.cu and trt/spconv/mm.h compiled for sm_100a into
+oracle/_ref/libref_spconv.so), on the tensors the product pipeline actually produced, plus the run-twice byte
+identity of the tensor-core convolution.
+
+Every layer is compared on its own: both sides get the product's input activation of that layer, so rounding does
+not compound through the network.  The reference convolution has no fused ReLU / residual (separate graph ops
+there, tests/cylinder/test_cylinder3d.py:91-92): they are applied to its output here.  Tolerances are those of the
+reference's own test (rtol 1e-2, atol 1e-1, tests/spconv/test_spconv.py:152-162) plus a relative L2 bound."""
+import numpy as np
+import pytest
+import torch
+
+from tests._util import pairs_equal
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ref():
+    from oracle import ref_gpu
+    L = ref_gpu.lib()
+    if L is None or not L.has_mm:
+        pytest.skip("oracle/_ref/libref_spconv.so (rulebooks and convolution) was not built")
+    return ref_gpu
+
+
+def _pipeline(kind):
+    from deploy3d_b200 import synth
+    from deploy3d_b200.pipeline import DetectionPipeline
+    frame = synth.config4_points() if kind == "centerpoint" else synth.config3_points()
+    boxes = synth.config4_boxes()
+    probe = DetectionPipeline(kind, DEV)
+    probe.load_frame(frame, boxes)
+    caps = probe.calibrate([frame])
+    del probe
+    torch.cuda.empty_cache()
+    pipe = DetectionPipeline(kind, DEV, caps=caps, overlap_rulebooks=False)
+    pipe.load_frame(frame, boxes)
+    pipe.enqueue()
+    torch.cuda.synchronize()
+    return pipe
+
+
+@pytest.fixture(scope="module", params=["centerpoint", "second"])
+def pipe(request):
+    p = _pipeline(request.param)
+    yield p
+    del p
+    torch.cuda.empty_cache()
+
+
+def test_every_rulebook_matches_reference_gpu(d3d, orc, ref, pipe):
+    """All rulebooks of the frame at full size: SubM byte for byte (padding included), strided after the
+    canonicalisation the reference's own test performs (output coordinate sets and every per-offset pair list)."""
+    net = pipe.net
+    counts = net.counts()
+    counts["in"] = int(pipe.vox_num.item())
+    checked = 0
+    for key, rb in net.rulebooks.items():
+        src, dst = net.sets[rb.in_set], net.sets[rb.out_set]
+        n = int(src["num"].item())
+        coors = src["coors"][:n].contiguous()
+        lay = next(l for l in net.layers if l.key == key)
+        subm = rb.kind == "subm"
+        want = ref.spconv_index(coors, src["cap"], dst["shape"], lay.ksize, lay.stride, lay.padding, (1, 1, 1),
+                                dst["cap"], subm, False)
+        got_num, want_num = int(rb.num_index.item()), int(want[1].item())
+        assert got_num == want_num, key
+        if subm:
+            assert torch.equal(rb.index, want[0]), "SubM rulebook %s differs from the reference's byte for byte" % key
+        else:
+            got_out, want_out = int(dst["num"].item()), int(want[3].item())
+            assert got_out == want_out and want_out < dst["cap"], key
+            gc, gp, _ = orc.canonical_conv(rb.index.cpu().numpy(), got_num, dst["coors"].cpu().numpy(), got_out,
+                                           rb.kvol)
+            wc, wp, _ = orc.canonical_conv(want[0].cpu().numpy(), want_num, want[2].cpu().numpy(), want_out, rb.kvol)
+            assert (gc == wc).all(), "output coordinate set of %s differs from the reference's" % key
+            pairs_equal(gp, wp, rb.kvol)
+        checked += 1
+        del want
+    assert checked == len(net.rulebooks) == 8
+
+
+def _exact_layer(x, w_t, b_t, index, num_index, inverse, rows):
+    """fp32 restatement on the GPU of what the layer computes: out = bias; out[scatter] += in[gather] @ W[k] per
+    kernel offset (the torch loop of the reference's test, tests/spconv/test_spconv.py:152-161), on the fp16
+    operands both implementations get."""
+    n = int(num_index.item())
+    g, s_, k = (index[1], index[0], index[2]) if inverse else (index[0], index[1], index[2])
+    g, s_, k = g[:n].long(), s_[:n].long(), k[:n].long()
+    out = b_t.float().repeat(rows, 1)
+    xf, wf = x.float(), w_t.float()
+    for off in range(w_t.shape[0]):
+        sel = (k == off).nonzero(as_tuple=True)[0]
+        if sel.numel():
+            out.index_add_(0, s_[sel], xf[g[sel]] @ wf[off])
+    return out
+
+
+def test_every_layer_matches_reference_gpu(d3d, ref, pipe):
+    """Every convolution layer of the backbone at full size: against the reference's indexedSpConv (fp16 atomics)
+    and against the fp32 restatement.  The product must sit within 1e-2 (relative to |value| + RMS) of the fp32
+    result and no further from it than the reference; product and reference must agree at the reference's own test
+    tolerance on all but a vanishing share of the elements (a chain of 27 half-precision atomic adds leaves a few
+    of the tens of millions of elements outside it) and within 5e-3 in relative L2."""
+    from deploy3d_b200.backbone import make_weights
+    net = pipe.net
+    weights = make_weights(net.layers, 0)
+    saved, x = {}, pipe.vox_feats_lp
+    report = []
+    for li, (lay, (plug, out_buf, out_set)) in enumerate(zip(net.layers, net.mm)):
+        if lay.source is not None:
+            x = saved[lay.source]
+        rb = net.rulebooks[lay.key]
+        inverse = lay.kind == "inverse"
+        table = rb.table_inv if inverse else rb.table_fwd
+        res = saved[lay.residual] if lay.residual else None
+        w, b = weights[li]
+        if w.shape[1] != x.shape[1]:  # the first layer's input is zero-padded to 16 channels
+            wp = np.zeros((w.shape[0], x.shape[1], w.shape[2]), dtype=np.float32)
+            wp[:, :w.shape[1]] = w
+            w = wp
+        w_t = torch.from_numpy(w).to(DEV, torch.float16)
+        b_t = torch.from_numpy(np.asarray(b, dtype=np.float32)).to(DEV, torch.float16)
+        cap = net.sets[out_set]["cap"]
+        m = int(net.sets[out_set]["num"].item())
+
+        def finish(t):
+            t = t.float()
+            if res is not None:
+                t = t + res.float()
+            return torch.relu(t) if lay.relu else t
+
+        # the reference's add / ReLU are half-precision graph ops: their result is rounded to fp16 like the product's
+        want = finish(ref.spconv_mm(x, w_t, b_t, rb.index, rb.num_index, inverse, cap))[:m].half().float()
+        exact = finish(_exact_layer(x, w_t, b_t, rb.index, rb.num_index, inverse, cap))[:m]
+        got = plug.run(x, net.sets[out_set]["num"], table, out=out_buf, relu=lay.relu, residual=res)
+        torch.cuda.synchronize()
+        g = got[:m].float()
+        rms = float(torch.sqrt((exact ** 2).mean())) + 1e-30
+        worst_vs_exact = float(((g - exact).abs() / (exact.abs() + rms)).max())
+        outside = float(((g - want).abs() > 1e-1 + 1e-2 * want.abs()).float().mean())
+        l2_ref = float(torch.sqrt(((g - want) ** 2).sum() / (want ** 2).sum().clamp_min(1e-30)))
+        err_got = float(torch.sqrt(((g - exact) ** 2).sum()))
+        err_ref = float(torch.sqrt(((want - exact) ** 2).sum()))
+        report.append((li, w.shape[1], w.shape[2], m, worst_vs_exact, outside, l2_ref, err_got, err_ref))
+        x = got
+        if lay.save:
+            saved[lay.save] = x
+        del want, exact, g
+    table_txt = "\n".join("layer %2d %3d->%3d M=%7d  worst vs fp32 %.2e  outside ref tolerance %.2e  relL2 vs ref %.2e"
+                          "  |err| ours %.3e reference %.3e" % r for r in report)
+    for li, _, _, _, worst, outside, l2_ref, err_got, err_ref in report:
+        assert worst <= 1e-2, "layer %d leaves the fp32 result by more than 1e-2\n%s" % (li, table_txt)
+        assert outside <= 1e-4, "layer %d: too many elements outside the reference test's tolerance\n%s" % (li, table_txt)
+        assert l2_ref < 5e-3, "layer %d: relative L2 distance to the reference\n%s" % (li, table_txt)
+        assert err_got <= 1.05 * err_ref + 1e-6, "layer %d: further from fp32 than the reference\n%s" % (li, table_txt)
+    print(table_txt)
+
+
+@pytest.mark.parametrize("cin,cout,residual", [(16, 16, False), (32, 64, True), (64, 64, True), (128, 128, False),
+                                               (256, 128, True)])
+def test_tensor_core_convolution_is_deterministic(d3d, cin, cout, residual):
+    """The same launch twice gives the same bytes (no atomics, fixed accumulation order), with one and with two CTAs
+    per SM; the reference scatters with half-precision atomics and has no such property
+    (trt/spconv/mm/output_iterator.h:189-206)."""
+    from deploy3d_b200 import synth
+    from deploy3d_b200.ops import data_s_spconv_index, data_s_spconv_mm
+    from deploy3d_b200.plugins import SPConvMMPlugin, deserialize_plugin
+    r = np.random.Generator(np.random.PCG64(99 + cin))
+    vox = synth.lidar_like_voxels(r, 40000, (21, 300, 300))
+    n = len(vox)
+    coors = torch.from_numpy(np.concatenate([np.zeros((n, 1), np.int32), vox], 1)).to(DEV)
+    num = torch.tensor([n], dtype=torch.int32, device=DEV)
+    shape = torch.empty([1, 0, 21, 300, 300], dtype=torch.int32, device=DEV)
+    ip = deserialize_plugin("SPConvIdx3d", data_s_spconv_index((3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), (0, 0, 0),
+                                                                n, True, False))
+    index, num_index = ip.enqueue(coors, num, shape)
+    table = SPConvMMPlugin.prepare(27, False, n, index, num_index)
+    w = synth.kaiming_weight(r, 27, cin, cout)
+    b = (r.standard_normal(cout) * 0.1).astype(np.float32)
+    x = torch.randn((n, cin), device=DEV).half()
+    res = torch.randn((n, cout), device=DEV).half() if residual else None
+    first = None
+    for which in (2, 3):
+        plug = deserialize_plugin("SPConvMM", data_s_spconv_mm((3, 3, 3), cin, cout, n, True, False, w, b))
+        plug.configure(torch.float16)
+        plug.set_kernel(which)
+        for _ in range(3):
+            y = plug.run(x, num, table, relu=True, residual=res)
+            torch.cuda.synchronize()
+            if first is None:
+                first = y.clone()
+            assert torch.equal(y, first), "kernel choice %d: output bytes changed between runs" % which
+
+
+def test_whole_frame_twice_is_identical(d3d):
+    """Two runs of the same config-4 frame through the pipeline: identical rulebooks, features and BEV map."""
+    p = _pipeline("centerpoint")
+    feats, coors, num = p.enqueue()
+    torch.cuda.synchronize()
+    snap = [t.clone() for t in (feats, coors, num, p.bev, p.nms_scores)] + [rb.index.clone()
+                                                                           for rb in p.net.rulebooks.values()]
+    feats, coors, num = p.enqueue()
+    torch.cuda.synchronize()
+    again = [feats, coors, num, p.bev, p.nms_scores] + [rb.index for rb in p.net.rulebooks.values()]
+    for a, b in zip(snap, again):
+        assert torch.equal(a, b)

@@ -1,5 +1,6 @@
-"""The multi-GPU path is frame replication: ranks never exchange data, only the timings are reduced (max over
-ranks) and the frame counts summed.  That host logic is exercised here with two gloo ranks on the CPU."""
+"""The multi-GPU path is frame replication: ranks never exchange data, only the timings are gathered over the host
+(the slowest rank decides) and the frame counts summed.  That host logic -- the very gloo group bench.py uses --
+is exercised here with two ranks on the CPU."""
 import os
 import subprocess
 import sys
@@ -15,11 +16,14 @@ WORKER = textwrap.dedent("""
     dist.init_process_group("gloo")
     rank, world = dist.get_rank(), dist.get_world_size()
     # rank r pretends its timed region took (1 + r) seconds device-side and (2 + 3 r) seconds end to end
-    elapsed, e2e = bench.max_over_ranks([1.0 + rank, 2.0 + 3 * rank], dist, "cpu")
-    fps = bench.aggregate_frames_per_second(world, steps=10, frames_per_step=1, elapsed_max=elapsed)
+    per_rank = bench.gather_ranks([1.0 + rank, 2.0 + 3 * rank], dist)
+    elapsed, e2e = max(r[0] for r in per_rank), max(r[1] for r in per_rank)
+    fps = bench.aggregate_frames_per_second(world, steps=10, frames_per_step=bench.FRAMES_PER_STEP,
+                                            elapsed_max=elapsed)
     dist.barrier()
     if rank == 0:
-        print(json.dumps({"elapsed": elapsed, "e2e": e2e, "fps": fps, "world": world}))
+        print(json.dumps({"elapsed": elapsed, "e2e": e2e, "fps": fps, "world": world,
+                          "fastest": min(r[0] for r in per_rank)}))
     dist.destroy_process_group()
 """) % ROOT
 
@@ -35,13 +39,13 @@ def test_timings_reduce_to_the_slowest_rank(tmp_path):
     import json
     line = [ln for ln in out.stdout.splitlines() if ln.startswith("{")][-1]
     got = json.loads(line)
-    assert got == {"elapsed": 2.0, "e2e": 5.0, "fps": 10.0, "world": 2}
+    assert got == {"elapsed": 2.0, "e2e": 5.0, "fps": 100.0, "world": 2, "fastest": 1.0}
 
 
 def test_single_rank_is_identity():
     sys.path.insert(0, ROOT)
     import bench
-    assert bench.max_over_ranks([1.5, 2.5], None, "cpu") == [1.5, 2.5]
+    assert bench.gather_ranks([1.5, 2.5], None) == [[1.5, 2.5]]
     assert bench.aggregate_frames_per_second(1, 20, 1, 0.5) == 40.0
 
 
