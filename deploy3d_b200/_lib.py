@@ -98,6 +98,7 @@ SIGNATURES = {
     "d3d_spconv_mm_serialize": (ctypes.c_int, [_vp, _vp, _szp]),
     "d3d_spconv_mm_configure": (ctypes.c_int, [_vp, ctypes.c_int]),
     "d3d_spconv_mm_destroy": (ctypes.c_int, [_vp]),
+    "d3d_spconv_mm_output_desc": (ctypes.c_int, [_vp, _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_spconv_mm_workspace": (ctypes.c_int, _workspace_sig(_vp)),
     "d3d_spconv_mm_enqueue": (ctypes.c_int, _enqueue_sig(_vp)),
     "d3d_spconv_mm_table_bytes": (_sz, [ctypes.c_int, ctypes.c_int64]),
@@ -108,19 +109,25 @@ SIGNATURES = {
     "d3d_spconv_mm_set_kernel": (ctypes.c_int, [_vp, ctypes.c_int]),
     "d3d_spconv_mm_set_dependent_launch": (ctypes.c_int, [_vp, ctypes.c_int]),
     "d3d_bev_densify_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(BevDensifyParams)]),
+    "d3d_bev_densify_output_desc": (ctypes.c_int, [ctypes.POINTER(BevDensifyParams), _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_bev_densify_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(BevDensifyParams))),
     "d3d_bev_densify_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(BevDensifyParams))),
     "d3d_simple_mean_encoder_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(VoxelEncoderParams)]),
+    "d3d_simple_mean_encoder_output_desc": (ctypes.c_int, [ctypes.POINTER(VoxelEncoderParams), _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_simple_mean_encoder_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(VoxelEncoderParams))),
     "d3d_simple_mean_encoder_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(VoxelEncoderParams))),
     "d3d_cylinder_encoder_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(VoxelEncoderParams)]),
+    "d3d_cylinder_encoder_output_desc": (ctypes.c_int, [ctypes.POINTER(VoxelEncoderParams), _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_cylinder_encoder_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(VoxelEncoderParams))),
     "d3d_cylinder_encoder_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(VoxelEncoderParams))),
     "d3d_scatter_to_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(ScatterToParams)]),
+    "d3d_scatter_to_output_desc": (ctypes.c_int, [ctypes.POINTER(ScatterToParams), _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_scatter_to_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(ScatterToParams))),
     "d3d_gather_back_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(GatherBackParams)]),
+    "d3d_gather_back_output_desc": (ctypes.c_int, [ctypes.POINTER(GatherBackParams), _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_gather_back_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(GatherBackParams))),
     "d3d_nms3d_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(Nms3dParams)]),
+    "d3d_nms3d_output_desc": (ctypes.c_int, [ctypes.POINTER(Nms3dParams), _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_nms3d_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(Nms3dParams))),
     "d3d_nms3d_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(Nms3dParams))),
     "d3d_yolox3d_decode_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(YoloX3dDecodeParams)]),

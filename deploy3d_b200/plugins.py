@@ -48,8 +48,18 @@ class _Plugin:
     def _params_ref(self):
         raise NotImplementedError
 
+    num_outputs = 1
+
     def output_descs(self, in_descs):
-        raise NotImplementedError
+        """getOutputDimensions / getOutputDataType, from the library (one source with the TensorRT shells)."""
+        fn = getattr(lib(), self._prefix + "_output_desc")
+        outs = []
+        for i in range(self.num_outputs):
+            d = _lib.TensorDesc()
+            check(self._prefix + "_output_desc", fn(self._params_ref(), desc_array(in_descs), len(in_descs), i,
+                                                    ctypes.byref(d)))
+            outs.append(d)
+        return outs
 
     def workspace_size(self, in_descs):
         fn = getattr(lib(), self._prefix + "_workspace", None)
@@ -149,9 +159,6 @@ class SPConvMMPlugin(_Plugin):
         check("d3d_spconv_mm_serialize", lib().d3d_spconv_mm_serialize(self.handle, buf, ctypes.byref(n)))
         return buf.raw
 
-    def output_descs(self, in_descs):
-        return [make_desc(in_descs[0].dtype, (self.p.max_num_act_out, self.p.out_channels))]
-
     def enqueue(self, *inputs, outputs=None, stream=None):
         """configurePlugin for the dtype of ``inFeats`` (a no-op when already done), then enqueue: the C entry
         point itself refuses a handle that was not configured, as it may not allocate."""
@@ -228,19 +235,13 @@ class BEVDensifyPlugin(_PodPlugin):
     _prefix = "d3d_bev_densify"
     _params_t = _lib.BevDensifyParams
 
-    def output_descs(self, d):
-        return [make_desc(d[0].dtype, (d[3].dims[0], self.p.out_channels, d[3].dims[3], d[3].dims[4]))]
-
 
 class SimpleMeanEncoderPlugin(_PodPlugin):
     """``SimpleMeanEncoder`` (trt/voxel_encoder/simple_mean_trt.cu:181-314)."""
     name = "SimpleMeanEncoder"
     _prefix = "d3d_simple_mean_encoder"
     _params_t = _lib.VoxelEncoderParams
-
-    def output_descs(self, d):
-        m = self.p.max_num_act_out
-        return [make_desc(d[0].dtype, (m, d[0].dims[1])), make_desc(D3D_INT32, (m, 4)), make_desc(D3D_INT32, (1,))]
+    num_outputs = 3
 
 
 class CylinderEncoderPlugin(_PodPlugin):
@@ -248,11 +249,7 @@ class CylinderEncoderPlugin(_PodPlugin):
     name = "CylinderEncoder"
     _prefix = "d3d_cylinder_encoder"
     _params_t = _lib.VoxelEncoderParams
-
-    def output_descs(self, d):
-        m, n = self.p.max_num_act_out, d[0].dims[0]
-        return [make_desc(d[0].dtype, (n, d[0].dims[1] + 5)), make_desc(D3D_INT32, (n,)), make_desc(D3D_INT32, (m,)),
-                make_desc(D3D_INT32, (m, 4)), make_desc(D3D_INT32, (1,))]
+    num_outputs = 5
 
 
 class ScatterToPlugin(_PodPlugin):
@@ -261,9 +258,6 @@ class ScatterToPlugin(_PodPlugin):
     _prefix = "d3d_scatter_to"
     _params_t = _lib.ScatterToParams
 
-    def output_descs(self, d):
-        return [make_desc(d[0].dtype, (d[2].dims[0], d[0].dims[1]))]
-
 
 class GatherBackPlugin(_PodPlugin):
     """``GatherBack`` (trt/point_voxel_mapping/gather_back.cu:77-184)."""
@@ -271,18 +265,12 @@ class GatherBackPlugin(_PodPlugin):
     _prefix = "d3d_gather_back"
     _params_t = _lib.GatherBackParams
 
-    def output_descs(self, d):
-        return [make_desc(d[0].dtype, (d[1].dims[0],) + tuple(d[0].dims[1:d[0].nb_dims]))]
-
 
 class NMS3dPlugin(_PodPlugin):
     """``NMS3d`` (trt/decoder/nms3d.cu:135-236).  ``iou_threshold`` is fixed to 0.1 by the reference."""
     name = "NMS3d"
     _prefix = "d3d_nms3d"
     _params_t = _lib.Nms3dParams
-
-    def output_descs(self, d):
-        return [make_desc(D3D_FLOAT, tuple(d[0].dims[:d[0].nb_dims]))]
 
 
 class YoloX3dDecodePlugin(_PodPlugin):

@@ -151,6 +151,9 @@ int d3d_spconv_mm_serialize(d3d_spconv_mm_t handle, void* buffer, size_t* len);
 /* configurePlugin: convert weights to `dtype` and upload them to the current device (allocates). */
 int d3d_spconv_mm_configure(d3d_spconv_mm_t handle, int dtype);
 int d3d_spconv_mm_destroy(d3d_spconv_mm_t handle);
+/* getOutputDimensions / getOutputDataType (mm_trt.cu:96-105) with concrete dims */
+int d3d_spconv_mm_output_desc(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int n_in, int index,
+                              d3d_tensor_desc* out);
 /* The reference needs no workspace (mm_trt.cu:143-148); this implementation keeps an
  * output-stationary neighbour table [ceil(maxNumActOut/128), kVol, 128] there. */
 int d3d_spconv_mm_workspace(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int n_in, size_t* bytes);
@@ -196,6 +199,9 @@ typedef struct {
   int32_t out_channels;
 } d3d_bev_densify_params;
 int d3d_bev_densify_parse(const void* data_s, size_t len, d3d_bev_densify_params* p);
+/* getOutputDimensions / getOutputDataType (bev_densify_trt.cu:93-108) */
+int d3d_bev_densify_output_desc(const d3d_bev_densify_params* p, const d3d_tensor_desc* in, int n_in, int index,
+                                d3d_tensor_desc* out);
 int d3d_bev_densify_workspace(const d3d_bev_densify_params* p, const d3d_tensor_desc* in, int n_in, size_t* bytes);
 int d3d_bev_densify_enqueue(const d3d_bev_densify_params* p, const d3d_tensor_desc* in, int n_in,
                             const d3d_tensor_desc* out, int n_out, const void* const* inputs,
@@ -213,6 +219,9 @@ typedef struct {
   int32_t max_num_act_out;
 } d3d_voxel_encoder_params;
 int d3d_simple_mean_encoder_parse(const void* data_s, size_t len, d3d_voxel_encoder_params* p);
+/* getOutputDimensions / getOutputDataType (simple_mean_trt.cu:220-245) */
+int d3d_simple_mean_encoder_output_desc(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
+                                        int index, d3d_tensor_desc* out);
 int d3d_simple_mean_encoder_workspace(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
                                       size_t* bytes);
 int d3d_simple_mean_encoder_enqueue(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
@@ -228,6 +237,9 @@ int d3d_simple_mean_encoder_enqueue(const d3d_voxel_encoder_params* p, const d3d
  *          3 outCoors int32 [maxNumActOut, 4] (b,rho,phi,z), 4 numActOut int32[1]
  * ------------------------------------------------------------------------------------------- */
 int d3d_cylinder_encoder_parse(const void* data_s, size_t len, d3d_voxel_encoder_params* p);
+/* getOutputDimensions / getOutputDataType (cylinder_trt.cu:226-259) */
+int d3d_cylinder_encoder_output_desc(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in, int index,
+                                     d3d_tensor_desc* out);
 int d3d_cylinder_encoder_workspace(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
                                    size_t* bytes);
 int d3d_cylinder_encoder_enqueue(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
@@ -254,6 +266,11 @@ typedef struct {
   float fill_val;
 } d3d_gather_back_params;
 int d3d_scatter_to_parse(const void* data_s, size_t len, d3d_scatter_to_params* p);
+/* getOutputDimensions / getOutputDataType (scatter_to.cu:152-160, gather_back.cu:110-120) */
+int d3d_scatter_to_output_desc(const d3d_scatter_to_params* p, const d3d_tensor_desc* in, int n_in, int index,
+                               d3d_tensor_desc* out);
+int d3d_gather_back_output_desc(const d3d_gather_back_params* p, const d3d_tensor_desc* in, int n_in, int index,
+                                d3d_tensor_desc* out);
 int d3d_scatter_to_enqueue(const d3d_scatter_to_params* p, const d3d_tensor_desc* in, int n_in,
                            const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                            void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
@@ -274,6 +291,9 @@ typedef struct {
   float iou_threshold;
 } d3d_nms3d_params;
 int d3d_nms3d_parse(const void* data_s, size_t len, d3d_nms3d_params* p);
+/* getOutputDimensions / getOutputDataType (nms3d.cu:166-176) */
+int d3d_nms3d_output_desc(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in, int index,
+                          d3d_tensor_desc* out);
 int d3d_nms3d_workspace(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in, size_t* bytes);
 int d3d_nms3d_enqueue(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in, const d3d_tensor_desc* out,
                       int n_out, const void* const* inputs, void* const* outputs, void* workspace,
