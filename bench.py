@@ -212,7 +212,8 @@ def conv_launch_times(pipe, frames, reps):
     import torch
     from deploy3d_b200.plugins import SPConvMMPlugin
     net = pipe.net
-    n_layers = len(net.layers)
+    n_layers = sum(1 for L in net.layers if L.kind != "ew")
+    conv_layers = [L for L in net.layers if L.kind != "ew"]
     acc = np.zeros(n_layers)
     work = None
     for r in range(reps):
@@ -221,8 +222,18 @@ def conv_launch_times(pipe, frames, reps):
         torch.cuda.synchronize()
         if work is None:
             work = net.layer_work()
-        saved, x = {}, pipe.vox_feats_lp
-        for li, (L, (plug, out_buf, out_set)) in enumerate(zip(net.layers, net.mm)):
+        saved, x = {"input": pipe.vox_feats_lp}, pipe.vox_feats_lp
+        ci = -1
+        for L, (plug, out_buf, out_set) in zip(net.layers, net.mm):
+            if L.kind == "ew":  # element-wise graph op between plugins: not a convolution launch
+                from deploy3d_b200.backbone import ew_apply
+                out_buf.copy_(ew_apply(L.ew[0], [saved[t].float() for t in L.ew[1]], torch))
+                x = out_buf
+                if L.save:
+                    saved[L.save] = x
+                continue
+            ci += 1
+            li = ci
             if L.source is not None:
                 x = saved[L.source]
             rb = net.rulebooks[L.key]
@@ -232,10 +243,10 @@ def conv_launch_times(pipe, frames, reps):
             # bracket kernel time and not the host's launch path
             xin = x
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            x = plug.run(xin, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu, residual=res)
+            x = plug.run(xin, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res)
             e0.record()
             for _ in range(INNER_LAUNCHES):
-                x = plug.run(xin, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu, residual=res)
+                x = plug.run(xin, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res)
             e1.record()
             e1.synchronize()
             acc[li] += e0.elapsed_time(e1) * 1e-3 / INNER_LAUNCHES
@@ -248,7 +259,7 @@ def conv_launch_times(pipe, frames, reps):
         out.append(dict(layer=li, cin=cin, cout=cout, kvol=kvol, m=m, pairs=pairs, seconds=t,
                         flops_dense=2.0 * m * kvol * cin * cout, flops_pair=2.0 * pairs * cin * cout,
                         bytes=m * cin * esz + m * cout * esz + kvol * cin * cout * esz + 4.0 * kvol * m +
-                        (m * cout * esz if net.layers[li].residual else 0)))
+                        (m * cout * esz if conv_layers[li].residual else 0)))
     return out
 
 
@@ -494,6 +505,146 @@ def run_ours(args):
     return line
 
 
+METRIC5 = "sparse segmentation frames/s (Cylinder3D-shaped frame, fp16)"
+WORKLOAD5 = ("config5: batch of 8 frames x 120000 pts x4 -> CylinderEncoder 480x360x32 -> ScatterTo(max) -> asymmetric "
+             "3x1x3/1x3x3 SubM encoder-decoder 32/64/128/256 fp16 -> 20-class logits -> GatherBack -> argmax")
+BATCH5 = 8
+
+
+def run_config5(args):
+    """Benchmark config 5: a batch of 8 Cylinder3D-shaped frames sharded over the GPUs (8, 4, 2 or 1 frames per GPU
+    and step), one pipeline pair per GPU, no exchange between GPUs.  One step = the whole batch; `value` is the
+    whole job's frames per second (strong scaling: the batch is fixed)."""
+    import torch
+    from deploy3d_b200 import _lib, synth
+    from deploy3d_b200.pipeline import SegmentationPipeline
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if BATCH5 % world:
+        raise SystemExit("config 5 shards a batch of %d frames: --gpus must divide it" % BATCH5)
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
+    _lib.lib()
+    torch.cuda.set_device(local)
+    dev = "cuda:%d" % local
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("gloo")
+    share = BATCH5 // world
+    frames = [synth.config5_points(rank * share + i) for i in range(share)]
+    all_frames = frames if world == 1 else [synth.config5_points(i) for i in range(BATCH5)]
+    probe = SegmentationPipeline(dev)
+    caps = {k: (probe.n_pts if k == "in" else 3 * probe.n_pts) for k in probe.set_names}
+    del probe
+    probe = SegmentationPipeline(dev, caps=caps)
+    caps = probe.calibrate(all_frames)  # every rank sizes its buffers for the whole batch: identical engines
+    del probe
+    torch.cuda.empty_cache()
+    n_pipes = max(1, args.in_flight)
+    pipes = []
+    for _ in range(n_pipes):
+        q = SegmentationPipeline(dev, caps=caps)
+        q.load_frame(frames[0])
+        q.capture()
+        pipes.append(q)
+    streams = [torch.cuda.Stream(device=dev) for _ in range(n_pipes)]
+    main = torch.cuda.current_stream()
+    dev_pts = [torch.from_numpy(f["points"]).to(dev) for f in frames]
+    host_pts = [torch.from_numpy(f["points"]).pin_memory() for f in frames]
+    host_labels = [torch.zeros(pipes[0].n_pts, dtype=torch.int32).pin_memory() for _ in range(2)]
+    torch.cuda.synchronize()
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+
+    def loop(steps, e2e):
+        for st in streams:
+            st.wait_stream(main)
+        for i in range(steps * share):
+            k = i % n_pipes
+            with torch.cuda.stream(streams[k]):
+                if e2e:
+                    pipes[k].points.copy_(host_pts[i % share], non_blocking=True)
+                else:
+                    pipes[k].points.copy_(dev_pts[i % share], non_blocking=True)
+                pipes[k].replay()
+                if e2e:
+                    host_labels[k % 2].copy_(pipes[k].labels, non_blocking=True)
+        for st in streams:
+            main.wait_stream(st)
+
+    results = []
+    clocks = None
+    for e2e in (False, True):
+        loop(args.warmup, e2e)
+        barrier()
+        sampler = ClockSampler(local)
+        if rank == 0 and not e2e:
+            sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        loop(args.steps, e2e)
+        e1.record()
+        barrier()
+        results.append(e0.elapsed_time(e1) * 1e-3)
+        if rank == 0 and not e2e:
+            clocks = sampler.stop()
+    per_rank = gather_ranks(results, dist)
+    elapsed_all = [r[0] for r in per_rank]
+    elapsed, e2e_elapsed = max(elapsed_all), max(r[1] for r in per_rank)
+    if rank == 0:
+        peaks = measured_peaks()
+        pipe = pipes[0]
+        layers = conv_launch_times(pipe, frames, reps=2)
+        t_conv = sum(l["seconds"] for l in layers)
+        achieved = sum(l["flops_dense"] for l in layers) / t_conv / 1e12
+        labels = host_labels[0].numpy()
+        if not (labels.max() > 0 and labels.min() >= 0 and labels.max() < pipe.n_class):
+            raise RuntimeError("end-to-end labels look wrong")
+        line = {
+            "metric": METRIC5, "value": BATCH5 * args.steps / elapsed, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed / args.steps * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp16 (fp32 accumulate)",
+            "data": "synthetic",
+            "config": {"workload": WORKLOAD5, "frames_per_gpu_per_step": share, "batch": BATCH5,
+                       "ms_per_frame_per_gpu": elapsed / (args.steps * share) * 1e3,
+                       "parallelism": "batch of %d frames sharded %d per GPU (no collective)" % (BATCH5, share),
+                       "frames_in_flight_per_gpu": n_pipes,
+                       "voxels": {k: int(v) for k, v in pipe.net.counts().items()},
+                       "conv_layers": len(layers),
+                       "rank_seconds": {"min": min(elapsed_all), "median": float(np.median(elapsed_all)),
+                                        "max": max(elapsed_all)}},
+            "clocks": clocks,
+            "e2e": {"value": BATCH5 * args.steps / e2e_elapsed, "unit": UNIT,
+                    "h2d_bytes_per_step": host_pts[0].numel() * 4 * share,
+                    "d2h_bytes_per_step": host_labels[0].numel() * 4 * share,
+                    "ms_per_step": e2e_elapsed / args.steps * 1e3},
+            "gpu_launches": None,
+            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                         "frac": achieved / peaks["bf16_tflops"], "traffic": None,
+                         "algorithmic_bytes": sum(l["bytes"] for l in layers) / len(layers),
+                         "kernel": "SPConvMM (tcgen05) over the %d convolution layers of the network, dense-equivalent "
+                                   "FLOPs, time = sum of per-launch CUDA-event durations" % len(layers),
+                         "peak_source": peaks["source"] + ", burst bf16",
+                         "useful_tflops": sum(l["flops_pair"] for l in layers) / t_conv / 1e12,
+                         "conv_ms_per_frame": t_conv * 1e3},
+            "cpu_baseline": None,
+        }
+        if args.layers:
+            for l in layers:
+                sys.stderr.write("layer %2d  %3d->%3d k%2d  M=%7d P=%8d  %8.1f us  %7.2f TF/s dense  %6.2f TF/s pair\n"
+                                 % (l["layer"], l["cin"], l["cout"], l["kvol"], l["m"], l["pairs"], l["seconds"] * 1e6,
+                                    l["flops_dense"] / l["seconds"] / 1e12, l["flops_pair"] / l["seconds"] / 1e12))
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def plugin_order_rate(dev, caps, frames, boxes, dev_pts, args):
     """What a TensorRT engine built from the reference's graph would get from this library: ONE pipeline on ONE
     stream, every node in ONNX order through the plugin-level entry points only (d3d_spconv_index_enqueue once per
@@ -562,6 +713,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20, help="timed steps of %d frames per GPU each" % FRAMES_PER_STEP)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="config4", choices=["config4", "config5"],
+                    help="config4: the headline CenterPoint-shaped frame; config5: the Cylinder3D-shaped batch of 8 "
+                         "frames sharded over the GPUs (this implementation only)")
     ap.add_argument("--kernel", type=int, default=0, help="SPConvMM kernel: 0 auto, 1 SIMT, 2 tcgen05")
     ap.add_argument("--in-flight", type=int, default=2,
                     help="pipelines (buffers + CUDA graph + stream each) that take the frames in turn")
@@ -574,6 +728,8 @@ def main():
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "config5":
+        run_config5(args)
     else:
         run_ours(args)
 

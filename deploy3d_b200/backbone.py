@@ -18,18 +18,41 @@ from .plugins import SPConvMMPlugin, deserialize_plugin
 class Layer:
     """One sparse convolution.
 
-    kind      'subm' | 'conv' (strided, creates a new voxel set) | 'inverse' (back to the inputs of `key`'s conv)
+    kind      'subm' | 'conv' (strided, creates a new voxel set) | 'inverse' (back to the inputs of `key`'s conv) |
+              'ew' (an element-wise graph op between plugins: `ew` = (name, [saved tags]); TensorRT-native layers in
+              the reference's graph, plain tensor ops here)
     key       rulebook name (``indice_key``); the first layer naming a key builds it
-    residual  name of a saved activation added before the ReLU (fused epilogue), or None
+    residual  name of a saved activation added to the result (fused epilogue), or None
+    act_first the ReLU comes before the residual add (sum of two activated branches) instead of after it
     save      name under which the output is kept for a later residual / skip connection
+    source    name of the saved activation the layer reads (default: the previous layer's output)
     """
 
     def __init__(self, kind, key, cin, cout, ksize=(3, 3, 3), stride=(1, 1, 1), padding=None, relu=True,
-                 residual=None, save=None, source=None):
+                 residual=None, save=None, source=None, act_first=False, ew=None):
         self.kind, self.key, self.cin, self.cout = kind, key, cin, cout
         self.ksize, self.stride = tuple(ksize), tuple(stride)
         self.padding = tuple(k // 2 for k in ksize) if padding is None else tuple(padding)
         self.relu, self.residual, self.save, self.source = relu, residual, save, source
+        self.act_first, self.ew = act_first, ew
+
+    @property
+    def relu_mode(self):
+        """The `relu` field of d3d_spconv_mm_epilogue."""
+        return 0 if not self.relu else (2 if self.act_first else 1)
+
+
+def ew_apply(name, xs, xp):
+    """The element-wise graph ops of the Cylinder3D-shaped network, for torch tensors (xp = torch) and numpy arrays
+    (xp = numpy) alike, in fp32: 'recon' = (sigmoid(a) + sigmoid(b) + sigmoid(c)) * x, the ReconBlock of
+    tests/cylinder/test_cylinder3d.py:181-205; 'concat' = channel concatenation (:262-263)."""
+    if name == "recon":
+        a, b, c, x = xs
+        sig = (lambda t: 1.0 / (1.0 + xp.exp(-t)))
+        return (sig(a) + sig(b) + sig(c)) * x
+    if name == "concat":
+        return xp.cat(xs, 1) if hasattr(xp, "cat") else xp.concatenate(xs, 1)
+    raise ValueError(name)
 
 
 def res_block(key, c, tag):
@@ -89,11 +112,68 @@ def seg_unet(cin, n_class=16):
     ]
 
 
+def cylinder3d(cin, n_class=20, init=32):
+    """Cylinder3D-shaped asymmetric encoder-decoder, channels init / 2 init / 4 init / 8 init (32 / 64 / 128 / 256),
+    composed as the reference composes it (tests/cylinder/test_cylinder3d.py:100-272): ResContextBlock, three
+    ResBlocks (two branches of 3x1x3 / 1x3x3 SubM convolutions over shared rulebooks, summed, then a strided
+    pooling convolution), three UpBlocks (3x3x3 SubM, inverse of the matching pooling convolution, skip connection,
+    1x3x3 / 3x1x3 / 3x3x3 SubM), ReconBlock (3x1x1, 1x3x1, 1x1x3 with sigmoid, summed, times the input), channel
+    concatenation and the 3x3x3 logits convolution.  Batch norm is folded into weight and bias (:24-37); the
+    activation is ReLU (the plugin has none: it is a graph op after it, :91-92)."""
+    k133, k313 = (1, 3, 3), (3, 1, 3)
+    c = init
+    L = [  # ResContextBlock: shortcut = conv1_2(conv1(x)); out = conv3(conv2(x)) + shortcut
+        Layer("subm", "res2_1", cin, c, ksize=k133, source="input"),
+        Layer("subm", "res1_1", c, c, ksize=k313, save="ctx_short"),
+        Layer("subm", "res1_1", cin, c, ksize=k313, source="input"),
+        Layer("subm", "res2_1", c, c, ksize=k133, residual="ctx_short", act_first=True, save="down0"),
+    ]
+    strides = [(2, 2, 2), (2, 2, 2), (2, 2, 1)]
+    for i in range(3):  # ResBlock i at stride 2^i: resA = conv3(conv2(x)) + conv1_2(conv1(x)); resB = pool(resA)
+        s = 1 << i
+        cout, src = 2 * c, "down%d" % i
+        L += [
+            Layer("subm", "res1_%d" % s, c, cout, ksize=k313, source=src),
+            Layer("subm", "res2_%d" % s, cout, cout, ksize=k133, save="short%d" % i),
+            Layer("subm", "res2_%d" % s, c, cout, ksize=k133, source=src),
+            Layer("subm", "res1_%d" % s, cout, cout, ksize=k313, residual="short%d" % i, act_first=True,
+                  save="skip%d" % i),
+            Layer("conv", "res_pool_%d" % s, cout, cout, stride=strides[i], padding=(1, 1, 1), relu=False,
+                  save="down%d" % (i + 1)),
+        ]
+        c = cout
+    for i in range(3):  # UpBlock at stride 4, 2, 1: up = inverse_pool(trans(x)) + skip; conv1, conv2, conv3
+        lvl = 2 - i
+        s = 1 << lvl
+        cout = c if i == 0 else c // 2
+        L += [
+            Layer("subm", "trans_dilao_%d" % s, c, cout),
+            Layer("inverse", "res_pool_%d" % s, cout, cout, relu=False, residual="skip%d" % lvl),
+            Layer("subm", "res2_%d" % s, cout, cout, ksize=k133),
+            Layer("subm", "res1_%d" % s, cout, cout, ksize=k313),
+            Layer("subm", "up3_%d" % s, cout, cout, save="up%d" % i),
+        ]
+        c = cout
+    L += [  # ReconBlock, concatenation, logits
+        Layer("subm", "rec1", c, c, ksize=(3, 1, 1), relu=False, source="up2", save="rec_a"),
+        Layer("subm", "rec1_2", c, c, ksize=(1, 3, 1), relu=False, source="up2", save="rec_b"),
+        Layer("subm", "rec1_3", c, c, ksize=(1, 1, 3), relu=False, source="up2", save="rec_c"),
+        Layer("ew", None, c, c, ew=("recon", ["rec_a", "rec_b", "rec_c", "up2"]), save="recon"),
+        Layer("ew", None, c, 2 * c, ew=("concat", ["recon", "up2"])),
+        Layer("subm", "logits", 2 * c, n_class, relu=False),
+    ]
+    return L
+
+
 def make_weights(layers, seed=0):
-    """Seeded Kaiming weights [kVol, Cin, Cout] and small biases (batch-norm folded) for every layer, in order."""
+    """Seeded Kaiming weights [kVol, Cin, Cout] and small biases (batch-norm folded) for every layer, in order
+    (None for the element-wise graph ops)."""
     rng = np.random.Generator(np.random.PCG64(4242 + seed))
     out = []
     for L in layers:
+        if L.kind == "ew":
+            out.append(None)
+            continue
         kvol = int(np.prod(L.ksize))
         w = synth.kaiming_weight(rng, kvol, L.cin, L.cout)
         b = (rng.standard_normal(L.cout) * 0.05).astype(np.float32)
@@ -111,7 +191,11 @@ class SparseNet:
     layers      list of Layer
     spatial     [B, Z, Y, X] of the input voxel grid
     caps        dict voxel-set name -> maximum active voxels ('in' for the input set, otherwise the key of the
-                'conv' layer that creates the set); missing entries default to `default_cap`
+                'conv' layer that creates the set)
+    The network input is available to later layers under the tag 'input'.  A first layer with 4, 5 or 9 input
+    channels runs with its input zero-padded to 16 channels (zero weight rows) and a last layer whose output
+    channel count is not a multiple of 16 with zero-padded output channels, which makes both eligible for the
+    tensor-core kernel; `forward` returns the un-padded view.
     """
 
     def __init__(self, layers, spatial, caps, dtype=torch.float16, device="cuda:0", seed=0, kernel=0,
@@ -130,12 +214,22 @@ class SparseNet:
         weights = make_weights(layers, seed)
         self.rulebooks = {}
         self.mm = []
-        self.bufs = []
         self.sets = {"in": dict(cap=int(caps["in"]), shape=[int(v) for v in spatial], coors=None, num=None)}
         cur = "in"
-        set_of_tag = {}
+        set_of_tag = {"input": "in"}
+        lp = dtype != torch.float32
+        first_cin = next(L.cin for L in layers if L.kind != "ew")
+        self.in_channels = (first_cin + 15) // 16 * 16 if (lp and pad_input and first_cin % 16) else first_cin
+        self.out_channels = layers[-1].cout
         with torch.cuda.device(self.device):
             for li, L in enumerate(layers):
+                if L.kind == "ew":
+                    cur = set_of_tag[L.ew[1][0]]
+                    out_buf = torch.zeros((self.sets[cur]["cap"], L.cout), dtype=dtype, device=self.device)
+                    self.mm.append((None, out_buf, cur))
+                    if L.save:
+                        set_of_tag[L.save] = cur
+                    continue
                 if L.source is not None:
                     cur = set_of_tag[L.source]
                 src = self.sets[cur]
@@ -186,24 +280,27 @@ class SparseNet:
                     out_set, in_set = rb.out_set, rb.in_set
                 assert in_set == cur, "layer %d expects voxel set %s but the data is on %s" % (li, in_set, cur)
                 w, b = weights[li]
-                cin = L.cin
-                if li == 0:
-                    # a first layer with 4 or 5 input channels is run with its input zero-padded to 16 channels (and
-                    # zero weight rows), which makes it eligible for the tensor-core kernel; the result is unchanged
-                    self.in_channels = cin
-                    if dtype != torch.float32 and cin % 16 != 0 and pad_input:
-                        self.in_channels = (cin + 15) // 16 * 16
-                        wp = np.zeros((w.shape[0], self.in_channels, w.shape[2]), dtype=np.float32)
-                        wp[:, :cin] = w
-                        w, cin = wp, self.in_channels
+                cin, cout = L.cin, L.cout
+                reads_input = (li == 0 and L.source is None) or L.source == "input"
+                if reads_input and cin != self.in_channels:
+                    wp = np.zeros((w.shape[0], self.in_channels, w.shape[2]), dtype=np.float32)
+                    wp[:, :cin] = w
+                    w, cin = wp, self.in_channels
+                if li == len(layers) - 1 and lp and cout % 16:
+                    cout = (cout + 15) // 16 * 16
+                    wp = np.zeros((w.shape[0], w.shape[1], cout), dtype=np.float32)
+                    wp[:, :, :L.cout] = w
+                    bp = np.zeros(cout, dtype=np.float32)
+                    bp[:L.cout] = b
+                    w, b = wp, bp
                 plug = deserialize_plugin("SPConvMM", data_s_spconv_mm(
-                    L.ksize, cin, L.cout, self.sets[out_set]["cap"], L.kind == "subm", L.kind == "inverse", w, b))
+                    L.ksize, cin, cout, self.sets[out_set]["cap"], L.kind == "subm", L.kind == "inverse", w, b))
                 plug.configure(dtype)
                 plug.set_kernel(kernel)
                 # single-stream execution: the next layer's prologue overlaps this layer's tail; with the rulebook
                 # chain on a side stream its kernels fill those tails instead (measured: 1 % better per frame)
                 plug.set_dependent_launch(not overlap_rulebooks)
-                out_buf = torch.zeros((self.sets[out_set]["cap"], L.cout), dtype=dtype, device=self.device)
+                out_buf = torch.zeros((self.sets[out_set]["cap"], cout), dtype=dtype, device=self.device)
                 self.mm.append((plug, out_buf, out_set))
                 cur = out_set
                 if L.save:
@@ -244,7 +341,7 @@ class SparseNet:
             self.side_subm.wait_stream(main)
             done = set()
             for L in self.layers:
-                if L.key in done:
+                if L.kind == "ew" or L.key in done:
                     continue
                 done.add(L.key)
                 rb = self.rulebooks[L.key]
@@ -258,9 +355,16 @@ class SparseNet:
                     ev.record(stream)
                     ready[L.key] = ev
         built = set()
-        saved = {}
+        saved = {"input": feats}
         x = feats
         for L, (plug, out_buf, out_set) in zip(self.layers, self.mm):
+            if L.kind == "ew":  # element-wise graph op between plugins, in fp32 like the CPU restatement
+                y = ew_apply(L.ew[0], [saved[t].float() for t in L.ew[1]], torch)
+                out_buf.copy_(y)
+                x = out_buf
+                if L.save:
+                    saved[L.save] = x
+                continue
             if L.source is not None:
                 x = saved[L.source]
             rb = self.rulebooks[L.key]
@@ -275,20 +379,24 @@ class SparseNet:
                 in_set = rb.out_set if L.kind == "inverse" else rb.in_set
                 plug.enqueue(x, self.sets[in_set]["num"], self.sets[out_set]["num"], rb.index, rb.num_index,
                              outputs=[out_buf])
+                if L.relu and L.act_first:
+                    out_buf.relu_()
                 if res is not None:
                     out_buf.add_(res)
-                if L.relu:
+                if L.relu and not L.act_first:
                     out_buf.relu_()
                 x = out_buf
             else:
                 table = rb.table_inv if L.kind == "inverse" else rb.table_fwd
-                x = plug.run(x, self.sets[out_set]["num"], table, out=out_buf, relu=L.relu, residual=res)
+                x = plug.run(x, self.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res)
             if L.save:
                 saved[L.save] = x
         if self.overlap_rulebooks:
             main.wait_stream(self.side)
             main.wait_stream(self.side_subm)
         o = self.sets[self.out_set]
+        if x.shape[1] != self.out_channels:
+            x = x[:, :self.out_channels]
         return x, o["coors"], o["num"]
 
     def counts(self):
@@ -296,13 +404,16 @@ class SparseNet:
         return {k: int(v["num"].item()) for k, v in self.sets.items() if v["num"] is not None}
 
     def layer_work(self):
-        """Per layer: (Cin, Cout, kVol, M, pairs P) after a forward pass (host sync)."""
+        """Per convolution layer: (Cin, Cout, kVol, M, pairs P) after a forward pass (host sync)."""
         out = []
         pairs = {}
         for L, (plug, _, out_set) in zip(self.layers, self.mm):
+            if L.kind == "ew":
+                continue
             rb = self.rulebooks[L.key]
             if L.key not in pairs:
                 k = rb.index[2, :int(rb.num_index.item())]
                 pairs[L.key] = int((k >= 0).sum().item())
-            out.append((L.cin, L.cout, rb.kvol, int(self.sets[out_set]["num"].item()), pairs[L.key]))
+            out.append((plug.p.in_channels, plug.p.out_channels, rb.kvol, int(self.sets[out_set]["num"].item()),
+                        pairs[L.key]))
         return out

@@ -175,8 +175,9 @@ spconv_mm_simt_kernel(const T* __restrict__ in_feats, int64_t n_in_max, const T*
       int col = cg + 8 * j;
       if (col < cout) {
         float v = acc[j] + bias[col];
+        if (relu == 2) v = fmaxf(v, 0.f);
         if (residual) v += to_f32(residual[o * cout + col]);
-        if (relu) v = fmaxf(v, 0.f);
+        if (relu == 1) v = fmaxf(v, 0.f);
         out_feats[o * cout + col] = from_f32<T>(v);
       }
     }

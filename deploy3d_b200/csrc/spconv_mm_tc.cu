@@ -335,6 +335,10 @@ __device__ __forceinline__ void store_chunk(const uint32_t* acc, const float* bi
   float v[16];
 #pragma unroll
   for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(acc[j]) + bias_s[col0 + j];
+  if (relu == 2) {  // activation before the residual is added (sum of two activated branches)
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = fmaxf(v[j], 0.f);
+  }
   if (res_row) {
     const uint4* r4 = reinterpret_cast<const uint4*>(reinterpret_cast<const unsigned short*>(res_row) + col0);
 #pragma unroll
@@ -361,7 +365,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t* acc, const float* bi
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       float a = v[q * 8 + 2 * e], b = v[q * 8 + 2 * e + 1];
-      if (relu) a = fmaxf(a, 0.f), b = fmaxf(b, 0.f);
+      if (relu == 1) a = fmaxf(a, 0.f), b = fmaxf(b, 0.f);
       if (kBf16) {
         __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
         w[e] = *reinterpret_cast<uint32_t*>(&h);

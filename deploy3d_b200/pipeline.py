@@ -167,18 +167,28 @@ class DetectionPipeline:
 
 
 class SegmentationPipeline:
-    """Cylinder3D-shaped frame pipeline: CylinderEncoder -> ScatterTo (max) -> encoder-decoder sparse network with
-    inverse convolutions -> GatherBack to per-point logits (the op chain of tests/cylinder/test_cylinder3d.py)."""
+    """Cylinder3D-shaped frame pipeline: CylinderEncoder -> ScatterTo (max) -> asymmetric encoder-decoder sparse
+    network with inverse convolutions -> GatherBack to per-point logits (the op chain of
+    tests/cylinder/test_cylinder3d.py:275-325).  ``net='cylinder3d'`` is the network of benchmark config 5 (3x1x3 /
+    1x3x3 SubM blocks, channels 32 / 64 / 128 / 256, 20 classes); ``net='unet'`` a small 3x3x3 encoder-decoder."""
 
-    def __init__(self, device="cuda:0", n_pts=120000, caps=None, n_class=16, dtype=torch.float16, kernel=0):
+    def __init__(self, device="cuda:0", n_pts=120000, caps=None, n_class=None, dtype=torch.float16, kernel=0,
+                 net="cylinder3d", overlap_rulebooks=True):
         from .ops import data_s_gather_back, data_s_scatter_to
         frame = synth.config5_points()
         self.device, self.dtype, self.n_pts = torch.device(device), dtype, int(n_pts)
         self.c_pts = frame["points"].shape[1]
         self.spatial = frame["spatial_shape"]
         self.cylinder_config = frame["cylinder_config"]
-        self.layers = backbone.seg_unet(self.c_pts + 5, n_class)
-        self.caps = caps or {"in": self.n_pts, "d1": self.n_pts, "d2": self.n_pts}
+        if net == "cylinder3d":
+            self.n_class = n_class or 20
+            self.layers = backbone.cylinder3d(self.c_pts + 5, self.n_class)
+        else:
+            self.n_class = n_class or 16
+            self.layers = backbone.seg_unet(self.c_pts + 5, self.n_class)
+        n_class = self.n_class
+        self.set_names = ["in"] + [L.key for L in self.layers if L.kind == "conv"]
+        self.caps = caps or {k: self.n_pts for k in self.set_names}
         dev = self.device
         with torch.cuda.device(dev):
             cap = self.caps["in"]
@@ -195,19 +205,39 @@ class SegmentationPipeline:
             self.scatter = deserialize_plugin("ScatterTo", data_s_scatter_to(0))
             self.vox_feats = torch.zeros((cap, self.c_pts + 5), dtype=torch.float32, device=dev)
             spatial_b = [self.spatial[0]] + list(self.spatial[2:])
-            self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel)
+            self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel,
+                                          overlap_rulebooks=overlap_rulebooks)
             self.vox_feats_lp = torch.zeros((cap, self.net.in_channels), dtype=dtype, device=dev)
             self.net.set_input(self.vox_coors, self.vox_num)
             self.gather = deserialize_plugin("GatherBack", data_s_gather_back(0.0))
             # GatherBack is an fp32 operator (as in the reference): the network output is widened first
             self.net_out_f32 = torch.zeros((cap, n_class), dtype=torch.float32, device=dev)
             self.logits = torch.zeros((self.n_pts, n_class), dtype=torch.float32, device=dev)
+            self.labels = torch.zeros(self.n_pts, dtype=torch.int32, device=dev)
+        self.graph = None
 
     def load_frame(self, frame):
         self.points.copy_(torch.from_numpy(frame["points"]))
         self.batch.copy_(torch.from_numpy(frame["batch"]))
 
+    def calibrate(self, frames, margin=1.15):
+        """Run `frames` once with generous buffers, read the voxel counts back and return tight caps."""
+        peak = {}
+        for f in frames:
+            self.load_frame(f)
+            self.enqueue()
+            torch.cuda.synchronize(self.device)
+            cnt = self.net.counts()
+            cnt["in"] = int(self.vox_num.item())
+            for k, v in cnt.items():
+                if v >= self.caps[k]:
+                    raise RuntimeError("voxel set %s filled its buffer (%d): raise the calibration caps" % (k, v))
+                peak[k] = max(peak.get(k, 0), v)
+        return {k: _roundup(v * margin + 256, 1024) for k, v in peak.items()}
+
     def enqueue(self):
+        """One frame on the current stream: no host synchronisation, no allocation by this library (the
+        element-wise graph ops between plugins are torch's)."""
         self.encoder.enqueue(self.points, self.batch, self.cfg, self.shape_tensor,
                              outputs=[self.pts_feats, self.scatter_index, self.scatter_count, self.vox_coors,
                                       self.vox_num])
@@ -216,4 +246,22 @@ class SegmentationPipeline:
         feats, _, _ = self.net.forward(self.vox_feats_lp)
         self.net_out_f32.copy_(feats)
         self.gather.enqueue(self.net_out_f32, self.scatter_index, outputs=[self.logits])
+        self.labels.copy_(torch.argmax(self.logits, dim=1))  # the label pass of the reference (test_cylinder3d.py:322)
         return self.logits
+
+    def capture(self):
+        """Capture enqueue() into a CUDA graph (after a warm-up call so every workspace exists)."""
+        with torch.cuda.device(self.device):
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                self.enqueue()
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.enqueue()
+        return self.graph
+
+    def replay(self):
+        self.graph.replay()

@@ -204,7 +204,7 @@ class SPConvMMPlugin(_Plugin):
         if out is None:
             out = torch.empty((self.p.max_num_act_out, self.p.out_channels), dtype=in_feats.dtype,
                               device=in_feats.device)
-        epi = _lib.SpconvMMEpilogue(int(bool(relu)), residual.data_ptr() if residual is not None else None)
+        epi = _lib.SpconvMMEpilogue(int(relu), residual.data_ptr() if residual is not None else None)  # relu: 0 / 1 / 2
         with torch.cuda.device(in_feats.device):
             check("d3d_spconv_mm_run",
                   lib().d3d_spconv_mm_run(self.handle, _TORCH2D3D[in_feats.dtype],

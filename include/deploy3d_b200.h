@@ -138,7 +138,9 @@ typedef struct {
 } d3d_spconv_mm_params;
 
 /* Epilogue fused after bias; all zero == the reference plugin (activation is a separate graph op there,
- * tests/cylinder/test_cylinder3d.py:91-92). `residual` (same dtype/shape as outFeats) is added before ReLU. */
+ * tests/cylinder/test_cylinder3d.py:91-92).  `residual` (same dtype/shape as outFeats) is added to the result.
+ * relu: 0 none; 1 ReLU after the residual add (residual block); 2 ReLU before it (sum of two activated branches,
+ * tests/cylinder/test_cylinder3d.py:113-124). */
 typedef struct {
   int32_t relu;
   const void* residual;

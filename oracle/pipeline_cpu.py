@@ -22,12 +22,19 @@ def _round_lp(a, dtype):
 
 def run_net(layers, weights, feats, coors, spatial_b, dtype="fp16"):
     """feats [N, Cin] float32 (already rounded to `dtype`), coors [N, 4]; returns (feats, coors, shape, stats)."""
-    rulebooks, saved, sets = {}, {}, {"in": (coors, list(spatial_b))}
-    set_of_tag = {}
+    rulebooks, sets = {}, {"in": (coors, list(spatial_b))}
+    saved, set_of_tag = {"input": feats}, {"input": "in"}
     cur = "in"
     x = feats
     stats = []
-    for L, (w, b) in zip(layers, weights):
+    for L, wb in zip(layers, weights):
+        if L.kind == "ew":  # element-wise graph op between plugins (fp32, result rounded like any activation)
+            y = backbone.ew_apply(L.ew[0], [saved[t] for t in L.ew[1]], np)
+            x, cur = _round_lp(y.astype(np.float32), dtype), set_of_tag[L.ew[1][0]]
+            if L.save:
+                saved[L.save], set_of_tag[L.save] = x, cur
+            continue
+        w, b = wb
         if L.source is not None:
             x, cur = saved[L.source], set_of_tag[L.source]
         c_in, shape_in = sets[cur]
@@ -47,9 +54,11 @@ def run_net(layers, weights, feats, coors, spatial_b, dtype="fp16"):
             in_set, out_set = out_set, in_set
         m = len(sets[out_set][0])
         y = oracle.spconv_mm(x, _round_lp(w, dtype), _round_lp(b, dtype), index, num, L.kind == "inverse", m)
+        if L.relu and L.act_first:
+            y = np.maximum(y, 0)
         if L.residual:
             y = y + saved[L.residual]
-        if L.relu:
+        if L.relu and not L.act_first:
             y = np.maximum(y, 0)
         x = _round_lp(y, dtype)
         cur = out_set
@@ -74,10 +83,14 @@ def run_frame(kind, points, batch, voxel_config, spatial, boxes=None, iou_thresh
     return out
 
 
-def run_segmentation_frame(points, batch, cylinder_config, spatial, n_class=16, dtype="fp16", seed=0):
-    """The Cylinder3D-shaped frame on the CPU: cylinder encoder -> scatter (max) -> seg_unet -> gather back.
+def run_segmentation_frame(points, batch, cylinder_config, spatial, n_class=None, dtype="fp16", seed=0,
+                           net="cylinder3d"):
+    """The Cylinder3D-shaped frame on the CPU: cylinder encoder -> scatter (max) -> network -> gather back.
     Returns dict(logits [N_pts, n_class], num_voxels)."""
-    layers = backbone.seg_unet(points.shape[1] + 5, n_class)
+    if net == "cylinder3d":
+        layers = backbone.cylinder3d(points.shape[1] + 5, n_class or 20)
+    else:
+        layers = backbone.seg_unet(points.shape[1] + 5, n_class or 16)
     weights = backbone.make_weights(layers, seed)
     n = len(points)
     aug, scatter_index, scatter_count, coors, nv = oracle.cylinder(points, batch, cylinder_config, spatial, n)

@@ -58,10 +58,14 @@ def test_frame_matches_cpu_pipeline(d3d, kind, denom, graph):
     assert (pipe.nms_scores.cpu().numpy() == want["nms_scores"]).all()
 
 
-def test_segmentation_frame_matches_cpu_pipeline(d3d):
+@pytest.mark.parametrize("net", ["cylinder3d", "unet"])
+def test_segmentation_frame_matches_cpu_pipeline(d3d, net):
     """Cylinder3D-shaped chain on an azimuth sector of a config-5 frame: CylinderEncoder -> ScatterTo(max) ->
-    encoder-decoder with inverse convolutions and skip connections -> GatherBack.  Per-point logits do not depend on
-    the (implementation-defined) voxel numbering, so they are compared directly."""
+    encoder-decoder -> GatherBack.  'cylinder3d' is the network of benchmark config 5: asymmetric 3x1x3 / 1x3x3 SubM
+    blocks over shared rulebooks, channels 32 / 64 / 128 / 256, strided pooling and its inverse, skip connections,
+    the sigmoid ReconBlock and 20 classes (the composition of tests/cylinder/test_cylinder3d.py:100-272).  Per-point
+    logits do not depend on the (implementation-defined) voxel numbering, so they are compared directly; the frame is
+    then captured in a CUDA graph and replayed with the same result."""
     from deploy3d_b200 import synth
     from deploy3d_b200.pipeline import SegmentationPipeline
     from oracle import pipeline_cpu
@@ -77,17 +81,26 @@ def test_segmentation_frame_matches_cpu_pipeline(d3d):
     pts = pts[synth.drop_edge_points(cyl, mins, steps)]
     n = len(pts)
     batch = np.zeros(n, np.int32)
-    pipe = SegmentationPipeline("cuda:0", n_pts=n, caps={"in": n, "d1": 4 * n, "d2": 4 * n})
+    probe = SegmentationPipeline("cuda:0", n_pts=n, net=net)
+    caps = {k: (n if k == "in" else 4 * n) for k in probe.set_names}
+    del probe
+    pipe = SegmentationPipeline("cuda:0", n_pts=n, caps=caps, net=net)
     pipe.load_frame(dict(points=pts, batch=batch))
     got = pipe.enqueue().float().cpu().numpy()
     torch.cuda.synchronize()
-    want = pipeline_cpu.run_segmentation_frame(pts, batch, cfg, shape)
+    want = pipeline_cpu.run_segmentation_frame(pts, batch, cfg, shape, net=net)
     assert int(pipe.vox_num.item()) == want["num_voxels"]
     ref = want["logits"]
-    assert got.shape == ref.shape
+    assert got.shape == ref.shape and got.shape[1] == (20 if net == "cylinder3d" else 16)
     scale = np.sqrt((ref ** 2).mean()) + 1e-12
     err = np.abs(got - ref)
     rel_l2 = np.sqrt((err ** 2).sum() / ((ref ** 2).sum() + 1e-30))
     assert rel_l2 < 1e-2, "relative L2 error %.3e" % rel_l2
     bad = err > 2e-2 * (np.abs(ref) + scale)
     assert not bad.any(), "%d logits off, worst %.3e at scale %.3e" % (bad.sum(), err[bad].max(), scale)
+    pipe.capture()
+    pipe.logits.zero_()
+    pipe.replay()
+    torch.cuda.synchronize()
+    assert np.array_equal(pipe.logits.cpu().numpy(), got), "graph replay differs from the eager frame"
+    assert np.array_equal(pipe.labels.cpu().numpy(), got.argmax(1))
