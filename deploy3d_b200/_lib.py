@@ -32,6 +32,15 @@ class SpconvIndexParams(ctypes.Structure):
                 ("transpose", ctypes.c_int32)]
 
 
+class SpconvIndexExtras(ctypes.Structure):
+    _fields_ = [("persistent_buffers", ctypes.c_int32), ("first_call", ctypes.c_int32),
+                ("subm_table", ctypes.c_void_p)]
+
+
+class MeanEncoderExtras(ctypes.Structure):
+    _fields_ = [("lp_feats", ctypes.c_void_p), ("lp_dtype", ctypes.c_int32), ("lp_channels", ctypes.c_int32)]
+
+
 class SpconvMMParams(ctypes.Structure):
     _fields_ = [("kernel_vol", ctypes.c_int32), ("in_channels", ctypes.c_int32), ("out_channels", ctypes.c_int32),
                 ("max_num_act_out", ctypes.c_int32), ("subm", ctypes.c_int32), ("inverse", ctypes.c_int32),
@@ -93,6 +102,9 @@ SIGNATURES = {
                                                      ctypes.c_int, _descp]),
     "d3d_spconv_index_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(SpconvIndexParams))),
     "d3d_spconv_index_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(SpconvIndexParams))),
+    "d3d_spconv_index_subm_table_ok": (ctypes.c_int, [ctypes.POINTER(SpconvIndexParams)]),
+    "d3d_spconv_index_enqueue_ex": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(SpconvIndexParams)) +
+                                    [ctypes.POINTER(SpconvIndexExtras)]),
     "d3d_spconv_mm_create": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(_vp)]),
     "d3d_spconv_mm_get_params": (ctypes.c_int, [_vp, ctypes.POINTER(SpconvMMParams)]),
     "d3d_spconv_mm_serialize": (ctypes.c_int, [_vp, _vp, _szp]),
@@ -116,6 +128,8 @@ SIGNATURES = {
     "d3d_simple_mean_encoder_output_desc": (ctypes.c_int, [ctypes.POINTER(VoxelEncoderParams), _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_simple_mean_encoder_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(VoxelEncoderParams))),
     "d3d_simple_mean_encoder_enqueue": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(VoxelEncoderParams))),
+    "d3d_simple_mean_encoder_enqueue_ex": (ctypes.c_int, _enqueue_sig(ctypes.POINTER(VoxelEncoderParams)) +
+                                           [ctypes.POINTER(MeanEncoderExtras)]),
     "d3d_cylinder_encoder_parse": (ctypes.c_int, [_vp, _sz, ctypes.POINTER(VoxelEncoderParams)]),
     "d3d_cylinder_encoder_output_desc": (ctypes.c_int, [ctypes.POINTER(VoxelEncoderParams), _descp, ctypes.c_int, ctypes.c_int, _descp]),
     "d3d_cylinder_encoder_workspace": (ctypes.c_int, _workspace_sig(ctypes.POINTER(VoxelEncoderParams))),

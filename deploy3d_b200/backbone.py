@@ -268,6 +268,10 @@ class SparseNet:
                         max(SPConvMMPlugin.table_bytes(rb.kvol, out["cap"]), 16), dtype=torch.uint8,
                         device=self.device)
                     rb.table_inv = None
+                    # the net owns index, workspace and tables for its whole life: stale-padding-only refills, and
+                    # the table of a mirror-symmetric SubM rulebook straight from the probe kernel
+                    rb.calls = 0
+                    rb.fused_table = subm and not plugin_order and rb.plugin.subm_table_ok()
                     self.rulebooks[L.key] = rb
                 rb = self.rulebooks[L.key]
                 if L.kind == "inverse":
@@ -312,15 +316,24 @@ class SparseNet:
 
     def _build_rulebook(self, rb):
         src, dst = self.sets[rb.in_set], self.sets[rb.out_set]
+        if self.plugin_order:  # the plain plugin entry point; every SPConvMM node builds its own table
+            outs = [rb.index, rb.num_index] if rb.kind == "subm" else \
+                [rb.index, rb.num_index, dst["coors"], dst["num"], rb.out_shape_tensor]
+            rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor, outputs=outs)
+            return
+        first = rb.calls == 0
+        rb.calls += 1
         if rb.kind == "subm":
-            rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor, outputs=[rb.index, rb.num_index])
+            rb.plugin.enqueue_ex(src["coors"], src["num"], rb.shape_tensor, outputs=[rb.index, rb.num_index],
+                                 persistent=True, first_call=first,
+                                 subm_table=rb.table_fwd if rb.fused_table else None)
         else:
-            rb.plugin.enqueue(src["coors"], src["num"], rb.shape_tensor,
-                              outputs=[rb.index, rb.num_index, dst["coors"], dst["num"], rb.out_shape_tensor])
-        if self.plugin_order:
-            return  # every SPConvMM node builds its own table inside its enqueue
-        SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd,
-                               mirror=rb.mirror)
+            rb.plugin.enqueue_ex(src["coors"], src["num"], rb.shape_tensor,
+                                 outputs=[rb.index, rb.num_index, dst["coors"], dst["num"], rb.out_shape_tensor],
+                                 persistent=True, first_call=first)
+        if not rb.fused_table:
+            SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd,
+                                   mirror=rb.mirror)
         if rb.table_inv is not None:
             SPConvMMPlugin.prepare(rb.kvol, True, src["cap"], rb.index, rb.num_index, table=rb.table_inv)
 

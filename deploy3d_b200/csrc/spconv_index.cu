@@ -177,17 +177,41 @@ __global__ void subm_probe_kernel(const unsigned long long* __restrict__ table, 
 // per-(offset, CTA) counts are collected in shared memory with a single barrier at the end.
 // kPlane3x3: the two trailing kernel extents are 3 x 3 (the usual case); the nine probes of a leading tap are
 // then issued together.
+// With `nbr` != null (a mirror-symmetric rulebook: odd kernel, padding = dilation * (k - 1) / 2 on every axis) the
+// kernel also writes the output-stationary neighbour table SPConvMM consumes, [tile of 128 outputs][kvol][128]: the
+// voxel found for offset k is, read the other way round, the input that feeds voxel i through offset kvol - 1 - k,
+// so thread i fills its own column of the table -- coalesced stores, no scatter pass, no fill pass -- and the
+// per-tile offset masks are collected with shared-memory atomics.  `nbr_tiles` = tiles the table holds.
 template <bool kPlane3x3>
 __global__ void __launch_bounds__(kIdxThreads, 4)
 subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ coors,
                    const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
-                   int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk) {
+                   int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk,
+                   int32_t* __restrict__ nbr, uint32_t* __restrict__ nbr_mask, int64_t nbr_tiles) {
   constexpr int kBatch = 4;  // probes in flight per thread
+  constexpr int kTilesPerCta = kIdxThreads / 128;
   __shared__ int cnt[kMaxKernelVol];
+  __shared__ unsigned tile_bits[kTilesPerCta];
   const int n = live_count(num_act_in, n_max);
-  if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
+  const int64_t tile0 = (int64_t)blockIdx.x * kTilesPerCta;
+  if ((int64_t)blockIdx.x * kIdxThreads >= n) {
+    // no live voxel here: the tiles of this CTA take part in no offset and hold no neighbour
+    if (nbr) {
+      if (threadIdx.x < kTilesPerCta && tile0 + threadIdx.x < nbr_tiles) nbr_mask[tile0 + threadIdx.x] = 0u;
+      const int64_t tile = tile0 + (threadIdx.x >> 7);
+      if (tile < nbr_tiles)
+        for (int k = 0; k < g.kvol; ++k) nbr[(tile * g.kvol + k) * 128 + (threadIdx.x & 127)] = -1;
+    }
+    return;
+  }
   for (int t = threadIdx.x; t < g.kvol; t += kIdxThreads) cnt[t] = 0;
+  if (threadIdx.x < kTilesPerCta) tile_bits[threadIdx.x] = 0u;
   __syncthreads();
+  const int my_tile = threadIdx.x >> 7;
+  // this thread's column of the table: entry of offset k' at nbr_col[k' * 128]
+  int32_t* nbr_col = nullptr;
+  if (nbr && tile0 + my_tile < nbr_tiles)
+    nbr_col = nbr + ((tile0 + my_tile) * g.kvol) * 128 + (threadIdx.x & 127);
   const uint32_t mask = hash_capacity((long long)n * kSubmFan, cap_max) - 1;
   const int i = blockIdx.x * kIdxThreads + threadIdx.x;
   const bool live = i < n;
@@ -248,6 +272,8 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
         if (live) pair_out[(int64_t)(k + b) * n_max + i] = v[b];
         const unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
         if (lane_id() == 0 && hits) atomicAdd(&cnt[k + b], __popc(hits));
+        if (nbr_col) nbr_col[(g.kvol - 1 - (k + b)) * 128] = v[b];
+        if (nbr && lane_id() == 0 && hits) atomicOr(&tile_bits[my_tile], 1u << (g.kvol - 1 - (k + b)));
       }
       k += 9;
       continue;
@@ -276,6 +302,8 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
             if (live) pair_out[(int64_t)(k + b) * n_max + i] = v[b];
             const unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
             if (lane_id() == 0 && hits) atomicAdd(&cnt[k + b], __popc(hits));
+            if (nbr_col) nbr_col[(g.kvol - 1 - (k + b)) * 128] = v[b];
+            if (nbr && lane_id() == 0 && hits) atomicOr(&tile_bits[my_tile], 1u << (g.kvol - 1 - (k + b)));
           }
         }
         k += (g.klast - k2 < kBatch) ? g.klast - k2 : kBatch;
@@ -284,6 +312,8 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
   }
   __syncthreads();
   for (int t = threadIdx.x; t < g.kvol; t += kIdxThreads) block_counts[(int64_t)t * nblk + blockIdx.x] = cnt[t];
+  if (nbr && threadIdx.x < kTilesPerCta && tile0 + threadIdx.x < nbr_tiles)
+    nbr_mask[tile0 + threadIdx.x] = tile_bits[threadIdx.x];
 }
 
 // Conv insert: every valid (input, offset) inserts its output key with value = i*kvol + k; the smallest pair id
@@ -555,9 +585,13 @@ conv_translate_packed_kernel(int32_t* __restrict__ pair_out, const int32_t* __re
 // Single CTA of 1024 threads.  Warp w scans the counts of offsets w, w+32, ..; then the segment starts
 // (each rounded up to 128, trt/spconv/index.cu:148-156) and numIndex (index.cu:139-144) are produced.
 // seg[0..kvol] = start of each segment (seg[kvol] = numIndex), seg[kvol+1 .. 2*kvol] = pair count of each offset.
+// `state` (two words kept in the workspace between calls): [0] where the padding fill of this call ends, [1] the
+// num_index of this call.  A caller that owns the index buffer across calls (`persistent`) and did not pass
+// `first` gets only [num_index, previous num_index) refilled: everything beyond is still -1 from earlier calls.
 __global__ void segment_scan_kernel(int32_t* __restrict__ block_counts, int nblk, int kvol,
                                     const int32_t* num_act_in, int64_t n_max, int32_t* __restrict__ seg,
-                                    int32_t* num_index) {
+                                    int32_t* num_index, int32_t* __restrict__ state, int persistent, int first,
+                                    int64_t row_len) {
   __shared__ int counts[kMaxKernelVol];
   int n = live_count(num_act_in, n_max);
   int live_blk = (n + kIdxThreads - 1) / kIdxThreads;
@@ -588,6 +622,10 @@ __global__ void segment_scan_kernel(int32_t* __restrict__ block_counts, int nblk
     }
     seg[kvol] = pos;
     *num_index = pos;
+    const int64_t prev = state[1];
+    const bool partial = persistent && !first && prev >= 0 && prev <= row_len;
+    state[0] = (int32_t)(partial ? (prev > pos ? prev : pos) : row_len);
+    state[1] = pos;
   }
 }
 
@@ -731,8 +769,9 @@ compact_packed_kernel(const int32_t* __restrict__ pair_out, const int32_t* __res
 // Everything that is not a pair is -1: the unused tail of each 128-aligned segment and the rows beyond
 // numIndex (the reference memsets the three rows beforehand, trt/spconv/index.cu:352-354).
 __global__ void fill_padding_kernel(const int32_t* __restrict__ seg, int kvol, int32_t* __restrict__ index,
-                                    int64_t row_len) {
+                                    int64_t row_len, const int32_t* __restrict__ state) {
   int num_index = seg[kvol];
+  const int64_t fill_end = state[0];  // row_len, or where the previous rulebook in this buffer ended
   int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   // in-segment padding: at most 127 entries per offset
@@ -747,7 +786,7 @@ __global__ void fill_padding_kernel(const int32_t* __restrict__ seg, int kvol, i
   }
   // tail of the three rows; num_index is a multiple of 128, so 16-byte stores work whenever the rows themselves
   // start 16-byte aligned
-  const int64_t tail = row_len - num_index;
+  const int64_t tail = fill_end - num_index;  // both multiples of 128
   if (tail <= 0) return;
   if ((row_len & 3) == 0 && (reinterpret_cast<uintptr_t>(index) & 15) == 0) {
     const int64_t tail4 = tail >> 2;
@@ -784,6 +823,7 @@ struct Plan {
   int32_t* slot_out;
   int32_t* winners;
   uint32_t* win_bits;  // per input: which of its offsets won an output voxel (kvol <= 32)
+  int32_t* state;      // two words that survive between calls (see segment_scan_kernel)
   bool packed;         // strided rulebook kept as kPackedSlots entries per input instead of kvol
   size_t bytes;
 };
@@ -849,6 +889,7 @@ int make_plan(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n
   plan->packed = !p->subm && !g.transpose && ndim == 3 && g.ksize[0] <= 3 && g.ksize[1] <= 3 && g.ksize[2] <= 3 &&
                  fan <= kPackedSlots && g.kvol > kPackedSlots /* the pair table has kvol rows */ && plan->cap_max <= (1u << kPackedShift) &&
                  p->max_num_act_out <= (1 << kPackedShift);
+  plan->state = w.take<int32_t>(2);
   plan->bytes = w.off;
   return D3D_OK;
 }
@@ -921,7 +962,28 @@ extern "C" int d3d_spconv_index_workspace(const d3d_spconv_index_params* p, cons
 extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
                                         const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                         void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  return d3d_spconv_index_enqueue_ex(p, in, n_in, out, n_out, inputs, outputs, workspace, workspace_bytes, stream,
+                                     nullptr);
+}
+
+extern "C" int d3d_spconv_index_subm_table_ok(const d3d_spconv_index_params* p) {
+  if (!p || !p->subm || p->ndim != 3) return 0;
+  for (int d = 0; d < 3; ++d)
+    if (p->kernel_size[d] % 2 == 0 || p->stride[d] != 1 ||
+        p->padding[d] != p->dilation[d] * (p->kernel_size[d] - 1) / 2)
+      return 0;
+  return 1;
+}
+
+extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
+                                           const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                                           void* const* outputs, void* workspace, size_t workspace_bytes,
+                                           void* stream, const d3d_spconv_index_extras* extras) {
   D3D_REQUIRE(inputs && outputs && out, D3D_ERR_INVALID_ARGUMENT);
+  const int persistent = extras ? extras->persistent_buffers : 0;
+  const int first = extras ? extras->first_call : 1;
+  int32_t* nbr = extras ? reinterpret_cast<int32_t*>(extras->subm_table) : nullptr;
+  D3D_REQUIRE(!nbr || d3d_spconv_index_subm_table_ok(p), D3D_ERR_INVALID_ARGUMENT);
   Plan plan;
   int rc = make_plan(p, in, n_in, workspace, &plan);
   if (rc != D3D_OK) return rc;
@@ -948,13 +1010,23 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
   if (p->subm) {
     subm_insert_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max);
     if (g.ndim == 3 && !g.transpose && g.stride[0] == 1 && g.stride[1] == 1 && g.stride[2] == 1) {
+      // the fused neighbour table covers ceil(n_max / 128) tiles, masks right behind the ids (SPConvMM's layout)
+      const int64_t nbr_tiles = (n_max + 127) / 128;
+      uint32_t* nbr_mask = nbr ? reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(nbr) +
+                                                             align_up((size_t)g.kvol * nbr_tiles * 128 * 4, 256))
+                               : nullptr;
+      // one CTA per 256 rows up to the end of the table, so that rows beyond the live count get their -1 / masks
+      const int nblk_t = nbr ? (int)ceil_div(nbr_tiles * 128, kIdxThreads) : nblk;
       if (g.ksize[1] == 3 && g.klast == 3)
-        subm_probe3_kernel<true><<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
-                                                               plan.pair_out, plan.block_counts, nblk);
+        subm_probe3_kernel<true><<<nblk_t, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
+                                                                 plan.pair_out, plan.block_counts, nblk, nbr, nbr_mask,
+                                                                 nbr_tiles);
       else
-        subm_probe3_kernel<false><<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
-                                                                plan.pair_out, plan.block_counts, nblk);
+        subm_probe3_kernel<false><<<nblk_t, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
+                                                                  plan.cap_max, plan.pair_out, plan.block_counts, nblk,
+                                                                  nbr, nbr_mask, nbr_tiles);
     } else {
+      D3D_REQUIRE(!nbr, D3D_ERR_INVALID_ARGUMENT);
       subm_probe_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
                                                                     plan.cap_max, plan.pair_out, plan.block_counts,
                                                                     nblk);
@@ -986,7 +1058,8 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
       conv_translate_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max, g.kvol,
                                                               plan.block_counts, nblk);
   }
-  segment_scan_kernel<<<1, 1024, 0, st>>>(plan.block_counts, nblk, g.kvol, num_act_in, n_max, plan.seg, num_index);
+  segment_scan_kernel<<<1, 1024, 0, st>>>(plan.block_counts, nblk, g.kvol, num_act_in, n_max, plan.seg, num_index,
+                                          plan.state, persistent, first, plan.row_len);
   if (!p->subm && plan.packed)
     compact_packed_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in, n_max,
                                                         nblk, g.kvol, index, plan.row_len);
@@ -996,7 +1069,8 @@ extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const 
   else
     compact_kernel<<<dim3(nblk, g.kvol), kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg,
                                                                num_act_in, n_max, nblk, index, plan.row_len);
-  fill_padding_kernel<<<stream_grid(3 * plan.row_len, 256), 256, 0, st>>>(plan.seg, g.kvol, index, plan.row_len);
+  fill_padding_kernel<<<stream_grid(3 * plan.row_len, 256), 256, 0, st>>>(plan.seg, g.kvol, index, plan.row_len,
+                                                                          plan.state);
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }

@@ -163,11 +163,23 @@ __global__ void mean_accumulate_kernel(const int32_t* __restrict__ slot_of, cons
 }
 
 // trt/voxel_encoder/simple_mean_trt.cu:93-102
+// With `lp` != null the mean is also written in half / bfloat16 into rows of `lp_c` >= c channels (the extra
+// channels zero): the tensor the first sparse convolution reads, without a separate cast-and-pad kernel.
+template <class LP>
 __global__ void mean_divide_kernel(float* __restrict__ out_feats, const int32_t* __restrict__ count,
-                                   const int32_t* num_act_out, int c) {
+                                   const int32_t* num_act_out, int c, LP* __restrict__ lp, int lp_c) {
   int64_t n = (int64_t)*num_act_out * c;
-  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x)
-    out_feats[e] = __fdiv_rn(out_feats[e], (float)count[e / c]);
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t v = e / c;
+    const float mean = __fdiv_rn(out_feats[e], (float)count[v]);
+    out_feats[e] = mean;
+    if (lp) {
+      const int ch = (int)(e - v * c);
+      lp[v * lp_c + ch] = LP(mean);
+      if (ch == c - 1)
+        for (int z = c; z < lp_c; ++z) lp[v * lp_c + z] = LP(0.f);
+    }
+  }
 }
 
 // trt/voxel_encoder/cylinder_trt.cu:87-111
@@ -265,7 +277,20 @@ extern "C" int d3d_simple_mean_encoder_enqueue(const d3d_voxel_encoder_params* p
                                                const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                                void* const* outputs, void* workspace, size_t workspace_bytes,
                                                void* stream) {
+  return d3d_simple_mean_encoder_enqueue_ex(p, in, n_in, out, n_out, inputs, outputs, workspace, workspace_bytes,
+                                            stream, nullptr);
+}
+
+extern "C" int d3d_simple_mean_encoder_enqueue_ex(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in,
+                                                  int n_in, const d3d_tensor_desc* out, int n_out,
+                                                  const void* const* inputs, void* const* outputs, void* workspace,
+                                                  size_t workspace_bytes, void* stream,
+                                                  const d3d_mean_encoder_extras* extras) {
   D3D_REQUIRE(inputs && outputs && out && n_out >= 3, D3D_ERR_INVALID_ARGUMENT);
+  void* lp = extras ? extras->lp_feats : nullptr;
+  D3D_REQUIRE(!lp || ((extras->lp_dtype == D3D_HALF || extras->lp_dtype == D3D_BF16) &&
+                      extras->lp_channels >= in[0].dims[1]),
+              D3D_ERR_INVALID_ARGUMENT);
   EncPlan pl;
   int rc = make_enc_plan(p, in, n_in, workspace, true, &pl);
   if (rc != D3D_OK) return rc;
@@ -292,7 +317,12 @@ extern "C" int d3d_simple_mean_encoder_enqueue(const d3d_voxel_encoder_params* p
                                                           pl.dims[2], pl.dims[3], pl.slot_vid, out_coors);
     mean_accumulate_kernel<<<pl.nblk, kEncThreads, 0, st>>>(pl.slot_of, pl.slot_vid, pts, pl.n, pl.c, out_feats,
                                                             pl.count);
-    mean_divide_kernel<<<stream_grid(m_max * pl.c, 256), 256, 0, st>>>(out_feats, pl.count, num_act_out, pl.c);
+    if (lp && extras->lp_dtype == D3D_BF16)
+      mean_divide_kernel<__nv_bfloat16><<<stream_grid(m_max * pl.c, 256), 256, 0, st>>>(
+          out_feats, pl.count, num_act_out, pl.c, reinterpret_cast<__nv_bfloat16*>(lp), extras->lp_channels);
+    else
+      mean_divide_kernel<__half><<<stream_grid(m_max * pl.c, 256), 256, 0, st>>>(
+          out_feats, pl.count, num_act_out, pl.c, reinterpret_cast<__half*>(lp), lp ? extras->lp_channels : 0);
   }
   D3D_CHECK_LAUNCH();
   return D3D_OK;

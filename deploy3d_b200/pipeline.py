@@ -113,10 +113,14 @@ class DetectionPipeline:
             self.side.wait_stream(main)
             with torch.cuda.stream(self.side):
                 self.nms.enqueue(self.scores, self.boxes, outputs=[self.nms_scores])
-        self.vfe.enqueue(self.points, self.batch, self.cfg, self.shape_tensor,
-                         outputs=[self.vox_feats, self.vox_coors, self.vox_num])
-        # fp32 -> fp16 reformat (TensorRT inserts this layer itself); padding columns stay zero
-        self.vox_feats_lp[:, :self.c_pts].copy_(self.vox_feats)
+        if self.plugin_order or self.dtype == torch.float32:
+            self.vfe.enqueue(self.points, self.batch, self.cfg, self.shape_tensor,
+                             outputs=[self.vox_feats, self.vox_coors, self.vox_num])
+            # fp32 -> fp16 reformat (TensorRT inserts this layer itself); padding columns stay zero
+            self.vox_feats_lp[:, :self.c_pts].copy_(self.vox_feats)
+        else:  # the encoder writes the half-precision, channel-padded copy itself
+            self.vfe.enqueue_lp(self.points, self.batch, self.cfg, self.shape_tensor,
+                                outputs=[self.vox_feats, self.vox_coors, self.vox_num], lp_feats=self.vox_feats_lp)
         feats, coors, num = self.net.forward(self.vox_feats_lp)
         self.densify.enqueue(feats, coors, num, self.out_shape_tensor, outputs=[self.bev])
         if self.plugin_order:

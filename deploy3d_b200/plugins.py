@@ -128,6 +128,32 @@ class SPConvIdxPlugin(_Plugin):
         return outs
 
 
+    def subm_table_ok(self):
+        """True when enqueue_ex can write SPConvMM's neighbour table itself (mirror-symmetric 3-D SubM rulebook)."""
+        return bool(lib().d3d_spconv_index_subm_table_ok(ctypes.byref(self.p)))
+
+    def enqueue_ex(self, *inputs, outputs, persistent=False, first_call=True, subm_table=None, stream=None):
+        """enqueue for a caller that owns its buffers across calls: `persistent` refills only the stale part of the
+        -1 padding (same bytes in `index`), `subm_table` receives the neighbour table of a mirror-symmetric SubM
+        rulebook straight from the probe kernel.  `outputs` must be given (they are the persistent buffers)."""
+        inputs = [t if t.is_contiguous() else t.contiguous() for t in inputs]
+        device = inputs[0].device
+        in_descs = [_desc_of(t) for t in inputs]
+        out_descs = self.output_descs(in_descs)
+        ws_bytes = self.workspace_size(in_descs)
+        ws = self._get_workspace(ws_bytes, device)
+        extras = _lib.SpconvIndexExtras(int(bool(persistent)), int(bool(first_call)),
+                                        subm_table.data_ptr() if subm_table is not None else None)
+        with torch.cuda.device(device):
+            status = lib().d3d_spconv_index_enqueue_ex(
+                ctypes.byref(self.p), desc_array(in_descs), len(in_descs), desc_array(out_descs), len(out_descs),
+                ptr_array([t.data_ptr() for t in inputs]), ptr_array([t.data_ptr() for t in outputs]),
+                ctypes.c_void_p(ws.data_ptr() if ws is not None else 0), ctypes.c_size_t(ws_bytes),
+                _stream_ptr(stream), ctypes.byref(extras))
+        check("d3d_spconv_index_enqueue_ex", status)
+        return tuple(outputs)
+
+
 class SPConvMMPlugin(_Plugin):
     """``SPConvMM`` (trt/spconv/mm_trt.cu:39-206); owns the weight handle."""
     name = "SPConvMM"
@@ -242,6 +268,25 @@ class SimpleMeanEncoderPlugin(_PodPlugin):
     _prefix = "d3d_simple_mean_encoder"
     _params_t = _lib.VoxelEncoderParams
     num_outputs = 3
+
+
+    def enqueue_lp(self, *inputs, outputs, lp_feats, stream=None):
+        """enqueue that also writes the voxel means in half / bfloat16, zero-padded to lp_feats.shape[1] channels."""
+        inputs = [t if t.is_contiguous() else t.contiguous() for t in inputs]
+        device = inputs[0].device
+        in_descs = [_desc_of(t) for t in inputs]
+        out_descs = self.output_descs(in_descs)
+        ws_bytes = self.workspace_size(in_descs)
+        ws = self._get_workspace(ws_bytes, device)
+        extras = _lib.MeanEncoderExtras(lp_feats.data_ptr(), _TORCH2D3D[lp_feats.dtype], int(lp_feats.shape[1]))
+        with torch.cuda.device(device):
+            status = lib().d3d_simple_mean_encoder_enqueue_ex(
+                ctypes.byref(self.p), desc_array(in_descs), len(in_descs), desc_array(out_descs), len(out_descs),
+                ptr_array([t.data_ptr() for t in inputs]), ptr_array([t.data_ptr() for t in outputs]),
+                ctypes.c_void_p(ws.data_ptr() if ws is not None else 0), ctypes.c_size_t(ws_bytes),
+                _stream_ptr(stream), ctypes.byref(extras))
+        check("d3d_simple_mean_encoder_enqueue_ex", status)
+        return tuple(outputs)
 
 
 class CylinderEncoderPlugin(_PodPlugin):

@@ -111,6 +111,30 @@ int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const d3d_tensor_
                              const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                              void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
 
+/* Optional extras for callers that own their buffers across calls (no reference counterpart; TensorRT owns and
+ * reuses a plugin's tensors, so the shells never pass them).
+ *  persistent_buffers  the `index` output and the workspace are the same memory as in the previous call with this
+ *                      flag and nobody else wrote them in between: the -1 padding beyond the previous rulebook is
+ *                      still in place, so only [numIndex, previous numIndex) is refilled instead of the whole tail
+ *                      of the three rows.  The bytes of `index` are the same as without the flag.
+ *  first_call          with persistent_buffers: nothing is known about the buffers yet (do the full fill).
+ *  subm_table          when non-null, a buffer of d3d_spconv_mm_table_bytes(kVol, maxNumActIn) bytes that receives
+ *                      the neighbour table d3d_spconv_mm_prepare(kVol, 0, maxNumActIn, index, ..) would build from
+ *                      this rulebook, written by the probe kernel itself.  Only for rulebooks for which
+ *                      d3d_spconv_index_subm_table_ok() returns 1 (3-D SubM, odd kernel, stride 1, padding =
+ *                      dilation * (k - 1) / 2 on every axis: offsets k and kVol-1-k mirror each other,
+ *                      tests/spconv/test_spconv.py:101-108) and input coordinates without duplicates. */
+typedef struct {
+  int32_t persistent_buffers;
+  int32_t first_call;
+  void* subm_table;
+} d3d_spconv_index_extras;
+int d3d_spconv_index_subm_table_ok(const d3d_spconv_index_params* p);
+int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
+                                const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                                void* const* outputs, void* workspace, size_t workspace_bytes, void* stream,
+                                const d3d_spconv_index_extras* extras);
+
 /* ---------------------------------------------------------------------------------------------
  * SPConvMM -- gather / GEMM / scatter over the rulebook.
  * Replaces spconv::SPConvMMPlugin (trt/spconv/mm_trt.cu:39-206) and
@@ -229,6 +253,19 @@ int d3d_simple_mean_encoder_workspace(const d3d_voxel_encoder_params* p, const d
 int d3d_simple_mean_encoder_enqueue(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
                                     const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                     void* const* outputs, void* workspace, size_t workspace_bytes, void* stream);
+/* Optional extra output (no reference counterpart; in the reference's graph TensorRT inserts a reformat layer
+ * between the fp32 encoder and the fp16 convolutions): the voxel means also in half / bfloat16, in rows of
+ * lp_channels >= C channels (the additional channels zero), for the live voxels -- the tensor the first SPConvMM
+ * reads.  Rows beyond numActOut are left untouched. */
+typedef struct {
+  void* lp_feats;      /* [maxNumActOut, lp_channels], or NULL */
+  int32_t lp_dtype;    /* D3D_HALF or D3D_BF16 */
+  int32_t lp_channels; /* >= C */
+} d3d_mean_encoder_extras;
+int d3d_simple_mean_encoder_enqueue_ex(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
+                                       const d3d_tensor_desc* out, int n_out, const void* const* inputs,
+                                       void* const* outputs, void* workspace, size_t workspace_bytes, void* stream,
+                                       const d3d_mean_encoder_extras* extras);
 
 /* ---------------------------------------------------------------------------------------------
  * CylinderEncoder.  Replaces voxel_encoder::CylinderEncoderPlugin

@@ -189,3 +189,29 @@ def test_bev_densify_config3_shape(d3d, orc):
                               _shape([1, 0, 2, y, x]), 256)
         want = orc.bev_densify(feats.astype(np.float32), coors, n, [1, 0, 2, y, x])
         assert (out.float().cpu().numpy() == want).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_mean_encoder_low_precision_output(d3d, dtype):
+    """The optional extra output of SimpleMeanEncoder: the voxel means in half / bfloat16, zero-padded to 16
+    channels, equal to rounding the fp32 output (what a separate cast-and-pad kernel would give)."""
+    from deploy3d_b200 import synth
+    from deploy3d_b200.ops import data_s_voxel_encoder
+    from deploy3d_b200.plugins import deserialize_plugin
+    f = synth.config4_points()
+    n = 50000
+    pts = torch.from_numpy(f["points"][:n]).cuda()
+    batch = torch.zeros(n, dtype=torch.int32, device="cuda")
+    cfg = torch.from_numpy(f["voxel_config"]).cuda()
+    shp = torch.empty(f["spatial_shape"], dtype=torch.int32, device="cuda")
+    plug = deserialize_plugin("SimpleMeanEncoder", data_s_voxel_encoder(n))
+    feats = torch.zeros((n, 5), device="cuda")
+    coors = torch.zeros((n, 4), dtype=torch.int32, device="cuda")
+    num = torch.zeros(1, dtype=torch.int32, device="cuda")
+    lp = torch.full((n, 16), 7.0, dtype=dtype, device="cuda")
+    plug.enqueue_lp(pts, batch, cfg, shp, outputs=[feats, coors, num], lp_feats=lp)
+    torch.cuda.synchronize()
+    m = int(num.item())
+    assert 0 < m < n
+    assert torch.equal(lp[:m, :5], feats[:m].to(dtype)) and bool((lp[:m, 5:] == 0).all())
+    assert bool((lp[m:] == 7.0).all())  # rows beyond numActOut are left alone

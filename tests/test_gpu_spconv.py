@@ -268,3 +268,64 @@ def test_error_codes(d3d):
         mm.enqueue(torch.zeros((10, 4), dtype=torch.int8, device=DEV), n, n, idx, n)
     assert e.value.status == -2
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("ks,dil", [((3, 3, 3), (1, 1, 1)), ((3, 1, 3), (1, 1, 1)), ((1, 3, 3), (1, 2, 1)),
+                                    ((3, 1, 1), (1, 1, 1)), ((5, 3, 3), (1, 1, 1))])
+def test_extended_enqueue_same_index_and_table(d3d, ks, dil):
+    """d3d_spconv_index_enqueue_ex on buffers the caller keeps across calls: the index tensor is byte-identical to
+    the plain entry point's on every call although only the stale padding is refilled (three voxel sets of
+    different sizes in turn, shrinking and growing), and the neighbour table the probe kernel writes equals the one
+    d3d_spconv_mm_prepare builds from the rulebook (ids and per-tile offset masks)."""
+    from deploy3d_b200.ops import data_s_spconv_index
+    from deploy3d_b200.plugins import SPConvMMPlugin, deserialize_plugin
+    shape_b, cap = [2, 20, 26, 22], 5000
+    pad = tuple(d * (k // 2) for k, d in zip(ks, dil))
+    kvol = int(np.prod(ks))
+    blob = data_s_spconv_index(ks, (1, 1, 1), pad, dil, (0, 0, 0), cap, True, False)
+    plain, ex = deserialize_plugin("SPConvIdx3d", blob), deserialize_plugin("SPConvIdx3d", blob)
+    assert ex.subm_table_ok()
+    shp = torch.empty([shape_b[0], 0] + shape_b[1:], dtype=torch.int32, device=DEV)
+    index = torch.full((3, kvol * (cap + 128)), 12345, dtype=torch.int32, device=DEV)  # garbage: first_call fills all
+    num_index = torch.zeros(1, dtype=torch.int32, device=DEV)
+    nbytes = SPConvMMPlugin.table_bytes(kvol, cap)
+    table = torch.full((nbytes,), 77, dtype=torch.uint8, device=DEV)
+    tiles = (cap + 127) // 128
+    ids_bytes = kvol * tiles * 128 * 4
+    mask_off = (ids_bytes + 255) // 256 * 256
+    for call, n in enumerate((4000, 900, 2500, 4999, 1)):
+        coors = torch.zeros((cap, 4), dtype=torch.int32, device=DEV)
+        coors[:n] = _t(unique_coors(rng(500 + n), n, shape_b))
+        num = torch.tensor([n], dtype=torch.int32, device=DEV)
+        want = plain.enqueue(coors, num, shp)
+        ex.enqueue_ex(coors, num, shp, outputs=[index, num_index], persistent=True, first_call=call == 0,
+                      subm_table=table)
+        assert int(num_index.item()) == int(want[1].item())
+        assert torch.equal(index, want[0]), "call %d: index differs from the plain entry point's" % call
+        ref_table = SPConvMMPlugin.prepare(kvol, False, cap, want[0], want[1])
+        assert torch.equal(table[:ids_bytes].view(torch.int32), ref_table[:ids_bytes].view(torch.int32))
+        assert torch.equal(table[mask_off:mask_off + 4 * tiles].view(torch.int32),
+                           ref_table[mask_off:mask_off + 4 * tiles].view(torch.int32))
+
+
+def test_extended_enqueue_strided_persistent(d3d):
+    """Stale-padding-only refill for a strided rulebook: same index bytes as the plain entry point over several
+    voxel sets."""
+    from deploy3d_b200.ops import data_s_spconv_index
+    from deploy3d_b200.plugins import deserialize_plugin
+    shape_b, cap, mout = [1, 24, 40, 36], 6000, 30000
+    blob = data_s_spconv_index((3, 3, 3), (2, 2, 2), (1, 1, 1), (1, 1, 1), (0, 0, 0), mout, False, False)
+    plain, ex = deserialize_plugin("SPConvIdx3d", blob), deserialize_plugin("SPConvIdx3d", blob)
+    assert not ex.subm_table_ok()
+    shp = torch.empty([1, 0, 24, 40, 36], dtype=torch.int32, device=DEV)
+    outs = None
+    for call, n in enumerate((5000, 700, 3000)):
+        coors = torch.zeros((cap, 4), dtype=torch.int32, device=DEV)
+        coors[:n] = _t(unique_coors(rng(700 + n), n, shape_b))
+        num = torch.tensor([n], dtype=torch.int32, device=DEV)
+        want = plain.enqueue(coors, num, shp)
+        if outs is None:
+            outs = [torch.full_like(t, 99) if t.numel() else t for t in want]
+        ex.enqueue_ex(coors, num, shp, outputs=outs, persistent=True, first_call=call == 0)
+        m = int(want[3].item())
+        assert int(outs[3].item()) == m and torch.equal(outs[0], want[0]) and torch.equal(outs[2][:m], want[2][:m])
