@@ -40,7 +40,7 @@ def measured_peaks():
         with open(path) as f:
             p = json.load(f)
         return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"], source="measured (MEASURED_PEAKS.json)")
-    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback (earlier measurement on this pool)")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback (MEASURED_PEAKS.json absent: earlier B200 measurement)")
 
 
 class ClockSampler:

@@ -14,6 +14,7 @@ D3D_MAX_DIMS = 8
 D3D_MAX_NDIM = 4
 
 D3D_FLOAT, D3D_HALF, D3D_INT8, D3D_INT32, D3D_BOOL, D3D_BF16 = 0, 1, 2, 3, 4, 7
+D3D_STATUS_HASH_FULL, D3D_STATUS_OUTPUT_OVERFLOW = 1, 2
 
 
 class TensorDesc(ctypes.Structure):
@@ -34,11 +35,12 @@ class SpconvIndexParams(ctypes.Structure):
 
 class SpconvIndexExtras(ctypes.Structure):
     _fields_ = [("persistent_buffers", ctypes.c_int32), ("first_call", ctypes.c_int32),
-                ("subm_table", ctypes.c_void_p)]
+                ("subm_table", ctypes.c_void_p), ("status", ctypes.c_void_p)]
 
 
 class MeanEncoderExtras(ctypes.Structure):
-    _fields_ = [("lp_feats", ctypes.c_void_p), ("lp_dtype", ctypes.c_int32), ("lp_channels", ctypes.c_int32)]
+    _fields_ = [("lp_feats", ctypes.c_void_p), ("lp_dtype", ctypes.c_int32), ("lp_channels", ctypes.c_int32),
+                ("status", ctypes.c_void_p)]
 
 
 class SpconvMMParams(ctypes.Structure):

@@ -88,6 +88,7 @@ extern "C" int d3d_bev_densify_workspace(const d3d_bev_densify_params* p, const 
 extern "C" int d3d_bev_densify_enqueue(const d3d_bev_densify_params* p, const d3d_tensor_desc* in, int n_in,
                                        const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                        void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  D3D_NVTX_RANGE("d3d_bev_densify_enqueue");
   D3D_REQUIRE(p && in && out && inputs && outputs && n_in >= 4 && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
   int64_t elems;
   int rc = densify_map_elems(in, n_in, &elems);

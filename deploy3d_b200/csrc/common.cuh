@@ -4,11 +4,33 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <nvtx3/nvToolsExt.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "../../include/deploy3d_b200.h"
 
 namespace d3d {
+
+// NVTX range around every C-ABI enqueue, off unless the process was started with D3D_NVTX=1 (the reference has a
+// per-layer profiler on the TensorRT side only, deploy3d/symfun/trt_utils/trt_module.py:20-44).
+inline bool nvtx_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("D3D_NVTX");
+    return v && v[0] == '1';
+  }();
+  return on;
+}
+struct NvtxRange {
+  bool on;
+  explicit NvtxRange(const char* name) : on(nvtx_enabled()) {
+    if (on) nvtxRangePushA(name);
+  }
+  ~NvtxRange() {
+    if (on) nvtxRangePop();
+  }
+};
+#define D3D_NVTX_RANGE(name) ::d3d::NvtxRange d3d_nvtx_range_(name)
 
 constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids of streaming kernels are sized in multiples of it
 
@@ -185,8 +207,17 @@ __device__ __forceinline__ uint32_t hash_capacity(long long keys, uint32_t cap_m
   return cap;
 }
 
-// Single CTA: in-place exclusive scan of `totals[0..n)`; *clamped_total = min(sum, limit).
-static __global__ void scan_totals_kernel(int32_t* totals, int n, int32_t limit, int32_t* clamped_total) {
+// Soft failures a kernel reports in the caller's optional status word (atomicOr; the word is the caller's to
+// clear): they drop work instead of faulting, exactly where the reference is silent
+// (trt/include/common/hash32.h:70, trt/spconv/index.cu:163-168).
+__device__ __forceinline__ void report_status(int32_t* status, int bit) {
+  if (status) atomicOr(status, bit);
+}
+
+// Single CTA: in-place exclusive scan of `totals[0..n)`; *clamped_total = min(sum, limit).  A sum above the limit
+// (more voxels than the output buffers hold: the surplus is dropped) sets D3D_STATUS_OUTPUT_OVERFLOW.
+static __global__ void scan_totals_kernel(int32_t* totals, int n, int32_t limit, int32_t* clamped_total,
+                                          int32_t* status = nullptr) {
   __shared__ int scratch[40];
   int carry = 0;
   for (int base = 0; base < n; base += blockDim.x) {
@@ -197,7 +228,10 @@ static __global__ void scan_totals_kernel(int32_t* totals, int n, int32_t limit,
     if (j < n) totals[j] = carry + ex;
     carry += total;
   }
-  if (threadIdx.x == 0) *clamped_total = carry < limit ? carry : limit;
+  if (threadIdx.x == 0) {
+    *clamped_total = carry < limit ? carry : limit;
+    if (carry > limit) report_status(status, D3D_STATUS_OUTPUT_OVERFLOW);
+  }
 }
 
 }  // namespace d3d

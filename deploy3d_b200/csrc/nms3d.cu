@@ -15,6 +15,8 @@
 //                  (nms3d.cu:106-127, launched <<<B, 1>>>).
 #include <math.h>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace d3d {
@@ -307,9 +309,28 @@ extern "C" int d3d_nms3d_workspace(const d3d_nms3d_params* p, const d3d_tensor_d
   return D3D_OK;
 }
 
+// The two launches of an NMS3d call over a mask scratch of b * k * nw words.  Neither sweep reads a word the mask
+// kernel did not write in the same call (the diagonal word and the words behind it; the staged sweep copies whole
+// rows into shared memory but uses the same words), so the scratch needs no initialisation.
+static int launch_nms(const d3d_nms3d_params* p, int b, int k, int bd, int nw, const void* const* inputs,
+                      void* const* outputs, unsigned long long* mask, void* stream) {
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  overlap_mask_kernel<<<dim3(nw, nw, b), 256, 0, st>>>(reinterpret_cast<const float*>(inputs[1]), k, bd,
+                                                       p->iou_threshold, nw, mask);
+  if (nw <= kStagedMaxWords)
+    suppress_staged_kernel<<<b, kStagedThreads, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
+                                                         reinterpret_cast<float*>(outputs[0]));
+  else
+    suppress_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
+                                      reinterpret_cast<float*>(outputs[0]));
+  D3D_CHECK_LAUNCH();
+  return D3D_OK;
+}
+
 extern "C" int d3d_nms3d_enqueue(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in,
                                  const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                  void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  D3D_NVTX_RANGE("d3d_nms3d_enqueue");
   D3D_REQUIRE(p && out && inputs && outputs && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
   int b, k, bd;
   int rc = nms_dims(in, n_in, &b, &k, &bd);
@@ -318,18 +339,7 @@ extern "C" int d3d_nms3d_enqueue(const d3d_nms3d_params* p, const d3d_tensor_des
   const int nw = (int)ceil_div(k, kNmsBlock);
   D3D_REQUIRE(workspace && workspace_bytes >= (size_t)b * k * nw * sizeof(unsigned long long),
               D3D_ERR_WORKSPACE_TOO_SMALL);
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  unsigned long long* mask = reinterpret_cast<unsigned long long*>(workspace);
-  overlap_mask_kernel<<<dim3(nw, nw, b), 256, 0, st>>>(reinterpret_cast<const float*>(inputs[1]), k, bd,
-                                                       p->iou_threshold, nw, mask);
-  if (nw <= kStagedMaxWords)
-    suppress_staged_kernel<<<b, kStagedThreads, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
-                                             reinterpret_cast<float*>(outputs[0]));
-  else
-    suppress_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
-                                      reinterpret_cast<float*>(outputs[0]));
-  D3D_CHECK_LAUNCH();
-  return D3D_OK;
+  return launch_nms(p, b, k, bd, nw, inputs, outputs, reinterpret_cast<unsigned long long*>(workspace), stream);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -353,12 +363,14 @@ static __device__ __align__(256) unsigned long long g_nms_static_mask[D3D_NMS3D_
 
 namespace {
 constexpr int kMaxStaticDevices = 64;
-unsigned long long* g_nms_static_ptr[kMaxStaticDevices];  // per-device address of g_nms_static_mask, 0 = not yet known
+// per-device address of g_nms_static_mask, null = not yet known; atomic because any host thread may be the first
+std::atomic<unsigned long long*> g_nms_static_ptr[kMaxStaticDevices];
 }  // namespace
 
 extern "C" int d3d_nms3d_enqueue_static(const d3d_nms3d_params* p, const d3d_tensor_desc* in, int n_in,
                                         const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                         void* const* outputs, void* stream) {
+  D3D_NVTX_RANGE("d3d_nms3d_enqueue_static");
   D3D_REQUIRE(p && out && inputs && outputs && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
   int b, k, bd;
   int rc = nms_dims(in, n_in, &b, &k, &bd);
@@ -369,18 +381,13 @@ extern "C" int d3d_nms3d_enqueue_static(const d3d_nms3d_params* p, const d3d_ten
   D3D_REQUIRE((size_t)b * k * nw <= (size_t)D3D_NMS3D_STATIC_MAX_WORDS, D3D_ERR_TOO_LARGE);
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxStaticDevices) return D3D_ERR_CUDA;
-  unsigned long long* mask = g_nms_static_ptr[dev];
+  unsigned long long* mask = g_nms_static_ptr[dev].load(std::memory_order_acquire);
   if (!mask) {
     void* addr = nullptr;
     if (cudaGetSymbolAddress(&addr, g_nms_static_mask) != cudaSuccess || !addr) return D3D_ERR_CUDA;
     mask = reinterpret_cast<unsigned long long*>(addr);
-    g_nms_static_ptr[dev] = mask;  // same value whichever thread stores it first
+    g_nms_static_ptr[dev].store(mask, std::memory_order_release);  // the same value whichever thread stores it
   }
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  overlap_mask_kernel<<<dim3(nw, nw, b), 256, 0, st>>>(reinterpret_cast<const float*>(inputs[1]), k, bd,
-                                                       p->iou_threshold, nw, mask);
-  suppress_kernel<<<b, 32, 0, st>>>(mask, reinterpret_cast<const float*>(inputs[0]), k, nw,
-                                    reinterpret_cast<float*>(outputs[0]));
-  D3D_CHECK_LAUNCH();
-  return D3D_OK;
+  // the same launches as the workspace variant, over the built-in scratch
+  return launch_nms(p, b, k, bd, nw, inputs, outputs, mask, stream);
 }

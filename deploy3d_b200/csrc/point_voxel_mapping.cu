@@ -85,6 +85,7 @@ extern "C" int d3d_scatter_to_parse(const void* data_s, size_t len, d3d_scatter_
 extern "C" int d3d_scatter_to_enqueue(const d3d_scatter_to_params* p, const d3d_tensor_desc* in, int n_in,
                                       const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                       void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  D3D_NVTX_RANGE("d3d_scatter_to_enqueue");
   (void)workspace, (void)workspace_bytes;
   D3D_REQUIRE(p && in && out && inputs && outputs && n_in >= 3 && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
   D3D_REQUIRE(in[0].dtype == D3D_FLOAT, D3D_ERR_UNSUPPORTED_DTYPE);
@@ -127,6 +128,7 @@ extern "C" int d3d_gather_back_parse(const void* data_s, size_t len, d3d_gather_
 extern "C" int d3d_gather_back_enqueue(const d3d_gather_back_params* p, const d3d_tensor_desc* in, int n_in,
                                        const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                        void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  D3D_NVTX_RANGE("d3d_gather_back_enqueue");
   (void)workspace, (void)workspace_bytes;
   D3D_REQUIRE(p && in && out && inputs && outputs && n_in >= 2 && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
   D3D_REQUIRE(in[0].dtype == D3D_FLOAT, D3D_ERR_UNSUPPORTED_DTYPE);

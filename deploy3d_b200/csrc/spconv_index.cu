@@ -110,7 +110,8 @@ __global__ void reset_table_kernel(unsigned long long* table, const int32_t* num
 }
 
 __global__ void subm_insert_kernel(unsigned long long* table, const int32_t* __restrict__ coors,
-                                   const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max) {
+                                   const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
+                                   int32_t* status) {
   int n = live_count(num_act_in, n_max);
   uint32_t mask = hash_capacity((long long)n * kSubmFan, cap_max) - 1;
   int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -122,7 +123,7 @@ __global__ void subm_insert_kernel(unsigned long long* table, const int32_t* __r
     if (c[d] < 0 || c[d] >= g.shape[d]) return;
     key = key * (uint32_t)g.shape[d] + (uint32_t)c[d];
   }
-  hash_insert_min(table, mask, key, (uint32_t)i);
+  if (hash_insert_min(table, mask, key, (uint32_t)i) == 0xFFFFFFFFu) report_status(status, D3D_STATUS_HASH_FULL);
 }
 
 // SubM probe: pair_out[k][i] = id of the active voxel at (coor_i + pad - k*dil), or -1 (trt/spconv/index.cu:48-84).
@@ -320,7 +321,7 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
 // survives in the slot.  pair_out[k][i] receives the slot (>= 0) or -1.
 __global__ void conv_insert_kernel(unsigned long long* table, const int32_t* __restrict__ coors,
                                    const int32_t* num_act_in, int64_t n_max, Geometry g, int fan, uint32_t cap_max,
-                                   int32_t* __restrict__ pair_out) {
+                                   int32_t* __restrict__ pair_out, int32_t* status) {
   int n = live_count(num_act_in, n_max);
   if ((int64_t)blockIdx.x * kIdxThreads >= n) return;
   uint32_t mask = hash_capacity((long long)n * fan, cap_max) - 1;
@@ -339,6 +340,7 @@ __global__ void conv_insert_kernel(unsigned long long* table, const int32_t* __r
       uint32_t slot = hash_insert_min(table, mask, prefix * (uint32_t)g.shape[dl + 1] + (uint32_t)o,
                                       (uint32_t)(i * g.kvol + k));
       v = slot == 0xFFFFFFFFu ? -1 : (int)slot;
+      if (slot == 0xFFFFFFFFu) report_status(status, D3D_STATUS_HASH_FULL);
     }
     pair_out[(int64_t)k * n_max + i] = v;
   }
@@ -363,7 +365,8 @@ __device__ __forceinline__ int entry_value(int e) { return e & kPackedValueMask;
 template <bool kPacked>
 __global__ void __launch_bounds__(kIdxThreads)
 conv_insert3_kernel(unsigned long long* table, const int32_t* __restrict__ coors, const int32_t* num_act_in,
-                    int64_t n_max, Geometry g, int fan, uint32_t cap_max, int32_t* __restrict__ pair_out) {
+                    int64_t n_max, Geometry g, int fan, uint32_t cap_max, int32_t* __restrict__ pair_out,
+                    int32_t* status) {
   constexpr bool kPacked_ = kPacked;
   const int n = live_count(num_act_in, n_max);
   const int i = blockIdx.x * kIdxThreads + threadIdx.x;
@@ -395,6 +398,7 @@ conv_insert3_kernel(unsigned long long* table, const int32_t* __restrict__ coors
             const uint32_t key = (((uint32_t)c.x * s1 + (uint32_t)o0[k0]) * s2 + (uint32_t)o1[k1]) * s3 + (uint32_t)o2[k2];
             const uint32_t slot = hash_insert_min(table, mask, key, pair_base + (uint32_t)k);
             v = slot == 0xFFFFFFFFu ? -1 : (int)slot;
+            if (slot == 0xFFFFFFFFu) report_status(status, D3D_STATUS_HASH_FULL);
           }
           if (!kPacked_) {
             pair_out[(int64_t)k * n_max + i] = v;
@@ -962,6 +966,7 @@ extern "C" int d3d_spconv_index_workspace(const d3d_spconv_index_params* p, cons
 extern "C" int d3d_spconv_index_enqueue(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
                                         const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                         void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  D3D_NVTX_RANGE("d3d_spconv_index_enqueue");
   return d3d_spconv_index_enqueue_ex(p, in, n_in, out, n_out, inputs, outputs, workspace, workspace_bytes, stream,
                                      nullptr);
 }
@@ -979,10 +984,12 @@ extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, con
                                            const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                            void* const* outputs, void* workspace, size_t workspace_bytes,
                                            void* stream, const d3d_spconv_index_extras* extras) {
+  D3D_NVTX_RANGE("d3d_spconv_index_enqueue_ex");
   D3D_REQUIRE(inputs && outputs && out, D3D_ERR_INVALID_ARGUMENT);
   const int persistent = extras ? extras->persistent_buffers : 0;
   const int first = extras ? extras->first_call : 1;
   int32_t* nbr = extras ? reinterpret_cast<int32_t*>(extras->subm_table) : nullptr;
+  int32_t* status = extras ? extras->status : nullptr;
   D3D_REQUIRE(!nbr || d3d_spconv_index_subm_table_ok(p), D3D_ERR_INVALID_ARGUMENT);
   Plan plan;
   int rc = make_plan(p, in, n_in, workspace, &plan);
@@ -1008,7 +1015,7 @@ extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, con
   reset_table_kernel<<<stream_grid(plan.cap_max / 2, 256), 256, 0, st>>>(plan.table, num_act_in, n_max, plan.fan,
                                                                          plan.cap_max);
   if (p->subm) {
-    subm_insert_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max);
+    subm_insert_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max, status);
     if (g.ndim == 3 && !g.transpose && g.stride[0] == 1 && g.stride[1] == 1 && g.stride[2] == 1) {
       // the fused neighbour table covers ceil(n_max / 128) tiles, masks right behind the ids (SPConvMM's layout)
       const int64_t nbr_tiles = (n_max + 127) / 128;
@@ -1038,16 +1045,16 @@ extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, con
     D3D_REQUIRE(out[2].dims[0] >= p->max_num_act_out, D3D_ERR_INVALID_ARGUMENT);
     if (plan.packed)
       conv_insert3_kernel<true><<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.fan,
-                                                              plan.cap_max, plan.pair_out);
+                                                              plan.cap_max, plan.pair_out, status);
     else if (g.ndim == 3 && g.ksize[0] <= 3 && g.ksize[1] <= 3 && g.ksize[2] <= 3)
       conv_insert3_kernel<false><<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.fan,
-                                                               plan.cap_max, plan.pair_out);
+                                                               plan.cap_max, plan.pair_out, status);
     else
       conv_insert_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
-                                                                     plan.fan, plan.cap_max, plan.pair_out);
+                                                                     plan.fan, plan.cap_max, plan.pair_out, status);
     conv_count_winners_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g.kvol,
                                                             plan.packed, plan.winners, plan.win_bits);
-    scan_totals_kernel<<<1, 1024, 0, st>>>(plan.winners, nblk, p->max_num_act_out, num_act_out);
+    scan_totals_kernel<<<1, 1024, 0, st>>>(plan.winners, nblk, p->max_num_act_out, num_act_out, status);
     conv_assign_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, plan.pair_out, num_act_in, n_max, g, plan.winners,
                                                      plan.win_bits,
                                                      p->max_num_act_out, plan.packed, plan.slot_out, out_coors);

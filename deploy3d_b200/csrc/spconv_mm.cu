@@ -387,6 +387,7 @@ extern "C" int d3d_spconv_mm_workspace(d3d_spconv_mm_t h, const d3d_tensor_desc*
 
 extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int mode, int64_t max_num_act_out, const int32_t* index,
                                      int64_t index_row_len, const int32_t* num_index, void* table, void* stream) {
+  D3D_NVTX_RANGE("d3d_spconv_mm_prepare");
   D3D_REQUIRE(kernel_vol >= 1 && max_num_act_out >= 0 && index_row_len >= 0 && mode >= 0 && mode <= 3,
               D3D_ERR_INVALID_ARGUMENT);
   if (max_num_act_out == 0) return D3D_OK;
@@ -413,6 +414,7 @@ extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int mode, int64_t max_num_a
 extern "C" int d3d_spconv_mm_run(d3d_spconv_mm_t h, int dtype, const void* in_feats, int64_t max_num_act_in,
                                  const int32_t* num_act_out, const void* table, void* out_feats,
                                  const d3d_spconv_mm_epilogue* epilogue, void* stream) {
+  D3D_NVTX_RANGE("d3d_spconv_mm_run");
   D3D_REQUIRE(h, D3D_ERR_INVALID_ARGUMENT);
   D3D_REQUIRE(dtype == D3D_FLOAT || dtype == D3D_HALF || dtype == D3D_BF16, D3D_ERR_UNSUPPORTED_DTYPE);
   D3D_REQUIRE(h->dtype == dtype, D3D_ERR_INVALID_ARGUMENT);  // configure() must have run for this dtype
@@ -436,6 +438,7 @@ extern "C" int d3d_spconv_mm_run(d3d_spconv_mm_t h, int dtype, const void* in_fe
 extern "C" int d3d_spconv_mm_enqueue(d3d_spconv_mm_t h, const d3d_tensor_desc* in, int n_in,
                                      const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                      void* const* outputs, void* workspace, size_t workspace_bytes, void* stream) {
+  D3D_NVTX_RANGE("d3d_spconv_mm_enqueue");
   D3D_REQUIRE(h && in && out && inputs && outputs && n_in >= 5 && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
   int dtype = in[0].dtype;
   D3D_REQUIRE(dtype == D3D_FLOAT || dtype == D3D_HALF || dtype == D3D_BF16, D3D_ERR_UNSUPPORTED_DTYPE);

@@ -32,7 +32,7 @@ __device__ __forceinline__ bool all_finite(const float* __restrict__ p, int c) {
 // trt/voxel_encoder/simple_mean_trt.cu:28-60: truncation toward zero, bounds check, insert.
 __global__ void voxelize_kernel(unsigned long long* table, uint32_t cap_mask, const float* __restrict__ pts,
                                 const int32_t* __restrict__ batch, const float* __restrict__ cfg, int64_t n, int c,
-                                int sb, int sz, int sy, int sx, int32_t* __restrict__ slot_of) {
+                                int sb, int sz, int sy, int sx, int32_t* __restrict__ slot_of, int32_t* status) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const float* p = pts + i * c;
@@ -46,6 +46,7 @@ __global__ void voxelize_kernel(unsigned long long* table, uint32_t cap_mask, co
       uint32_t key = (((uint32_t)b * sz + cz) * sy + cy) * sx + cx;
       uint32_t s = hash_insert_min(table, cap_mask, key, (uint32_t)i);
       slot = s == 0xFFFFFFFFu ? -1 : (int)s;
+      if (s == 0xFFFFFFFFu) report_status(status, D3D_STATUS_HASH_FULL);
     }
   }
   slot_of[i] = slot;
@@ -277,6 +278,7 @@ extern "C" int d3d_simple_mean_encoder_enqueue(const d3d_voxel_encoder_params* p
                                                const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                                void* const* outputs, void* workspace, size_t workspace_bytes,
                                                void* stream) {
+  D3D_NVTX_RANGE("d3d_simple_mean_encoder_enqueue");
   return d3d_simple_mean_encoder_enqueue_ex(p, in, n_in, out, n_out, inputs, outputs, workspace, workspace_bytes,
                                             stream, nullptr);
 }
@@ -286,8 +288,10 @@ extern "C" int d3d_simple_mean_encoder_enqueue_ex(const d3d_voxel_encoder_params
                                                   const void* const* inputs, void* const* outputs, void* workspace,
                                                   size_t workspace_bytes, void* stream,
                                                   const d3d_mean_encoder_extras* extras) {
+  D3D_NVTX_RANGE("d3d_simple_mean_encoder_enqueue_ex");
   D3D_REQUIRE(inputs && outputs && out && n_out >= 3, D3D_ERR_INVALID_ARGUMENT);
   void* lp = extras ? extras->lp_feats : nullptr;
+  int32_t* status = extras ? extras->status : nullptr;
   D3D_REQUIRE(!lp || ((extras->lp_dtype == D3D_HALF || extras->lp_dtype == D3D_BF16) &&
                       extras->lp_channels >= in[0].dims[1]),
               D3D_ERR_INVALID_ARGUMENT);
@@ -308,10 +312,10 @@ extern "C" int d3d_simple_mean_encoder_enqueue_ex(const d3d_voxel_encoder_params
                                                              m_max * pl.c);
   if (pl.n > 0) {
     voxelize_kernel<<<pl.nblk, kEncThreads, 0, st>>>(pl.table, pl.cap - 1, pts, batch, cfg, pl.n, pl.c, pl.dims[0],
-                                                     pl.dims[1], pl.dims[2], pl.dims[3], pl.slot_of);
+                                                     pl.dims[1], pl.dims[2], pl.dims[3], pl.slot_of, status);
     count_owners_kernel<<<pl.nblk, kEncThreads, 0, st>>>(pl.table, pl.slot_of, pl.n, pl.owners);
   }
-  scan_totals_kernel<<<1, 1024, 0, st>>>(pl.owners, pl.n > 0 ? pl.nblk : 0, (int32_t)m_max, num_act_out);
+  scan_totals_kernel<<<1, 1024, 0, st>>>(pl.owners, pl.n > 0 ? pl.nblk : 0, (int32_t)m_max, num_act_out, status);
   if (pl.n > 0 && m_max > 0) {
     number_voxels_kernel<<<pl.nblk, kEncThreads, 0, st>>>(pl.table, pl.slot_of, pl.n, pl.owners, m_max, pl.dims[1],
                                                           pl.dims[2], pl.dims[3], pl.slot_vid, out_coors);
@@ -332,6 +336,7 @@ extern "C" int d3d_cylinder_encoder_enqueue(const d3d_voxel_encoder_params* p, c
                                             const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                             void* const* outputs, void* workspace, size_t workspace_bytes,
                                             void* stream) {
+  D3D_NVTX_RANGE("d3d_cylinder_encoder_enqueue");
   D3D_REQUIRE(inputs && outputs && out && n_out >= 5, D3D_ERR_INVALID_ARGUMENT);
   EncPlan pl;
   int rc = make_enc_plan(p, in, n_in, workspace, false, &pl);

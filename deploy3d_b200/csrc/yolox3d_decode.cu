@@ -234,6 +234,7 @@ extern "C" int d3d_yolox3d_decode_enqueue(const d3d_yolox3d_decode_params* p, co
                                           const d3d_tensor_desc* out, int n_out, const void* const* inputs,
                                           void* const* outputs, void* workspace, size_t workspace_bytes,
                                           void* stream) {
+  D3D_NVTX_RANGE("d3d_yolox3d_decode_enqueue");
   (void)workspace, (void)workspace_bytes;
   D3D_REQUIRE(out && inputs && outputs, D3D_ERR_INVALID_ARGUMENT);
   int b, c, y, x, box_in, k;

@@ -132,7 +132,8 @@ class SPConvIdxPlugin(_Plugin):
         """True when enqueue_ex can write SPConvMM's neighbour table itself (mirror-symmetric 3-D SubM rulebook)."""
         return bool(lib().d3d_spconv_index_subm_table_ok(ctypes.byref(self.p)))
 
-    def enqueue_ex(self, *inputs, outputs, persistent=False, first_call=True, subm_table=None, stream=None):
+    def enqueue_ex(self, *inputs, outputs, persistent=False, first_call=True, subm_table=None, status=None,
+                   stream=None):
         """enqueue for a caller that owns its buffers across calls: `persistent` refills only the stale part of the
         -1 padding (same bytes in `index`), `subm_table` receives the neighbour table of a mirror-symmetric SubM
         rulebook straight from the probe kernel.  `outputs` must be given (they are the persistent buffers)."""
@@ -143,7 +144,8 @@ class SPConvIdxPlugin(_Plugin):
         ws_bytes = self.workspace_size(in_descs)
         ws = self._get_workspace(ws_bytes, device)
         extras = _lib.SpconvIndexExtras(int(bool(persistent)), int(bool(first_call)),
-                                        subm_table.data_ptr() if subm_table is not None else None)
+                                        subm_table.data_ptr() if subm_table is not None else None,
+                                        status.data_ptr() if status is not None else None)
         with torch.cuda.device(device):
             status = lib().d3d_spconv_index_enqueue_ex(
                 ctypes.byref(self.p), desc_array(in_descs), len(in_descs), desc_array(out_descs), len(out_descs),
@@ -270,15 +272,19 @@ class SimpleMeanEncoderPlugin(_PodPlugin):
     num_outputs = 3
 
 
-    def enqueue_lp(self, *inputs, outputs, lp_feats, stream=None):
-        """enqueue that also writes the voxel means in half / bfloat16, zero-padded to lp_feats.shape[1] channels."""
+    def enqueue_lp(self, *inputs, outputs, lp_feats=None, status=None, stream=None):
+        """enqueue that also writes the voxel means in half / bfloat16, zero-padded to lp_feats.shape[1] channels,
+        and / or reports soft failures (D3D_STATUS_* bits) in the int32 device tensor `status`."""
         inputs = [t if t.is_contiguous() else t.contiguous() for t in inputs]
         device = inputs[0].device
         in_descs = [_desc_of(t) for t in inputs]
         out_descs = self.output_descs(in_descs)
         ws_bytes = self.workspace_size(in_descs)
         ws = self._get_workspace(ws_bytes, device)
-        extras = _lib.MeanEncoderExtras(lp_feats.data_ptr(), _TORCH2D3D[lp_feats.dtype], int(lp_feats.shape[1]))
+        extras = _lib.MeanEncoderExtras(lp_feats.data_ptr() if lp_feats is not None else None,
+                                        _TORCH2D3D[lp_feats.dtype] if lp_feats is not None else 0,
+                                        int(lp_feats.shape[1]) if lp_feats is not None else 0,
+                                        status.data_ptr() if status is not None else None)
         with torch.cuda.device(device):
             status = lib().d3d_simple_mean_encoder_enqueue_ex(
                 ctypes.byref(self.p), desc_array(in_descs), len(in_descs), desc_array(out_descs), len(out_descs),

@@ -40,6 +40,13 @@ typedef enum {
   D3D_ERR_TOO_LARGE = -6
 } d3d_status;
 
+/* Soft failures: a kernel that has to drop work ORs one of these bits into the device word the caller passed in the
+ * `status` field of an extras struct (never a trap, never a host synchronisation; the caller reads and clears the
+ * word when it likes).  The reference is silent in both cases: an insert into a full table returns "no slot"
+ * (trt/include/common/hash32.h:70) and outputs beyond maxNumActOut are dropped (trt/spconv/index.cu:163-168). */
+#define D3D_STATUS_HASH_FULL 1       /* a key found no free slot: its pairs / points were dropped */
+#define D3D_STATUS_OUTPUT_OVERFLOW 2 /* more output voxels than maxNumActOut: the surplus was dropped */
+
 /* Values follow nvinfer1::DataType so a plugin shell can pass PluginTensorDesc::type through. */
 typedef enum {
   D3D_FLOAT = 0,
@@ -128,6 +135,7 @@ typedef struct {
   int32_t persistent_buffers;
   int32_t first_call;
   void* subm_table;
+  int32_t* status; /* optional device word that receives D3D_STATUS_* bits (see below), or NULL */
 } d3d_spconv_index_extras;
 int d3d_spconv_index_subm_table_ok(const d3d_spconv_index_params* p);
 int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n_in,
@@ -261,6 +269,7 @@ typedef struct {
   void* lp_feats;      /* [maxNumActOut, lp_channels], or NULL */
   int32_t lp_dtype;    /* D3D_HALF or D3D_BF16 */
   int32_t lp_channels; /* >= C */
+  int32_t* status;     /* optional device word that receives D3D_STATUS_* bits, or NULL */
 } d3d_mean_encoder_extras;
 int d3d_simple_mean_encoder_enqueue_ex(const d3d_voxel_encoder_params* p, const d3d_tensor_desc* in, int n_in,
                                        const d3d_tensor_desc* out, int n_out, const void* const* inputs,

@@ -1,6 +1,6 @@
 """Single-layer micro-benchmark of SPConvIdx + SPConvMM on synthetic LiDAR-like voxels.
 
-    python -m deploy3d_b200.microbench --cin 128 --cout 128 --voxels 66000 [--kernel 2] [--reps 20]
+    python microbench.py --cin 128 --cout 128 --voxels 66000 [--kernel 2] [--reps 20]
 
 Builds one SubM 3x3x3 rulebook over `--voxels` LiDAR-like active voxels (or a strided one with --stride 2),
 prepares the neighbour table once and times `--reps` launches of the convolution kernel with CUDA events.
@@ -13,9 +13,9 @@ import json
 import numpy as np
 import torch
 
-from . import synth
-from .ops import data_s_spconv_index, data_s_spconv_mm
-from .plugins import SPConvMMPlugin, deserialize_plugin
+from deploy3d_b200 import synth
+from deploy3d_b200.ops import data_s_spconv_index, data_s_spconv_mm
+from deploy3d_b200.plugins import SPConvMMPlugin, deserialize_plugin
 
 
 def main():
@@ -34,7 +34,7 @@ def main():
                     help="override the tensor-core kernel's pipeline plan (0 = automatic)")
     args = ap.parse_args()
     if args.plan:
-        from . import _lib
+        from deploy3d_b200 import _lib
         _lib.check("d3d_debug_set_tc_plan", _lib.lib().d3d_debug_set_tc_plan(*args.plan))
     dev = "cuda:0"
     rng = np.random.Generator(np.random.PCG64(77))

@@ -223,7 +223,7 @@ def yolox3d_decode(cls_scores, bbox_preds, voxel_config, stride, class_ids, topk
     """Restatement of the reference's YoloX3dDecode in numpy (trt/decoder/yolox3d_decode.cu): per (batch, class) a
     stable descending sort of the Y*X scores (:341-355; equal scores keep ascending cell order), the first
     K = min(topk, Y*X) entries (:192-206) decoded by `kernel::decode` (:25-126) with its float / double mix:
-    float arithmetic, M_PI terms in double, floorf on the value rounded to float.  Pinned on the GPU box against the
+    float arithmetic, M_PI terms in double, floorf on the value rounded to float.  Pinned on a B200 against the
     reference's own plugin compiled for sm_100a (tests/test_gpu_reference.py).
     Returns [(class_ids int32 [B,K], scores float32 [B,K], boxes float32 [B,K,7+a])] per class."""
     f32, f64 = np.float32, np.float64

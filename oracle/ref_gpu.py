@@ -23,7 +23,7 @@ _i64p = ctypes.POINTER(ctypes.c_int64)
 
 
 def lib():
-    """The library, or None when it was never built (no reference checkout on the build machine)."""
+    """The library, or None when it was never built (no reference checkout where the repository was built)."""
     global _LIB
     if _LIB is None:
         path = os.path.join(_HERE, "_ref", "libref_spconv.so")

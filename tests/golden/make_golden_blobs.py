@@ -62,7 +62,9 @@ class RecordingGraph:
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    here = os.path.dirname(os.path.abspath(__file__))
+    # the reference checkout: argv[1], by default a directory `reference` beside this repository
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.path.abspath(os.path.join(here, "..", "..", "..", "reference"))
     np.bool = np.bool_  # removed from numpy; the reference's exporter still spells it this way
     sys.path.insert(0, ref)
     import deploy3d.symfun.ops as ops

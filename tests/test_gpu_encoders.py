@@ -215,3 +215,24 @@ def test_mean_encoder_low_precision_output(d3d, dtype):
     assert 0 < m < n
     assert torch.equal(lp[:m, :5], feats[:m].to(dtype)) and bool((lp[:m, 5:] == 0).all())
     assert bool((lp[m:] == 7.0).all())  # rows beyond numActOut are left alone
+
+
+def test_mean_encoder_status_word(d3d):
+    """More voxels than maxNumActOut: the surplus is dropped and D3D_STATUS_OUTPUT_OVERFLOW is reported."""
+    from deploy3d_b200 import _lib, synth
+    from deploy3d_b200.ops import data_s_voxel_encoder
+    from deploy3d_b200.plugins import deserialize_plugin
+    f = synth.config4_points()
+    n = 20000
+    pts = torch.from_numpy(f["points"][:n]).cuda()
+    batch = torch.zeros(n, dtype=torch.int32, device="cuda")
+    cfg = torch.from_numpy(f["voxel_config"]).cuda()
+    shp = torch.empty(f["spatial_shape"], dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for cap, want in ((500, _lib.D3D_STATUS_OUTPUT_OVERFLOW), (n, 0)):
+        plug = deserialize_plugin("SimpleMeanEncoder", data_s_voxel_encoder(cap))
+        outs = [torch.zeros((cap, 5), device="cuda"), torch.zeros((cap, 4), dtype=torch.int32, device="cuda"),
+                torch.zeros(1, dtype=torch.int32, device="cuda")]
+        status.zero_()
+        plug.enqueue_lp(pts, batch, cfg, shp, outputs=outs, status=status)
+        assert int(status.item()) == want and int(outs[2].item()) <= cap

@@ -23,7 +23,7 @@ DEV = "cuda:0"
 def ref():
     from oracle import ref_gpu
     if ref_gpu.lib() is None:
-        pytest.skip("oracle/_ref/libref_spconv.so was not built (no reference checkout on the build machine)")
+        pytest.skip("oracle/_ref/libref_spconv.so was not built (no reference checkout where the repository was built)")
     return ref_gpu
 
 
@@ -101,7 +101,7 @@ def _features(r, n_rows, cin, cout, kvol):
 @pytest.mark.parametrize("kind", ["subm", "strided", "inverse"])
 def test_features_match_reference_gpu(d3d, orc, ref, kind, cin, cout):
     if not ref.lib().has_mm:
-        pytest.skip("the reference convolution was not built (no CUTLASS header tree on the build machine)")
+        pytest.skip("the reference convolution was not built (no CUTLASS header tree where the repository was built)")
     r = rng(8000 + cin * 7 + cout + len(kind))
     shape_b, spatial, n = [2, 120, 90, 8], [2, 0, 120, 90, 8], 20000
     coors = unique_coors(r, n, shape_b)

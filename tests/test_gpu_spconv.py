@@ -329,3 +329,25 @@ def test_extended_enqueue_strided_persistent(d3d):
         ex.enqueue_ex(coors, num, shp, outputs=outs, persistent=True, first_call=call == 0)
         m = int(want[3].item())
         assert int(outs[3].item()) == m and torch.equal(outs[0], want[0]) and torch.equal(outs[2][:m], want[2][:m])
+
+
+def test_status_word_reports_output_overflow(d3d):
+    """The optional status word: a strided rulebook whose maxNumActOut is smaller than the number of output voxels
+    drops the surplus (as the reference does, silently, trt/spconv/index.cu:163-168) and says so in the word; a
+    rulebook that fits leaves the word alone.  Nothing faults, nothing synchronises."""
+    from deploy3d_b200 import _lib
+    from deploy3d_b200.ops import data_s_spconv_index
+    from deploy3d_b200.plugins import deserialize_plugin
+    shape_b, n = [1, 24, 40, 36], 4000
+    coors = _t(unique_coors(rng(900), n, shape_b))
+    num = torch.tensor([n], dtype=torch.int32, device=DEV)
+    shp = torch.empty([1, 0, 24, 40, 36], dtype=torch.int32, device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    for max_out, want in ((300, _lib.D3D_STATUS_OUTPUT_OVERFLOW), (40000, 0)):
+        plug = deserialize_plugin("SPConvIdx3d", data_s_spconv_index((3, 3, 3), (2, 2, 2), (1, 1, 1), (1, 1, 1),
+                                                                      (0, 0, 0), max_out, False, False))
+        outs = plug.enqueue(coors, num, shp)
+        status.zero_()
+        plug.enqueue_ex(coors, num, shp, outputs=list(outs), status=status)
+        assert int(status.item()) == want
+        assert int(outs[3].item()) == min(max_out, int(outs[3].item()))
