@@ -181,14 +181,17 @@ __global__ void subm_probe_kernel(const unsigned long long* __restrict__ table, 
 // With `nbr` != null (a mirror-symmetric rulebook: odd kernel, padding = dilation * (k - 1) / 2 on every axis) the
 // kernel also writes the output-stationary neighbour table SPConvMM consumes, [tile of 128 outputs][kvol][128]: the
 // voxel found for offset k is, read the other way round, the input that feeds voxel i through offset kvol - 1 - k,
-// so thread i fills its own column of the table -- coalesced stores, no scatter pass, no fill pass -- and the
-// per-tile offset masks are collected with shared-memory atomics.  `nbr_tiles` = tiles the table holds.
+// so thread i fills its own column of the table -- coalesced stores, no scatter pass, no fill pass.  The ballot of
+// a warp over "neighbour found" is at once the row mask of its 32 rows under that offset (`nbr_rows`, four words
+// per (tile, offset)); the per-tile offset masks are collected with shared-memory atomics.  `nbr_tiles` = tiles
+// the table holds.
 template <bool kPlane3x3>
 __global__ void __launch_bounds__(kIdxThreads, 4)
 subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* __restrict__ coors,
                    const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
                    int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk,
-                   int32_t* __restrict__ nbr, uint32_t* __restrict__ nbr_mask, int64_t nbr_tiles) {
+                   int32_t* __restrict__ nbr, uint32_t* __restrict__ nbr_mask, uint32_t* __restrict__ nbr_rows,
+                   int64_t nbr_tiles) {
   constexpr int kBatch = 4;  // probes in flight per thread
   constexpr int kTilesPerCta = kIdxThreads / 128;
   __shared__ int cnt[kMaxKernelVol];
@@ -200,8 +203,10 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
     if (nbr) {
       if (threadIdx.x < kTilesPerCta && tile0 + threadIdx.x < nbr_tiles) nbr_mask[tile0 + threadIdx.x] = 0u;
       const int64_t tile = tile0 + (threadIdx.x >> 7);
-      if (tile < nbr_tiles)
+      if (tile < nbr_tiles) {
         for (int k = 0; k < g.kvol; ++k) nbr[(tile * g.kvol + k) * 128 + (threadIdx.x & 127)] = -1;
+        for (int w = threadIdx.x & 127; w < g.kvol * 4; w += 128) nbr_rows[tile * g.kvol * 4 + w] = 0u;
+      }
     }
     return;
   }
@@ -211,8 +216,11 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
   const int my_tile = threadIdx.x >> 7;
   // this thread's column of the table: entry of offset k' at nbr_col[k' * 128]
   int32_t* nbr_col = nullptr;
-  if (nbr && tile0 + my_tile < nbr_tiles)
+  uint32_t* rows_word = nullptr;  // this warp's word of the row masks: entry of offset k' at rows_word[k' * 4]
+  if (nbr && tile0 + my_tile < nbr_tiles) {
     nbr_col = nbr + ((tile0 + my_tile) * g.kvol) * 128 + (threadIdx.x & 127);
+    rows_word = nbr_rows + ((tile0 + my_tile) * g.kvol) * 4 + ((threadIdx.x >> 5) & 3);
+  }
   const uint32_t mask = hash_capacity((long long)n * kSubmFan, cap_max) - 1;
   const int i = blockIdx.x * kIdxThreads + threadIdx.x;
   const bool live = i < n;
@@ -274,6 +282,7 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
         const unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
         if (lane_id() == 0 && hits) atomicAdd(&cnt[k + b], __popc(hits));
         if (nbr_col) nbr_col[(g.kvol - 1 - (k + b)) * 128] = v[b];
+        if (rows_word && lane_id() == 0) rows_word[(g.kvol - 1 - (k + b)) * 4] = hits;
         if (nbr && lane_id() == 0 && hits) atomicOr(&tile_bits[my_tile], 1u << (g.kvol - 1 - (k + b)));
       }
       k += 9;
@@ -304,6 +313,7 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
             const unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
             if (lane_id() == 0 && hits) atomicAdd(&cnt[k + b], __popc(hits));
             if (nbr_col) nbr_col[(g.kvol - 1 - (k + b)) * 128] = v[b];
+            if (rows_word && lane_id() == 0) rows_word[(g.kvol - 1 - (k + b)) * 4] = hits;
             if (nbr && lane_id() == 0 && hits) atomicOr(&tile_bits[my_tile], 1u << (g.kvol - 1 - (k + b)));
           }
         }
@@ -1017,21 +1027,25 @@ extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, con
   if (p->subm) {
     subm_insert_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max, status);
     if (g.ndim == 3 && !g.transpose && g.stride[0] == 1 && g.stride[1] == 1 && g.stride[2] == 1) {
-      // the fused neighbour table covers ceil(n_max / 128) tiles, masks right behind the ids (SPConvMM's layout)
+      // the fused neighbour table covers ceil(n_max / 128) tiles; offset masks, then row masks, right behind the ids
+      // (SPConvMM's layout)
       const int64_t nbr_tiles = (n_max + 127) / 128;
       uint32_t* nbr_mask = nbr ? reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(nbr) +
                                                              align_up((size_t)g.kvol * nbr_tiles * 128 * 4, 256))
+                               : nullptr;
+      uint32_t* nbr_rows = nbr ? reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(nbr_mask) +
+                                                             align_up((size_t)nbr_tiles * sizeof(uint32_t), 256))
                                : nullptr;
       // one CTA per 256 rows up to the end of the table, so that rows beyond the live count get their -1 / masks
       const int nblk_t = nbr ? (int)ceil_div(nbr_tiles * 128, kIdxThreads) : nblk;
       if (g.ksize[1] == 3 && g.klast == 3)
         subm_probe3_kernel<true><<<nblk_t, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
                                                                  plan.pair_out, plan.block_counts, nblk, nbr, nbr_mask,
-                                                                 nbr_tiles);
+                                                                 nbr_rows, nbr_tiles);
       else
         subm_probe3_kernel<false><<<nblk_t, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
                                                                   plan.cap_max, plan.pair_out, plan.block_counts, nblk,
-                                                                  nbr, nbr_mask, nbr_tiles);
+                                                                  nbr, nbr_mask, nbr_rows, nbr_tiles);
     } else {
       D3D_REQUIRE(!nbr, D3D_ERR_INVALID_ARGUMENT);
       subm_probe_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,

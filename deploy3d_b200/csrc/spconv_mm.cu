@@ -22,10 +22,10 @@ namespace {
 // ---------------------------------------------------------------------------------------------
 // Neighbour table
 // ---------------------------------------------------------------------------------------------
-// `flags` holds one byte per (tile, offset < 32), cleared here, set by the scatter kernel with plain stores (many
-// writers, one value) and packed into the per-tile bit masks afterwards: atomics on the masks themselves serialise
-// on the few words all offsets of a tile share.
-__global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* flags32, int64_t flag_words) {
+// Fills the ids with -1 and clears the row masks (four 32-bit words per (tile, offset): bit r of word q says that
+// row 32 q + r of the tile has an input under that offset).  The scatter kernel sets the bits; the per-tile offset
+// masks are derived from them afterwards.
+__global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* row_masks, int64_t mask_words) {
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (int64_t)gridDim.x * blockDim.x;
   const int4 fill = make_int4(-1, -1, -1, -1);
   int64_t i = tid;
@@ -36,29 +36,32 @@ __global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* flags32, i
     table[i + 3 * nthreads] = fill;
   }
   for (; i < n16; i += nthreads) table[i] = fill;
-  for (int64_t w = tid; w < flag_words; w += nthreads) flags32[w] = 0u;
+  for (int64_t w = tid; w < mask_words; w += nthreads) row_masks[w] = 0u;
 }
 
-// One warp per tile: lane k reads the flag of offset k.
-__global__ void pack_mask_kernel(const unsigned char* __restrict__ flags, int64_t tiles,
+// One warp per tile: lane k looks at the four row-mask words of offset k.
+__global__ void pack_mask_kernel(const uint4* __restrict__ row_masks, int64_t tiles, int kvol,
                                  uint32_t* __restrict__ tile_mask) {
   const int64_t tile = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   if (tile >= tiles) return;
-  const unsigned m = __ballot_sync(0xffffffffu, flags[tile * 32 + (threadIdx.x & 31)] != 0);
-  if ((threadIdx.x & 31) == 0) tile_mask[tile] = m;
+  const int k = threadIdx.x & 31;
+  uint4 w = make_uint4(0u, 0u, 0u, 0u);
+  if (k < kvol) w = __ldg(row_masks + tile * kvol + k);
+  const unsigned m = __ballot_sync(0xffffffffu, (w.x | w.y | w.z | w.w) != 0u);
+  if (k == 0) tile_mask[tile] = m;
 }
 
 // index rows: gatherIn | scatterOut | kernelOffset (trt/spconv/index_trt.cu:211-213); `inverse` swaps the
 // first two (trt/spconv/mm_trt.cu:174-177).
-// Besides the ids, every tile of 128 outputs gets a bit mask of the kernel offsets (< 32) that feed it, so that the
-// convolution kernel can skip the others without scanning the ids.
+// Besides the ids, every (tile of 128 outputs, offset) gets a 128-bit mask of the rows that have an input: the
+// convolution kernel copies only those rows and lets the tensor core update only those accumulator lanes.
 __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t row_len,
                                      const int32_t* __restrict__ num_index, int inverse, int mirror, int kvol,
-                                     int64_t m_max, int32_t* __restrict__ table, unsigned char* __restrict__ flags) {
+                                     int64_t m_max, int32_t* __restrict__ table, uint32_t* __restrict__ row_masks) {
   int64_t n = *num_index;
   n = n > row_len ? row_len : n;
   // grid-stride over the live part of the rulebook only (the rows are sized for the worst case, mostly unused);
-  // whole warps iterate together so that the shuffle below is always fully populated
+  // whole warps iterate together so that the warp-wide match below is always fully populated
   const int64_t n_warp = (n + 31) & ~(int64_t)31;
   constexpr int kUnroll = 4;  // entries in flight per thread
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -88,11 +91,12 @@ __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t 
       const bool valid = k[u] >= 0 && k[u] < kvol && g[u] >= 0 && s[u] >= 0 && s[u] < m_max;
       // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
       if (valid) table[((int64_t)(s[u] >> 7) * kvol + k[u]) * 128 + (s[u] & 127)] = g[u];
-      // one flag store per run of equal (tile, offset) in the warp: neighbouring entries mostly share both
-      const unsigned key = (valid && k[u] < 32) ? ((unsigned)(s[u] >> 7) << 5) | (unsigned)k[u] : 0xFFFFFFFFu;
-      const unsigned prev = __shfl_up_sync(0xffffffffu, key, 1);
-      if (key != 0xFFFFFFFFu && ((threadIdx.x & 31) == 0 || prev != key))
-        flags[(int64_t)(s[u] >> 7) * 32 + k[u]] = 1;
+      // one atomic per distinct mask word in the warp: neighbouring entries mostly share (tile, offset, row quarter)
+      const unsigned long long word =
+          valid ? ((unsigned long long)(s[u] >> 7) * kvol + k[u]) * 4ull + (unsigned)((s[u] & 127) >> 5) : ~0ull;
+      const unsigned peers = __match_any_sync(0xffffffffu, word);
+      const unsigned bits = __reduce_or_sync(peers, valid ? 1u << (s[u] & 31) : 0u);
+      if (valid && (threadIdx.x & 31) == __ffs(peers) - 1) atomicOr(row_masks + word, bits);
     }
   }
 }
@@ -372,10 +376,11 @@ extern "C" int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t h, int which) {
 
 extern "C" size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out) {
   // rows are padded to a multiple of 128 entries so every 128-output tile can be read as a whole
-  // followed by one 32-bit offset mask per tile (zero-filled together with the -1 ids: see prepare)
+  // followed by one 32-bit offset mask per tile and four 32-bit row masks per (tile, offset)
   int64_t pitch = (max_num_act_out + 127) / 128 * 128;
-  return table_ids_bytes(kernel_vol, max_num_act_out) + align_up((size_t)(pitch / 128) * sizeof(uint32_t), 256) +
-         align_up((size_t)(pitch / 128) * 32, 256);
+  (void)pitch;
+  return table_ids_bytes(kernel_vol, max_num_act_out) + table_mask_bytes(max_num_act_out) +
+         table_rows_bytes(kernel_vol, max_num_act_out);
 }
 
 extern "C" int d3d_spconv_mm_workspace(d3d_spconv_mm_t h, const d3d_tensor_desc* in, int n_in, size_t* bytes) {
@@ -400,13 +405,16 @@ extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int mode, int64_t max_num_a
   uint32_t* tile_mask = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(table) +
                                                     table_ids_bytes(kernel_vol, max_num_act_out));
   const int64_t tiles = pitch / 128;
-  unsigned char* flags = reinterpret_cast<unsigned char*>(tile_mask) + align_up((size_t)tiles * sizeof(uint32_t), 256);
-  table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16,
-                                                           reinterpret_cast<uint32_t*>(flags), tiles * 8);
+  uint32_t* row_masks = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(tile_mask) +
+                                                    table_mask_bytes(max_num_act_out));
+  table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16, row_masks,
+                                                           tiles * kernel_vol * 4);
   if (index_row_len > 0)
     table_scatter_kernel<<<stream_grid(index_row_len, 256), 256, 0, st>>>(
-        index, index_row_len, num_index, inverse, mirror, kernel_vol, pitch, reinterpret_cast<int32_t*>(table), flags);
-  pack_mask_kernel<<<(unsigned)ceil_div(tiles * 32, 256), 256, 0, st>>>(flags, tiles, tile_mask);
+        index, index_row_len, num_index, inverse, mirror, kernel_vol, pitch, reinterpret_cast<int32_t*>(table),
+        row_masks);
+  pack_mask_kernel<<<(unsigned)ceil_div(tiles * 32, 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(row_masks),
+                                                                        tiles, kernel_vol, tile_mask);
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }

@@ -28,7 +28,9 @@ struct MmLaunch {
   const void* in_feats;
   int64_t max_num_act_in;
   const int32_t* num_act_out;
-  const int32_t* table;  // [tiles][kVol][128] input row per (output tile, offset, row in tile), -1 = none; tiles = ceil(max_num_act_out / 128); then one offset mask per tile
+  // [tiles][kVol][128] input row per (output tile, offset, row in tile), -1 = none; tiles = ceil(max_num_act_out /
+  // 128); then one offset mask per tile; then the row masks [tiles][kVol][4] (bit r of word q: row 32 q + r has an input)
+  const int32_t* table;
   void* out_feats;
   int relu;
   const void* residual;
@@ -39,6 +41,16 @@ struct MmLaunch {
 inline size_t table_ids_bytes(int kernel_vol, int64_t max_num_act_out) {
   const size_t pitch = (size_t)((max_num_act_out + 127) / 128 * 128);
   return ((size_t)kernel_vol * pitch * sizeof(int32_t) + 255) / 256 * 256;
+}
+
+// Bytes of the per-tile offset masks; the row masks (four words per (tile, offset)) follow them.
+inline size_t table_mask_bytes(int64_t max_num_act_out) {
+  const size_t tiles = (size_t)((max_num_act_out + 127) / 128);
+  return (tiles * sizeof(uint32_t) + 255) / 256 * 256;
+}
+inline size_t table_rows_bytes(int kernel_vol, int64_t max_num_act_out) {
+  const size_t tiles = (size_t)((max_num_act_out + 127) / 128);
+  return (tiles * (size_t)kernel_vol * 4 * sizeof(uint32_t) + 255) / 256 * 256;
 }
 
 int launch_spconv_mm_simt(const MmLaunch& a);

@@ -83,6 +83,7 @@ __device__ long long g_prof[3][8];
 struct TcParams {
   const int32_t* table;        // [tiles][kvol][128]
   const uint32_t* tile_mask;   // [tiles] bit k set: offset k feeds the tile
+  const uint32_t* row_masks;   // [tiles][kvol][4] bit r of word q set: row 32 q + r has an input under the offset
   const void* in_feats;        // [n_in_rows][cin]
   int64_t m_max;
   int32_t n_in_rows;  // rows of the gathered tensor (an id outside [0, n_in_rows) = zero row)
@@ -177,17 +178,15 @@ __device__ __forceinline__ void tma_load_2d(const CUtensorMap* map, uint64_t* ba
       : "r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
-// 16-byte asynchronous copy; with `zero` != 0 it writes 16 zero bytes and ignores the source (the ignore-src
-// predicate form: one instruction either way).  No memory clobber: it touches only the operand ring, which the
-// issuing thread never accesses with ordinary loads or stores, and the compiler may then overlap the id loads of
-// the next stage with these copies.  Predicated on `run` != 0 instead of branched around.
-__device__ __forceinline__ void cp_async_16_if(uint32_t run, uint32_t dst, const void* src, uint32_t zero) {
+// 16-byte asynchronous copy, predicated on `run` != 0 instead of branched around.  No memory clobber: it touches
+// only the operand ring, which the issuing thread never accesses with ordinary loads or stores, and the compiler may
+// then overlap the id loads of the next stage with these copies.
+__device__ __forceinline__ void cp_async_16_if(uint32_t run, uint32_t dst, const void* src) {
   asm volatile(
-      "{\n\t.reg .pred q, z;\n\t"
-      "setp.ne.b32 q, %3, 0;\n\t"
-      "setp.ne.b32 z, %2, 0;\n\t"
-      "@q cp.async.cg.shared.global [%0], [%1], 16, z;\n\t}" ::"r"(dst),
-      "l"(src), "r"(zero), "r"(run));
+      "{\n\t.reg .pred q;\n\t"
+      "setp.ne.b32 q, %2, 0;\n\t"
+      "@q cp.async.cg.shared.global [%0], [%1], 16;\n\t}" ::"r"(dst),
+      "l"(src), "r"(run));
 }
 // The barrier receives one arrival (counted in its expected arrivals) once all cp.async issued so far by this
 // thread have landed.
@@ -226,18 +225,27 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
-// D (+)= A * B, issued only when `run` != 0 (predicated, not branched around).
-__device__ __forceinline__ void umma_f16_if(uint32_t run, uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
-                                            uint32_t idesc, uint32_t accumulate) {
+// D += A * B on the accumulator lanes whose bit in `off` (lanes 0-31 in .x, ... 96-127 in .w) is clear; the other
+// lanes keep their value whatever the corresponding rows of A hold.  Issued only when `run` != 0 (predicated, not
+// branched around).
+__device__ __forceinline__ void umma_f16_rows_if(uint32_t run, uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                                 uint32_t idesc, const uint4& off) {
   asm volatile(
       "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "setp.ne.b32 q, %5, 0;\n\t"
-      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      "setp.eq.b32 p, 0, 0;\n\t"
+      "setp.ne.b32 q, %4, 0;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
       :
-      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(run)
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(run), "r"(off.x), "r"(off.y), "r"(off.z), "r"(off.w)
       : "memory");
 }
+// Writes `v` into 16 consecutive columns of this thread's TMEM lane.
+__device__ __forceinline__ void tmem_st16_same(uint32_t taddr, uint32_t v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};"
+      ::"r"(taddr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
@@ -248,7 +256,7 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-struct __align__(8) Shared {
+struct __align__(16) Shared {
   uint64_t full[kMaxStages];   // producers (+ the B load) -> MMA
   uint64_t empty[kMaxStages];  // MMA (tcgen05.commit) -> producers, control
   uint64_t acc_full[kNumAcc];
@@ -256,10 +264,9 @@ struct __align__(8) Shared {
   uint64_t b_ready;  // resident weights have landed
   uint32_t tmem_base;
   int abort_flag;
-  // zero-row flags of the producers: bit e * passes + i of zero_flags[slot][t] says that producer thread t (of a
-  // team) last zero-filled that position of the slot, so it still holds zeros.  In shared memory because the teams
-  // take the stages in turn and may meet the same slot.
-  uint32_t zero_flags[kMaxStages][kTileRows];
+  // row masks of the MMA warp's current and next tile, inverted (bit set = accumulator lane left alone), four words
+  // per kernel offset; sized so that a whole window of kMaxGroup offsets starting below 32 stays inside
+  __align__(16) uint32_t lanes_off[2][(32 + kMaxGroup) * 4];
 };
 
 // Carved dynamic shared memory: [stages x (group A blocks | group B blocks)] aligned to 1024, the resident weights,
@@ -278,7 +285,7 @@ template <int kGroup> __device__ __forceinline__ Smem carve_smem(unsigned char* 
   s.stage_bytes = (uint32_t)kGroup * (p.a_bytes + (p.b_resident ? 0u : p.b_bytes));
   s.bres = s.tiles + (size_t)p.stages * s.stage_bytes;
   s.bias = reinterpret_cast<float*>(s.bres + (p.b_resident ? (size_t)p.kvol * p.b_bytes : 0));
-  s.sh = reinterpret_cast<Shared*>(s.bias + ((p.cout + 1) & ~1));
+  s.sh = reinterpret_cast<Shared*>(s.bias + ((p.cout + 3) & ~3));
   return s;
 }
 
@@ -392,7 +399,6 @@ __device__ __forceinline__ uint32_t cta_setup(const TcParams& p, const Smem& s) 
     sh->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  for (int i = threadIdx.x; i < kMaxStages * kTileRows; i += blockDim.x) (&sh->zero_flags[0][0])[i] = 0u;
   for (int c = threadIdx.x; c < p.cout; c += blockDim.x) s.bias[c] = p.bias[c];
   if ((int)(threadIdx.x >> 5) == kProdWarps) tmem_alloc(&sh->tmem_base, p.tmem_cols);
   tc_fence_before();
@@ -420,8 +426,10 @@ __device__ __forceinline__ void cta_teardown(const TcParams& p, uint32_t tmem_ba
 // A warp instruction covers 32 / kPieces whole rows (lane = row * kPieces + piece: whole rows on the global side,
 // whole swizzle spans on the shared side); because a pass advances by a multiple of 4 rows and the warp's first row by
 // a multiple of 32, the XOR swizzle term of the destination is a per-lane constant (128-byte rows: two constants,
-// by pass parity).  The neighbour ids of the lane's rows come straight from the table in global memory (the lanes
-// of a row load the same word); the loads of the team's next stage are issued before the copies of this one.
+// by pass parity).  Only rows that have an input are copied: the row mask of the (tile, offset, quarter) -- one word,
+// the same for the whole warp -- predicates the copies, and the MMA warp keeps the other accumulator lanes out of the
+// product, so whatever an unused row of the ring holds is never seen.  Ids and row masks come straight from global
+// memory; the loads of the team's next stage are issued before the copies of this one.
 template <int kPieces, int kChunks, int kGroup, int kProdWarps>
 __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, int warp, int lane) {
   constexpr int kTeams = kProdWarps / 4;
@@ -433,7 +441,6 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   constexpr uint32_t kBlockBytes = kChunkBytes * kChunks;      // = p.a_bytes
   constexpr int kSwzShift = kRowBytes == 128 ? 0 : kRowBytes == 64 ? 1 : 2;
   constexpr int kSwzMask = kRowBytes == 128 ? 7 : kRowBytes == 64 ? 3 : 1;
-  static_assert(kGroup * kPasses <= 32, "one zero-row flag per (block slot, pass)");
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
   const int team = warp / 4, quarter = warp % 4;
@@ -443,17 +450,24 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
       (uint32_t)row0 * kRowBytes + ((uint32_t)(j ^ ((row0 >> kSwzShift) & kSwzMask)) << 4);
   const unsigned char* src_j = reinterpret_cast<const unsigned char*>(p.in_feats) + j * 16;
   const uint32_t row_src_bytes = (uint32_t)p.cin * 2;
-  const uint32_t n_in_rows = (uint32_t)p.n_in_rows;
+  const uint32_t last_in_row = (uint32_t)p.n_in_rows - 1u;
   const uint32_t tiles_addr = smem_u32(s.tiles);
-  uint32_t* const my_flags = &sh->zero_flags[0][quarter * 32 + lane];
 
-  auto load_ids = [&](const StageIter& it, int (&ids)[kGroup][kPasses]) {
-    const int32_t* base = p.table + ((int64_t)it.tile * p.kvol + it.base) * kTileRows + row0;
+  struct Ids {
+    int id[kGroup][kPasses];
+    uint32_t rows[kGroup];  // row mask word of this warp's quarter, 0 for an offset the stage does not take
+  };
+  auto load_ids = [&](const StageIter& it, Ids& v) {
+    const int64_t blk = (int64_t)it.tile * p.kvol + it.base;
+    const int32_t* base = p.table + blk * kTileRows + row0;
+    const uint32_t* rows = p.row_masks + blk * 4 + quarter;
 #pragma unroll
-    for (int e = 0; e < kGroup; ++e)
+    for (int e = 0; e < kGroup; ++e) {
+      const bool take = (it.take >> e) & 1u;
+      v.rows[e] = take ? __ldg(rows + e * 4) : 0u;
 #pragma unroll
-      for (int i = 0; i < kPasses; ++i)
-        ids[e][i] = ((it.take >> e) & 1u) ? __ldg(base + e * kTileRows + i * kRowsPerPass) : -1;
+      for (int i = 0; i < kPasses; ++i) v.id[e][i] = take ? __ldg(base + e * kTileRows + i * kRowsPerPass) : -1;
+    }
   };
   // the neighbour ids of a tile are kvol * 512 contiguous bytes: one 128-byte line per lane of a team
   auto prefetch_ids = [&](int tile) {
@@ -477,8 +491,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   PROF_DECL
   // One stage: find the team's stage after `cur` and start the loads of its ids, then wait for the slot and copy
   // `cur`.  Returns false when `cur` was the team's last stage or a wait gave up.
-  auto step = [&](const StageIter& cur, const int (&ids)[kGroup][kPasses], StageIter& nxt,
-                  int (&ids_next)[kGroup][kPasses]) -> bool {
+  auto step = [&](const StageIter& cur, const Ids& ids, StageIter& nxt, Ids& ids_next) -> bool {
     PROF(0);
     nxt = cur;
     const bool have_next = next_own(nxt);
@@ -492,38 +505,28 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
     const unsigned char* src_part = src_j + (size_t)cur.part * p.kchunk * 2;
     const uint32_t dst = tiles_addr + (uint32_t)stage * s.stage_bytes + dst_lane;
     // A lone warp issues a dependent instruction every four cycles or so, and the copies (volatile asm) keep their
-    // order: so everything a copy needs is computed first, for all copies of the stage at once -- independent chains
-    // the scheduler can interleave -- and the copies themselves follow as short, independent instruction groups.
-    uint32_t valid_bits = 0, run_bits = 0;  // bit e * kPasses + i
+    // order: so the source addresses of all copies of the stage come first -- independent chains the scheduler can
+    // interleave -- and the copies themselves follow as short, independent instruction groups.  An id without an
+    // input (-1) or beyond the tensor is clamped to the last row: its address stays inside the tensor whether or
+    // not the copy is predicated off.
     const unsigned char* src[kGroup][kPasses];
-#pragma unroll
-    for (int e = 0; e < kGroup; ++e) {
-      if ((cur.take >> e) & 1u) run_bits |= (uint32_t)((1ull << kPasses) - 1ull) << (e * kPasses);
-#pragma unroll
-      for (int i = 0; i < kPasses; ++i) {
-        const bool valid = (uint32_t)ids[e][i] < n_in_rows;  // negative = no neighbour
-        valid_bits |= (valid ? 1u : 0u) << (e * kPasses + i);
-        src[e][i] = src_part + (uint64_t)(valid ? (uint32_t)ids[e][i] : 0u) * row_src_bytes;
-      }
-    }
-    // Most rows of a block have no neighbour (LiDAR: about 5 of 27 offsets per voxel).  A position that was
-    // zero-filled the last time the slot was written is still zero, so a zero row over a zero row is skipped: it
-    // would only spend shared-memory bandwidth the tensor core needs.
-    uint32_t* flags = my_flags + stage * kTileRows;
-    const uint32_t was_zero = *flags;
-    const uint32_t copy_bits = (valid_bits | ~was_zero) & run_bits;
-    *flags = (was_zero & ~run_bits) | (~valid_bits & run_bits);
 #pragma unroll
     for (int e = 0; e < kGroup; ++e)
 #pragma unroll
+      for (int i = 0; i < kPasses; ++i)
+        src[e][i] = src_part + (uint64_t)min((uint32_t)ids.id[e][i], last_in_row) * row_src_bytes;
+#pragma unroll
+    for (int e = 0; e < kGroup; ++e) {
+      const uint32_t mine = ids.rows[e] >> rsub;  // bit i * kRowsPerPass: this lane's row of pass i
+#pragma unroll
       for (int i = 0; i < kPasses; ++i) {
-        const uint32_t bit = 1u << (e * kPasses + i);
         const uint32_t d = (kRowBytes == 128 ? (dst ^ (uint32_t)((i & 1) << 6)) : dst) +
                            (uint32_t)(e * kBlockBytes + i * kRowsPerPass * kRowBytes);
 #pragma unroll
         for (int c = 0; c < kChunks; ++c)
-          cp_async_16_if(copy_bits & bit, d + c * kChunkBytes, src[e][i] + c * 128, ~valid_bits & bit);
+          cp_async_16_if(mine & (1u << (i * kRowsPerPass)), d + c * kChunkBytes, src[e][i] + c * 128);
       }
+    }
     cp_async_arrive(&sh->full[stage]);  // one arrival per producer thread once its copies have landed
     PROF(3);
 #pragma unroll
@@ -533,7 +536,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   };
   // two id buffers used in turn: the loaded ids are first touched a whole stage after their loads were issued
   StageIter it_a, it_b;
-  int ids_a[kGroup][kPasses], ids_b[kGroup][kPasses];
+  Ids ids_a, ids_b;
   first_tile<kGroup>(p, it_a);
   bool have = true;
   for (int t = 0; t <= team && have; ++t) have = next_stage<kGroup>(p, it_a);
@@ -588,10 +591,12 @@ __device__ __forceinline__ void control_role(const TcParams& p, const Smem& s, c
 // swizzled K-major layouts).  Advancing the operand by `d` bytes adds d / 16 to this word.
 __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16); }
 
-// The whole warp walks the stage sequence; everything an MMA depends on (offset mask, stage slot, accumulate flag)
-// is kept warp-uniform in a form the compiler can see -- the mask goes through a shuffle from lane 0 -- so that
-// descriptor arithmetic stays in the uniform datapath; one elected lane issues the straight line of predicated
-// MMAs of a stage and the commit.
+// The whole warp walks the stage sequence; everything an MMA depends on (offset mask, stage slot) is kept
+// warp-uniform in a form the compiler can see -- the mask goes through a shuffle from lane 0 -- so that descriptor
+// arithmetic stays in the uniform datapath; one elected lane issues the straight line of predicated MMAs of a stage
+// and the commit.  Every MMA accumulates (the epilogue hands the accumulators over zeroed) and updates only the
+// accumulator lanes of rows that have an input under its offset: the row masks of a tile are loaded a tile ahead
+// (one coalesced load per 32 words), parked inverted in shared memory, and the issuing lane reads four words per offset.
 template <int kPieces, int kChunks, int kGroup>
 __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint32_t tmem_base) {
   constexpr int kSteps = kPieces * kChunks / 2;  // tcgen05.mma instructions (K = 16 each) per block
@@ -601,6 +606,7 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
   constexpr uint32_t gmask = (1u << kGroup) - 1u;
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
+  const int lane = threadIdx.x & 31;
   // descriptor high word: stride between 8-row groups, version, swizzle mode
   const uint64_t desc_hi = (uint64_t)(((8u * kRowBytes) >> 4) | (1u << 14) | (p.layout_type << 29)) << 32;
   const uint32_t cs_b = (uint32_t)(p.cout * kRowBytes) >> 4;
@@ -609,23 +615,39 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
   const uint32_t idesc = p.idesc;
   const bool resident = p.b_resident != 0;
   if (resident && !__all_sync(0xffffffffu, mbar_wait(&sh->b_ready, 0, abort_flag, 23))) return;
-  int stage = 0, acc = 0;
+  int stage = 0, acc = 0, buf = 0;
   uint32_t phase = 0, acc_phase = 0;
   const int num_stages = p.stages, kvol = p.kvol, kparts = p.kparts;
+  const int row_words = kvol * 4;  // at most 128
   bool landed = false;  // the stage about to be waited for was already seen full by the probe below
   pdl_wait();
   PROF_DECL
+  uint32_t rows_ahead[4];
+  auto load_rows = [&](int tile) {
+    const uint32_t* w = p.row_masks + (int64_t)tile * row_words + lane;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      rows_ahead[i] = (tile < p.num_tiles && lane + 32 * i < row_words) ? __ldg(w + 32 * i) : 0u;
+  };
   uint32_t mask_ahead = load_mask(p, blockIdx.x);
+  load_rows(blockIdx.x);
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
     const uint32_t mask = __shfl_sync(0xffffffffu, mask_ahead, 0);
-    mask_ahead = load_mask(p, tile + gridDim.x);  // a round trip to L2: in flight while this tile is issued
+    uint32_t* lanes_off = sh->lanes_off[buf];
+    if (mask != 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) lanes_off[lane + 32 * i] = ~rows_ahead[i];
+    }
+    // round trips to L2: in flight while this tile is issued
+    mask_ahead = load_mask(p, tile + gridDim.x);
+    load_rows(tile + gridDim.x);
     if (mask == 0) continue;  // a tile no offset feeds uses no accumulator: the epilogue writes its bias rows alone
+    __syncwarp();
     PROF(0);
-    if (!__all_sync(0xffffffffu, mbar_wait(&sh->acc_empty[acc], acc_phase ^ 1, abort_flag, 22))) return;
+    if (!__all_sync(0xffffffffu, mbar_wait(&sh->acc_empty[acc], acc_phase, abort_flag, 22))) return;
     tc_fence_after();
     PROF(4);
     const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.cout);
-    uint32_t done = 0;  // nonzero once the accumulator holds a product
     for (int base = 0; base < kvol; base += kGroup) {
       const uint32_t take = (mask >> base) & gmask;
       if (take == 0) continue;
@@ -645,14 +667,11 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
         const bool landed_next = mbar_test(&sh->full[stage_next], phase_next);
         const uint32_t a_lo = tiles_lo + (uint32_t)stage * stage_step;
         const uint32_t b_lo = resident ? bres_lo + (uint32_t)base * b_step : a_lo + (uint32_t)kGroup * a_step;
-        const uint32_t before = done | (uint32_t)part;
-        // descriptors and flags of all MMAs of the stage first (independent, warp-uniform arithmetic), then the
-        // straight line of MMAs: the issuing lane runs no dependent chain between two of them
+        // descriptors of all MMAs of the stage first (independent, warp-uniform arithmetic), then the straight
+        // line of MMAs: the issuing lane runs no dependent chain between two of them
         uint64_t desc_a[kGroup][kSteps], desc_b[kGroup][kSteps];
-        uint32_t earlier[kGroup];
 #pragma unroll
         for (int e = 0; e < kGroup; ++e) {
-          earlier[e] = before | (take & ((1u << e) - 1u));
 #pragma unroll
           for (int ks = 0; ks < kSteps; ++ks) {
             // 32 bytes per K step inside the swizzle span, the next 64-column block every 4 steps
@@ -663,34 +682,46 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
           }
         }
         if (elect_one()) {
+          const uint4* off = reinterpret_cast<const uint4*>(lanes_off) + base;
 #pragma unroll
-          for (int e = 0; e < kGroup; ++e)
+          for (int e = 0; e < kGroup; ++e) {
+            const uint4 o = off[e];  // beyond kvol: inside the buffer, never used (the offset is not taken)
 #pragma unroll
             for (int ks = 0; ks < kSteps; ++ks)
-              umma_f16_if((take >> e) & 1u, d_addr, desc_a[e][ks], desc_b[e][ks], idesc, ks > 0 ? 1u : earlier[e]);
+              umma_f16_rows_if((take >> e) & 1u, d_addr, desc_a[e][ks], desc_b[e][ks], idesc, o);
+          }
           umma_commit(&sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
         }
         __syncwarp();
         PROF(3);
         stage = stage_next, phase = phase_next, landed = landed_next;
       }
-      done |= take;
     }
     if (elect_one()) umma_commit(&sh->acc_full[acc]);
     __syncwarp();
+    buf ^= 1;
     if (++acc == kNumAcc) acc = 0, acc_phase ^= 1;
   }
   PROF_STORE(1, (threadIdx.x & 31) == 0)
 }
 
 // ---- epilogue ----------------------------------------------------------------------------------------------------
-// Epilogue warp `quad` (= warp index mod 4: it may touch TMEM lanes [32*quad, 32*quad + 32)).
+// Epilogue warp `quad` (= warp index mod 4: it may touch TMEM lanes [32*quad, 32*quad + 32)).  The accumulators are
+// handed to the MMA warp zeroed: once at the start, then every time one has been read.
 __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, uint32_t tmem_base, int quad) {
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
   const int lane = threadIdx.x & 31;
   int acc = 0;
   uint32_t acc_phase = 0;
+  const uint32_t lane_base = tmem_base + ((uint32_t)(quad * 32) << 16);
+  for (int a = 0; a < kNumAcc; ++a) {
+    for (int c0 = 0; c0 < p.cout; c0 += 16) tmem_st16_same(lane_base + (uint32_t)(a * p.cout + c0), 0u);
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&sh->acc_empty[a]);
+  }
   pdl_wait();  // residual rows come from an earlier layer; output rows may still be read by the preceding kernel
   uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
   PROF_DECL
@@ -709,7 +740,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
     unsigned short* out_row = reinterpret_cast<unsigned short*>(p.out) + row * p.cout;
     const unsigned short* res_row =
         (p.residual && row_ok) ? reinterpret_cast<const unsigned short*>(p.residual) + row * p.cout : nullptr;
-    const uint32_t taddr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.cout);
+    const uint32_t taddr = lane_base + (uint32_t)(acc * p.cout);
     for (int c0 = 0; c0 < p.cout; c0 += 16) {
       uint32_t v[16];
       if (empty_tile) {
@@ -718,6 +749,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
       } else {
         tmem_ld16(taddr + c0, v);
         tmem_ld_wait();
+        tmem_st16_same(taddr + c0, 0u);  // the next tile of this accumulator starts from zero
       }
       if (row_ok) {
         if (p.is_bf16) store_chunk<true>(v, s.bias, c0, out_row, res_row, p.relu);
@@ -725,6 +757,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
       }
     }
     if (!empty_tile) {
+      tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&sh->acc_empty[acc]);
@@ -874,6 +907,8 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.table = a.table;
   p.tile_mask = reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(a.table) +
                                                   table_ids_bytes(kvol, m_max));
+  p.row_masks = reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(p.tile_mask) +
+                                                  table_mask_bytes(m_max));
   p.in_feats = a.in_feats;
   p.m_max = m_max;
   p.n_in_rows = (int32_t)a.max_num_act_in;

@@ -50,3 +50,33 @@ def pairs_equal(a, b, kvol):
     for k in range(kvol):
         assert a[k].shape == b[k].shape, "offset %d: %s vs %s pairs" % (k, a[k].shape, b[k].shape)
         assert (a[k] == b[k]).all(), "offset %d: pair lists differ" % k
+
+
+def table_parts(table, kvol, max_num_act_out):
+    """The three parts of SPConvMM's neighbour table (a uint8 tensor): ids int32 [tiles, kvol, 128], offset masks
+    int32 [tiles], row masks int32 [tiles, kvol, 4]; every part starts on a multiple of 256 bytes."""
+    import torch
+    tiles = (max_num_act_out + 127) // 128
+    up = lambda v: (v + 255) // 256 * 256
+    ids_bytes, mask_bytes = kvol * tiles * 128 * 4, tiles * 4
+    mask_off = up(ids_bytes)
+    rows_off = mask_off + up(mask_bytes)
+    ids = table[:ids_bytes].view(torch.int32).view(tiles, kvol, 128)
+    mask = table[mask_off:mask_off + mask_bytes].view(torch.int32)
+    rows = table[rows_off:rows_off + tiles * kvol * 16].view(torch.int32).view(tiles, kvol, 4)
+    return ids, mask, rows
+
+
+def assert_table_consistent(ids, mask, rows):
+    """Row masks and offset masks say exactly what the ids say: bit r of word q <=> ids[.., 32 q + r] >= 0."""
+    import torch
+    tiles, kvol, _ = ids.shape
+    have = (ids >= 0).view(tiles, kvol, 4, 32).long()
+    weights = (1 << torch.arange(32, device=ids.device, dtype=torch.int64))
+    want_rows = (have * weights).sum(-1)
+    got_rows = rows.long() & 0xFFFFFFFF
+    assert torch.equal(got_rows, want_rows), "row masks disagree with the ids"
+    if kvol <= 32:
+        any_k = (want_rows != 0).any(-1).long()
+        want_mask = (any_k * (1 << torch.arange(kvol, device=ids.device, dtype=torch.int64))).sum(-1)
+        assert torch.equal(mask.long() & 0xFFFFFFFF, want_mask), "offset masks disagree with the ids"

@@ -8,7 +8,8 @@ import numpy as np
 import pytest
 import torch
 
-from tests._util import assert_feats_close, pairs_equal, rng, round_to, unique_coors
+from tests._util import (assert_feats_close, assert_table_consistent, pairs_equal, rng, round_to, table_parts,
+                         unique_coors)
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -276,7 +277,7 @@ def test_extended_enqueue_same_index_and_table(d3d, ks, dil):
     """d3d_spconv_index_enqueue_ex on buffers the caller keeps across calls: the index tensor is byte-identical to
     the plain entry point's on every call although only the stale padding is refilled (three voxel sets of
     different sizes in turn, shrinking and growing), and the neighbour table the probe kernel writes equals the one
-    d3d_spconv_mm_prepare builds from the rulebook (ids and per-tile offset masks)."""
+    d3d_spconv_mm_prepare builds from the rulebook (ids, per-tile offset masks, row masks)."""
     from deploy3d_b200.ops import data_s_spconv_index
     from deploy3d_b200.plugins import SPConvMMPlugin, deserialize_plugin
     shape_b, cap = [2, 20, 26, 22], 5000
@@ -290,9 +291,6 @@ def test_extended_enqueue_same_index_and_table(d3d, ks, dil):
     num_index = torch.zeros(1, dtype=torch.int32, device=DEV)
     nbytes = SPConvMMPlugin.table_bytes(kvol, cap)
     table = torch.full((nbytes,), 77, dtype=torch.uint8, device=DEV)
-    tiles = (cap + 127) // 128
-    ids_bytes = kvol * tiles * 128 * 4
-    mask_off = (ids_bytes + 255) // 256 * 256
     for call, n in enumerate((4000, 900, 2500, 4999, 1)):
         coors = torch.zeros((cap, 4), dtype=torch.int32, device=DEV)
         coors[:n] = _t(unique_coors(rng(500 + n), n, shape_b))
@@ -303,9 +301,10 @@ def test_extended_enqueue_same_index_and_table(d3d, ks, dil):
         assert int(num_index.item()) == int(want[1].item())
         assert torch.equal(index, want[0]), "call %d: index differs from the plain entry point's" % call
         ref_table = SPConvMMPlugin.prepare(kvol, False, cap, want[0], want[1])
-        assert torch.equal(table[:ids_bytes].view(torch.int32), ref_table[:ids_bytes].view(torch.int32))
-        assert torch.equal(table[mask_off:mask_off + 4 * tiles].view(torch.int32),
-                           ref_table[mask_off:mask_off + 4 * tiles].view(torch.int32))
+        got_parts, want_parts = table_parts(table, kvol, cap), table_parts(ref_table, kvol, cap)
+        for part, a, b in zip(("ids", "offset masks", "row masks"), got_parts, want_parts):
+            assert torch.equal(a, b), "call %d: %s differ from the prepared table's" % (call, part)
+        assert_table_consistent(*got_parts)
 
 
 def test_extended_enqueue_strided_persistent(d3d):

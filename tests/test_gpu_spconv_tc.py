@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 import torch
 
-from tests._util import assert_feats_close, rng, round_to, unique_coors
+from tests._util import assert_feats_close, assert_table_consistent, rng, round_to, table_parts, unique_coors
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -122,7 +122,7 @@ def test_ragged_and_empty_tiles(d3d, orc):
 @pytest.mark.parametrize("ks,dil", [((3, 3, 3), (1, 1, 1)), ((3, 1, 3), (1, 1, 2)), ((5, 3, 3), (1, 1, 1))])
 def test_mirror_table_build_gives_the_same_table(d3d, ks, dil):
     """A SubM rulebook with 'same' padding is mirror-symmetric; building the neighbour table in gather order from
-    the mirrored entries must give exactly the table (ids and per-tile offset masks) of the generic scatter."""
+    the mirrored entries must give exactly the table (ids, per-tile offset masks, row masks) of the generic scatter."""
     pad = tuple(d * (k // 2) for k, d in zip(ks, dil))
     shape = [2, 12, 30, 28]
     coors = unique_coors(rng(21), 3000, shape)
@@ -131,14 +131,12 @@ def test_mirror_table_build_gives_the_same_table(d3d, ks, dil):
     kvol = int(np.prod(ks))
     plain = SPConvMMPlugin.prepare(kvol, False, 3000, outs[0], outs[1])
     mirrored = SPConvMMPlugin.prepare(kvol, False, 3000, outs[0], outs[1], mirror=True)
-    tiles, ids_bytes = 3072 // 128, kvol * 3072 * 4  # 3000 outputs -> 24 tiles; the masks follow the ids, 256-aligned
-    ids_bytes_aligned = (ids_bytes + 255) // 256 * 256
-    ids_a, ids_b = plain[:ids_bytes].view(torch.int32), mirrored[:ids_bytes].view(torch.int32)
+    (ids_a, mask_a, rows_a), (ids_b, mask_b, rows_b) = table_parts(plain, kvol, 3000), table_parts(mirrored, kvol, 3000)
     assert (ids_a == ids_b).all()
     assert (ids_a >= 0).sum() == (outs[0][2, :int(outs[1].item())] >= 0).sum()
-    mask_a = plain[ids_bytes_aligned:ids_bytes_aligned + 4 * tiles].view(torch.int32)
-    mask_b = mirrored[ids_bytes_aligned:ids_bytes_aligned + 4 * tiles].view(torch.int32)
     assert (mask_a == mask_b).all() and (mask_a != 0).any()
+    assert (rows_a == rows_b).all()
+    assert_table_consistent(ids_a, mask_a, rows_a)
 
 
 def test_dependent_launch_is_bit_identical(d3d):
