@@ -377,8 +377,6 @@ extern "C" int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t h, int which) {
 extern "C" size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out) {
   // rows are padded to a multiple of 128 entries so every 128-output tile can be read as a whole
   // followed by one 32-bit offset mask per tile and four 32-bit row masks per (tile, offset)
-  int64_t pitch = (max_num_act_out + 127) / 128 * 128;
-  (void)pitch;
   return table_ids_bytes(kernel_vol, max_num_act_out) + table_mask_bytes(max_num_act_out) +
          table_rows_bytes(kernel_vol, max_num_act_out);
 }

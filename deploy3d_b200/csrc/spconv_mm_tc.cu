@@ -963,13 +963,18 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
         if (!k) continue;
         if (g_plan_group && group != g_plan_group) continue;
         if (group > 1 && (group * ksteps > 8 || group > kvol)) continue;
+        // with K parts, offsets that share a stage would accumulate part by part instead of offset by offset: keep
+        // the one accumulation order every plan produces
+        if (group > 1 && kparts > 1) continue;
         int stages = (int)(ring / ((size_t)group * blk));
         if (stages > kMaxStages) stages = kMaxStages;
         if (g_plan_stages && stages > g_plan_stages) stages = g_plan_stages;
         if (stages < 2) continue;
-        // three stages hide the gather latency, more add little; then as many MMAs per hand-over as possible
+        // eight MMAs per hand-over first (B200, 64 -> 64 at 238 k voxels: two offsets per stage in two stages 84 us,
+        // one offset per stage in four stages 94 us), then up to three stages (more add little), then more MMAs
         const int depth = stages >= 3 ? 3 : stages;
-        const int score = depth * 1000 + group * ksteps * 10 + (stages > 4 ? 4 : stages) + resident * 5;
+        const int mmas = group * ksteps;
+        const int score = (mmas > 8 ? 8 : mmas) * 400 + depth * 1000 + mmas * 10 + (stages > 4 ? 4 : stages) + resident * 5;
         if (score > best_score) {
           best_score = score;
           best.kchunk = kchunk, best.resident = resident, best.group = group, best.stages = stages, best.kernel = k;
