@@ -8,7 +8,10 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libs", "libdeploy3d_b200.so")
+# DEPLOY3D_B200_CHECKED=1 selects the checked build (python -m deploy3d_b200.build --checked): same entry points,
+# every id range-checked before use, first violation recorded (d3d_debug_take_bounds_violation)
+LIB_PATH = os.path.join(_HERE, "libs", "libdeploy3d_b200_checked.so" if os.environ.get("DEPLOY3D_B200_CHECKED") == "1"
+                        else "libdeploy3d_b200.so")
 
 D3D_MAX_DIMS = 8
 D3D_MAX_NDIM = 4
@@ -97,6 +100,7 @@ SIGNATURES = {
     "d3d_version": (ctypes.c_char_p, []),
     "d3d_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "d3d_debug_take_kernel_error": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "d3d_debug_take_bounds_violation": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int32)]),
     "d3d_debug_set_tc_plan": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "d3d_spconv_index_parse": (ctypes.c_int, [ctypes.c_int, _vp, _sz, ctypes.POINTER(SpconvIndexParams)]),
     "d3d_spconv_index_num_outputs": (ctypes.c_int, [ctypes.POINTER(SpconvIndexParams)]),
@@ -180,6 +184,15 @@ def lib():
             fn.argtypes = args
         _LIB = handle
     return _LIB
+
+
+def use_tuning_build(name):
+    """Load ``libs/libdeploy3d_b200_<name>.so`` (``python -m deploy3d_b200.build --tuning <name> ...``) instead of the
+    regular library; must be called before anything else touches the library.  For microbench.py only."""
+    global LIB_PATH
+    if _LIB is not None:
+        raise RuntimeError("the library is already loaded")
+    LIB_PATH = os.path.join(_HERE, "libs", "libdeploy3d_b200_%s.so" % name)
 
 
 def check(fn_name, status):

@@ -23,6 +23,9 @@ __global__ void map_scatter_kernel(int32_t* __restrict__ map, const int32_t* __r
   int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   int4 c = __ldg(reinterpret_cast<const int4*>(coors) + i);
+  if (!(D3D_BOUNDS_OK(c.x, 0, b, kSiteBevCoord) && D3D_BOUNDS_OK(c.y, 0, z, kSiteBevCoord) &&
+        D3D_BOUNDS_OK(c.z, 0, y, kSiteBevCoord) && D3D_BOUNDS_OK(c.w, 0, x, kSiteBevCoord)))
+    return;
   if (c.x < 0 || c.x >= b || c.y < 0 || c.y >= z || c.z < 0 || c.z >= y || c.w < 0 || c.w >= x) return;
   map[(((int64_t)c.x * z + c.y) * y + c.z) * x + c.w] = i;
 }

@@ -207,6 +207,31 @@ __device__ __forceinline__ uint32_t hash_capacity(long long keys, uint32_t cap_m
   return cap;
 }
 
+// Checked build (-DDEPLOY3D_BOUNDS_CHECK, python -m deploy3d_b200.build --checked): every row id, table entry or
+// coordinate a kernel is about to index with is range-checked first; the first violation is recorded (site, value,
+// limit), every one counted, and the access skipped.  One record for the whole library, so the checked build is
+// compiled as relocatable device code.  In the regular build the macro is the constant `true`: the kernels keep only
+// the range checks they need for safety and drop out-of-range entries silently, as the reference does.
+enum BoundsSite {
+  kSiteMmTcId = 1,      // SPConvMM tensor-core kernel: neighbour id outside [-1, rows of the input tensor)
+  kSiteMmSimtId = 2,    // SPConvMM SIMT kernel: the same
+  kSiteTableEntry = 3,  // neighbour table build: rulebook entry with a negative gather or an out-of-range scatter index
+  kSiteBevCoord = 4,    // BEVDensify: voxel coordinate outside the dense grid
+  kSiteScatterTo = 5,   // ScatterTo: voxel id >= number of voxels
+  kSiteGatherBack = 6,  // GatherBack: voxel id >= number of voxels
+};
+#ifdef DEPLOY3D_BOUNDS_CHECK
+extern __device__ int g_d3d_bounds[4];  // violations seen; site, value and limit of the first
+__device__ __forceinline__ bool bounds_ok(long long v, long long lo, long long hi, int site) {
+  if (v >= lo && v < hi) return true;
+  if (atomicAdd(&g_d3d_bounds[0], 1) == 0) g_d3d_bounds[1] = site, g_d3d_bounds[2] = (int)v, g_d3d_bounds[3] = (int)hi;
+  return false;
+}
+#define D3D_BOUNDS_OK(v, lo, hi, site) ::d3d::bounds_ok((long long)(v), (long long)(lo), (long long)(hi), site)
+#else
+#define D3D_BOUNDS_OK(v, lo, hi, site) true
+#endif
+
 // Soft failures a kernel reports in the caller's optional status word (atomicOr; the word is the caller's to
 // clear): they drop work instead of faulting, exactly where the reference is silent
 // (trt/include/common/hash32.h:70, trt/spconv/index.cu:163-168).

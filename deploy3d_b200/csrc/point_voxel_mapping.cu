@@ -35,7 +35,7 @@ __global__ void scatter_reduce_kernel(const float* __restrict__ in_feats, const 
   int64_t p = t / groups;
   int g = (int)(t % groups);
   int v = __ldg(scatter_to + p);
-  if (v < 0 || v >= m) return;
+  if (v < 0 || !D3D_BOUNDS_OK(v, 0, m, kSiteScatterTo) || v >= m) return;
   if (kVec) {
     float4 x = __ldg(reinterpret_cast<const float4*>(in_feats + p * c) + g);
     float* o = out + (int64_t)v * c + 4 * g;
@@ -63,7 +63,7 @@ __global__ void gather_rows_kernel(const V* __restrict__ in, const int32_t* __re
   if (t >= n * groups) return;
   int64_t p = t / groups, g = t % groups;
   int v = __ldg(scatter_to + p);
-  if (v < 0 || v >= m) {
+  if (v < 0 || !D3D_BOUNDS_OK(v, 0, m, kSiteGatherBack) || v >= m) {
     if (fill) out[t] = fill_val;
     return;
   }

@@ -88,7 +88,10 @@ __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t 
     for (int u = 0; u < kUnroll; ++u) {
       if (p0 + u * stride >= n_warp) break;  // warp-uniform
       // k outside [0, kvol) marks a padding entry
-      const bool valid = k[u] >= 0 && k[u] < kvol && g[u] >= 0 && s[u] >= 0 && s[u] < m_max;
+      const bool live = k[u] >= 0 && k[u] < kvol;
+      const bool valid = live && g[u] >= 0 && s[u] >= 0 && s[u] < m_max;
+      if (live) (void)(D3D_BOUNDS_OK(g[u], 0, 0x7fffffffll, kSiteTableEntry) &&
+                       D3D_BOUNDS_OK(s[u], 0, m_max, kSiteTableEntry));  // checked build: recorded
       // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
       if (valid) table[((int64_t)(s[u] >> 7) * kvol + k[u]) * 128 + (s[u] & 127)] = g[u];
       // one atomic per distinct mask word in the warp: neighbouring entries mostly share (tile, offset, row quarter)
@@ -135,7 +138,7 @@ spconv_mm_simt_kernel(const T* __restrict__ in_feats, int64_t n_in_max, const T*
   for (int k = warp; k < kvol; k += kSimtThreads / 32) {
     int64_t o = tile0 + lane;
     int v = o < m_max ? __ldg(table + ((o >> 7) * kvol + k) * 128 + (o & 127)) : -1;
-    if (v >= n_in_max) v = -1;
+    if (!D3D_BOUNDS_OK(v, -1, n_in_max, kSiteMmSimtId) || v >= n_in_max) v = -1;
     idx_s[k * kTileM + lane] = v;
     unsigned any = __ballot_sync(0xffffffffu, v >= 0);
     if (lane == 0) kvalid_s[k] = any != 0;
@@ -360,6 +363,28 @@ extern "C" int d3d_spconv_mm_destroy(d3d_spconv_mm_t h) {
   release_device(h);
   delete h;
   return D3D_OK;
+}
+
+#ifdef DEPLOY3D_BOUNDS_CHECK
+namespace d3d {
+__device__ int g_d3d_bounds[4];
+}
+#endif
+// Debug aid without a reference counterpart.  In a checked build (-DDEPLOY3D_BOUNDS_CHECK): synchronises the device,
+// copies {violations seen, site / value / limit of the first} to `record` and clears them.  The regular build checks
+// nothing and says so with D3D_ERR_INVALID_ARGUMENT.
+extern "C" int d3d_debug_take_bounds_violation(int32_t* record) {
+#ifdef DEPLOY3D_BOUNDS_CHECK
+  if (!record) return D3D_ERR_INVALID_ARGUMENT;
+  const int32_t zero[4] = {0, 0, 0, 0};
+  if (cudaDeviceSynchronize() != cudaSuccess) return D3D_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(record, d3d::g_d3d_bounds, sizeof(zero)) != cudaSuccess) return D3D_ERR_CUDA;
+  if (cudaMemcpyToSymbol(d3d::g_d3d_bounds, zero, sizeof(zero)) != cudaSuccess) return D3D_ERR_CUDA;
+  return D3D_OK;
+#else
+  (void)record;
+  return D3D_ERR_INVALID_ARGUMENT;
+#endif
 }
 
 extern "C" int d3d_spconv_mm_set_dependent_launch(d3d_spconv_mm_t h, int enable) {

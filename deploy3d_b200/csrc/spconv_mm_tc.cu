@@ -68,7 +68,20 @@ constexpr unsigned long long kWaitLimitNs = 1000ull * 1000ull * 1000ull;
 
 __device__ int g_tc_error;  // 0 ok; otherwise the code of the first wait that gave up
 
-// Cycle accounting per role (CTA 0 only), compiled in with -DD3D_TC_PROFILE for tuning builds.
+// Tuning builds (python -m deploy3d_b200.build --tuning NAME -D...):
+//   D3D_TC_PROFILE  cycle accounting per role (CTA 0 only), read back with d3d_debug_copy_prof
+//   D3D_TC_NO_MMA   every tcgen05.mma predicated off     } timing experiments: what is left when a part of the
+//   D3D_TC_NO_COPY  every gather copy predicated off     } work is removed (the results are meaningless)
+#ifdef D3D_TC_NO_MMA
+#define D3D_TC_MMA_RUN(run) ((run) & 0u)
+#else
+#define D3D_TC_MMA_RUN(run) (run)
+#endif
+#ifdef D3D_TC_NO_COPY
+#define D3D_TC_COPY_RUN(run) ((run) & 0u)
+#else
+#define D3D_TC_COPY_RUN(run) (run)
+#endif
 #ifdef D3D_TC_PROFILE
 __device__ long long g_prof[3][8];
 #define PROF_DECL long long prof_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long tprev_ = clock64();
@@ -186,7 +199,7 @@ __device__ __forceinline__ void cp_async_16_if(uint32_t run, uint32_t dst, const
       "{\n\t.reg .pred q;\n\t"
       "setp.ne.b32 q, %2, 0;\n\t"
       "@q cp.async.cg.shared.global [%0], [%1], 16;\n\t}" ::"r"(dst),
-      "l"(src), "r"(run));
+      "l"(src), "r"(D3D_TC_COPY_RUN(run)));
 }
 // The barrier receives one arrival (counted in its expected arrivals) once all cp.async issued so far by this
 // thread have landed.
@@ -236,7 +249,7 @@ __device__ __forceinline__ void umma_f16_rows_if(uint32_t run, uint32_t tmem_d, 
       "setp.ne.b32 q, %4, 0;\n\t"
       "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
       :
-      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(run), "r"(off.x), "r"(off.y), "r"(off.z), "r"(off.w)
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(D3D_TC_MMA_RUN(run)), "r"(off.x), "r"(off.y), "r"(off.z), "r"(off.w)
       : "memory");
 }
 // Writes `v` into 16 consecutive columns of this thread's TMEM lane.
@@ -514,7 +527,10 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
     for (int e = 0; e < kGroup; ++e)
 #pragma unroll
       for (int i = 0; i < kPasses; ++i)
+      {
+        (void)D3D_BOUNDS_OK(ids.id[e][i], -1, (long long)last_in_row + 1, kSiteMmTcId);  // checked build: recorded
         src[e][i] = src_part + (uint64_t)min((uint32_t)ids.id[e][i], last_in_row) * row_src_bytes;
+      }
 #pragma unroll
     for (int e = 0; e < kGroup; ++e) {
       const uint32_t mine = ids.rows[e] >> rsub;  // bit i * kRowsPerPass: this lane's row of pass i

@@ -70,6 +70,13 @@ const char* d3d_status_string(int status);
  * synchronises the device, returns in *code the error word a kernel of this library raised when one of its bounded
  * waits expired (0 = none) and clears it. */
 int d3d_debug_take_kernel_error(int* code);
+/* Debug aid (no reference counterpart).  A checked build of the library (-DDEPLOY3D_BOUNDS_CHECK) range-checks every
+ * row id, table entry and coordinate its kernels index with, skips an access that is out of range and records it:
+ * this call synchronises the device, copies {violations seen, site, value, limit of the first} to record[0..3] and
+ * clears them.  Sites: 1 / 2 neighbour id in SPConvMM (tensor-core / SIMT kernel), 3 rulebook entry while the
+ * neighbour table is built, 4 BEVDensify coordinate, 5 ScatterTo id, 6 GatherBack id.  The regular build checks
+ * nothing of the kind and returns D3D_ERR_INVALID_ARGUMENT. */
+int d3d_debug_take_bounds_violation(int32_t* record);
 /* Tuning aid (no reference counterpart): overrides the pipeline plan of the tensor-core SPConvMM kernel for every
  * later launch of the process: kernel offsets per pipeline stage, maximum number of stages, producer warps (4 or 8);
  * 0 = automatic.  Not thread-safe; results do not depend on the plan. */

@@ -32,7 +32,15 @@ def main():
     ap.add_argument("--index-reps", type=int, default=0, help="also time the rulebook + table build this many times")
     ap.add_argument("--plan", type=int, nargs=3, default=None, metavar=("GROUP", "STAGES", "PRODUCER_WARPS"),
                     help="override the tensor-core kernel's pipeline plan (0 = automatic)")
+    ap.add_argument("--lib", default=None, metavar="NAME",
+                    help="load the tuning build libs/libdeploy3d_b200_NAME.so (python -m deploy3d_b200.build --tuning NAME ...)")
+    ap.add_argument("--role-cycles", action="store_true",
+                    help="after the timed launches, one more launch whose per-role cycle counts (CTA 0) are printed; "
+                         "needs a tuning build with -DD3D_TC_PROFILE")
     args = ap.parse_args()
+    if args.lib:
+        from deploy3d_b200 import _lib
+        _lib.use_tuning_build(args.lib)
     if args.plan:
         from deploy3d_b200 import _lib
         _lib.check("d3d_debug_set_tc_plan", _lib.lib().d3d_debug_set_tc_plan(*args.plan))
@@ -75,6 +83,21 @@ def main():
            "us_per_launch": sec * 1e6, "tflops_dense": 2.0 * m * 27 * args.cin * args.cout / sec / 1e12,
            "tflops_pair": 2.0 * pairs * args.cin * args.cout / sec / 1e12,
            "neighbours_per_output": pairs / max(m, 1)}
+    if args.role_cycles:
+        import ctypes
+        from deploy3d_b200 import _lib
+        mm.run(x, num_out, table, out=out, relu=True)
+        buf = (ctypes.c_longlong * 24)()
+        copy_prof = _lib.lib().d3d_debug_copy_prof  # AttributeError without -DD3D_TC_PROFILE
+        copy_prof.restype, copy_prof.argtypes = ctypes.c_int, [ctypes.POINTER(ctypes.c_longlong)]
+        _lib.check("d3d_debug_copy_prof", copy_prof(buf))
+        c = np.array(list(buf)).reshape(3, 8)
+        res["role_cycles"] = {
+            "producer_warp0": {"other": int(c[0, 0]), "walk_and_id_loads": int(c[0, 1]), "wait_empty": int(c[0, 2]),
+                               "address_and_copy_issue": int(c[0, 3])},
+            "mma_warp": {"other": int(c[1, 0]), "wait_full": int(c[1, 1]), "proxy_fence": int(c[1, 2]),
+                         "issue_and_commit": int(c[1, 3]), "wait_accumulator": int(c[1, 4])},
+            "epilogue_warp0": {"other": int(c[2, 0]), "wait_accumulator_full": int(c[2, 1]), "work": int(c[2, 2])}}
     if args.index_reps:
         torch.cuda.synchronize()
         e0.record()
