@@ -1,48 +1,50 @@
 // SPConvMM on the 5th-generation tensor cores: output-stationary implicit GEMM.
 //
 // For a tile of 128 consecutive output voxels and every kernel offset k that feeds at least one of them:
-//   A = the 128 input rows named by the neighbour table (zero rows where the neighbour is missing), staged in shared
-//       memory in the K-major swizzled layout the tensor core reads,
-//   B = W[k]^T, K-major, loaded by a tiled TMA copy (once per kernel for small layers, else once per stage),
-//   D += A * B with tcgen05.mma (M = 128, N = Cout, K = 16 per instruction), fp32 accumulator in tensor memory.
+//   A = the input rows named by the neighbour table, staged in shared memory in the K-major swizzled layout the
+//       tensor core reads -- only the rows that exist: the table carries a 128-bit row mask per (tile, offset),
+//   B = W[k]^T, K-major, loaded by a tiled TMA copy (once per kernel when all offsets fit, else once per stage),
+//   D += A * B with tcgen05.mma (M = 128, N = Cout, K = 16 per instruction), fp32 accumulator in tensor memory,
+//       issued with the inverted row mask as disable_output_lane: accumulator lanes of rows without an input are
+//       not updated, so whatever an unused row of the operand ring holds is never seen (no zero fill).
 // All offsets of a tile accumulate into the same TMEM columns; the epilogue reads them once with tcgen05.ld, adds
-// bias (+ residual), applies ReLU, converts and stores the row.  No atomics, no bias-initialisation pass.
+// bias (+ residual), applies ReLU, converts and stores the row, and writes zeros back (tcgen05.st) for the next tile.
+// No atomics, no bias-initialisation pass.
 // (The reference: gather iterator + mma.sync tiles of 64 pairs of one offset, fp16 accumulate, half2 atomicAdd
 // scatter, trt/spconv/mm/kernel.h:84-179, mm/output_iterator.h:189-206.)
 //
-// The A rows are gathered with 16-byte cp.async (zero-fill for missing neighbours) written straight into the
-// swizzled layout.  A TMA tile::gather4 producer was measured on B200 at about 11 ns per gathered row whatever the
-// row width (a request-rate limit), 2-3x slower than cp.async for these row sizes, and is not used.
+// The A rows are gathered with 16-byte cp.async written straight into the swizzled layout.  A TMA tile::gather4
+// producer was measured on B200 at 11.4 ns per gathered row whatever the row width (a request-rate limit), three
+// times slower than cp.async for these row sizes (profiles/gather_rows_cp_async_vs_tma_gather4.md), and is not used.
 //
 // What bounds this kernel, measured on B200 (profiles/spconv_mm_tc_role_cycles.md):
-//   * the instruction streams of its roles.  The kernel ran no faster with every MMA predicated off, nor with every
-//     copy and id load removed.  One warp that waits for a stage, fences and issues eight M128 K16 MMAs needs about
+//   * the instruction streams of its roles.  With every MMA and every gather copy predicated off the layers still
+//     take 56-88 % of their time.  One warp that waits for a stage, fences and issues eight M128 K16 MMAs needs about
 //     750 cycles for what the tensor core executes in 320 to 512; two such warps on one SM keep it busy.  A lone
 //     warp issues a dependent instruction every four cycles or so, so what a role executes per stage besides its
 //     copies / MMAs (walking the stage sequence, waits, address arithmetic) costs as much as the work itself.
-//   * for layers of 64 channels and more, the shared-memory data pipe (128 B per clock and SM): every A block is
-//     written once by cp.async and read once by the tensor core, every B block likewise unless it is resident, so
-//     a 64 -> 64 offset block moves 24 KB in and about 19 KB out in the 192 cycles its four MMAs need.
+//   * for layers of 64 channels and more, weight traffic from L2 (W[k] is fetched again for every tile: as many
+//     bytes as the gathered rows) and the shared-memory data pipe (128 B per clock and SM): every A row is written
+//     once by cp.async and the whole block read once by the tensor core, every B block likewise.
 // Hence:
 //   * layers run TWO CTAs per SM wherever shared and tensor memory allow (two independent issue streams);
 //   * the MMA warp keeps every value that feeds an MMA warp-uniform in a way the compiler can see (offset masks
 //     pass through a shuffle from lane 0), computes all descriptors of a stage first and lets the lane chosen by
 //     elect.sync issue the MMAs as straight-line code; it probes the following stage's barrier before it issues;
-//   * the neighbour ids are read from global memory by the producer lanes themselves, a stage ahead (and the
-//     table lines of the next tile are prefetched into L2), not staged in shared memory: that memory is a third
-//     pipeline stage instead;
+//     the row masks of a tile are loaded a tile ahead and parked, inverted, in shared memory;
+//   * the neighbour ids and row-mask words are read from global memory by the producer lanes themselves, a stage
+//     ahead (and the table lines of the next tile are prefetched into L2), not staged in shared memory;
 //   * the producer warps work in teams of four that take the stages in turn, so that the per-stage overhead of a
 //     warp is paid once per two stages of the pipeline; address arithmetic of all copies of a stage comes first,
-//     the copies follow as independent instruction groups; a zero fill uses the ignore-src form of cp.async;
+//     the copies follow as independent instruction groups, predicated by the row-mask bit of their row;
 //   * every role loads the offset mask of its next tile while it works on the current one;
-//   * the epilogue handles 16 columns per tensor-memory load, which keeps the kernel at 61-72 registers (two
-//     CTAs of 448 threads per SM).
+//   * the epilogue handles 16 columns per tensor-memory load (two CTAs of 320 or 448 threads per SM fit).
 // Roles of a CTA, for W = 4 or 8 producer warps:
 //   W producer warps   teams of four; warp q of a team copies rows [32q, 32q + 32) of every A block of the team's
 //                      stages: lane = (row, 16-byte piece), so its shared-memory offsets are constants
 //   1 MMA warp         waits for a stage, one elected lane issues its tcgen05.mma and commits; owns the TMEM allocation
 //   1 control warp     one lane loads B by TMA (all offsets once when they fit, else per stage)
-//   4 epilogue warps   TMEM -> registers -> global
+//   4 epilogue warps   TMEM -> registers -> global, then zeros -> TMEM
 // Every role derives the stage sequence of a tile from the tile's offset mask (built with the neighbour table), so
 // no per-stage metadata is exchanged.  Stages and accumulators are handed over through mbarriers; every wait is
 // bounded (about one second) and on expiry raises an error word, lets the CTA drain and return instead of spinning.
@@ -970,8 +972,11 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
     best.stages = 0, best.group = 0, best.kernel = nullptr;
     int best_score = -1;
     for (int resident = 1; resident >= 0; --resident) {
-      // resident weights: only while they leave the ring at least three quarters of the memory
-      if (resident && (kparts != 1 || bres_bytes * 4 > budget)) continue;
+      // resident weights whenever two stages still fit beside them, streamed per stage only otherwise: a streamed
+      // W[k] crosses from L2 once per tile and sits in the hand-over loop (B200, 463 k voxels: 32 -> 32 85.6 vs
+      // 88.2 us, 16 -> 32 36.9 vs 39.9 us)
+      if (resident && (kparts != 1 || bres_bytes + 2 * a_bytes > budget)) continue;
+      if (!resident && best_score >= 0) continue;
       const size_t ring = budget - (resident ? bres_bytes : 0);
       const size_t blk = a_bytes + (resident ? 0 : b_bytes);
       for (int group = kMaxGroup; group >= 1; --group) {

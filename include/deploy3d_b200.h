@@ -68,7 +68,10 @@ const char* d3d_version(void);
 const char* d3d_status_string(int status);
 /* Debug aid (no reference counterpart; the reference only prints CUDA errors, trt/include/common/macros.h:14-34):
  * synchronises the device, returns in *code the error word a kernel of this library raised when one of its bounded
- * waits expired (0 = none) and clears it. */
+ * waits expired (0 = none) and clears it.  The word is one per process: a wait of the tensor-core SPConvMM kernel
+ * gives up after about one second of wall clock (far beyond any hand-over of a running kernel; a context that is
+ * time-sliced away for longer would trip it too), the CTA then drains, part of the output stays unwritten, and the
+ * asynchronous enqueue that launched it has long returned D3D_OK.  Not thread-safe. */
 int d3d_debug_take_kernel_error(int* code);
 /* Debug aid (no reference counterpart).  A checked build of the library (-DDEPLOY3D_BOUNDS_CHECK) range-checks every
  * row id, table entry and coordinate its kernels index with, skips an access that is out of range and records it:
@@ -210,7 +213,9 @@ int d3d_spconv_mm_enqueue(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int
  * asserts that the rulebook is a mirror-symmetric SubM rulebook (odd kernel, padding = dilation * (k - 1) / 2 on
  * every axis, so that offset k and kVol-1-k hold each other's pairs with the roles swapped -- the property the
  * reference's test checks, tests/spconv/test_spconv.py:101-108); the table is then written in gather order, which
- * is faster.  The result is the same table.  The plugin-level d3d_spconv_mm_enqueue never sets bit 1. */
+ * is faster.  The result is the same table.  Precondition the library does not verify: the input coordinates are
+ * unique and inside the grid (with duplicates the rulebook is not symmetric and the mirrored build writes a wrong
+ * table).  The plugin-level d3d_spconv_mm_enqueue never sets bit 1. */
 size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out);
 int d3d_spconv_mm_prepare(int kernel_vol, int mode, int64_t max_num_act_out, const int32_t* index,
                           int64_t index_row_len, const int32_t* num_index, void* table, void* stream);
