@@ -623,7 +623,7 @@ def run_config5(args):
                     "h2d_bytes_per_step": host_pts[0].numel() * 4 * share,
                     "d2h_bytes_per_step": host_labels[0].numel() * 4 * share,
                     "ms_per_step": e2e_elapsed / args.steps * 1e3},
-            "gpu_launches": None,
+            "gpu_launches": count_launches(pipes[0], "segmentation") * args.steps * share,
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                          "frac": achieved / peaks["bf16_tflops"], "traffic": None,
                          "algorithmic_bytes": sum(l["bytes"] for l in layers) / len(layers),
@@ -693,17 +693,28 @@ def aggregate_frames_per_second(world, steps, frames_per_step, elapsed_max):
     return world * steps * frames_per_step / elapsed_max
 
 
-def count_launches(pipe):
-    """Kernels of this library launched per frame (every enqueue is a fixed launch list; counted from the plan)."""
-    n = 7  # SimpleMeanEncoder: reset, voxelize, owners, scan, number, accumulate, divide
-    built = set()
-    for L in pipe.net.layers:
-        if L.key not in built:
-            built.add(L.key)
-            n += (6 if L.kind == "subm" else 9) + 3  # rulebook passes + neighbour-table fill / scatter / mask pack
-        n += 1  # SPConvMM
-    n += 3  # BEVDensify: map fill, map scatter, densify
-    n += 2  # NMS3d: overlap mask, suppression
+def count_launches(pipe, kind="detection"):
+    """Kernels of this library launched per frame, counted from the pipeline's plan (every enqueue is a fixed launch
+    list; `profiles/bench_config4_launch_list.md` shows the same 105 launches per config-4 frame)."""
+    net = pipe.net
+    n = 0
+    for rb in net.rulebooks.values():
+        # SubM: reset, insert, probe, segment scan, compact, padding fill; strided: reset, insert, count winners,
+        # scan, assign, translate, segment scan, compact, padding fill
+        n += 6 if rb.kind == "subm" else 9
+        if not getattr(rb, "fused_table", False):
+            n += 3  # neighbour table: fill, scatter, offset masks
+        if getattr(rb, "table_inv", None) is not None:
+            n += 3  # the inverse layers' table of the same rulebook
+    n += sum(1 for L in net.layers if L.kind != "ew")  # SPConvMM
+    if kind == "detection":
+        n += 7  # SimpleMeanEncoder: reset, voxelize, owners, scan, number, accumulate, divide
+        n += 3  # BEVDensify: map fill, map scatter, densify
+        n += 2  # NMS3d: overlap mask, suppression
+    else:
+        n += 6  # CylinderEncoder: reset, cylinderize, owners, scan, number, scatter ids
+        n += 2  # ScatterTo: fill, scatter-reduce
+        n += 1  # GatherBack
     return n
 
 
