@@ -243,10 +243,13 @@ def conv_launch_times(pipe, frames, reps):
             # bracket kernel time and not the host's launch path
             xin = x
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            x = plug.run(xin, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res)
+            hint = bool(getattr(rb, "regroup", False))
+            x = plug.run(xin, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res,
+                         regrouped=hint)
             e0.record()
             for _ in range(INNER_LAUNCHES):
-                x = plug.run(xin, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res)
+                x = plug.run(xin, net.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res,
+                             regrouped=hint)
             e1.record()
             e1.synchronize()
             acc[li] += e0.elapsed_time(e1) * 1e-3 / INNER_LAUNCHES
@@ -289,7 +292,7 @@ def run_ours(args):
 
     frames = [synth.config4_points(i) for i in range(N_ROTATE)]
     boxes = synth.config4_boxes()
-    probe = DetectionPipeline("centerpoint", dev, kernel=args.kernel)
+    probe = DetectionPipeline("centerpoint", dev, kernel=args.kernel, regroup=args.regroup)
     probe.load_frame(frames[0], boxes)
     caps = probe.calibrate(frames)
     del probe
@@ -300,7 +303,7 @@ def run_ours(args):
     n_pipes = max(1, args.in_flight)
     pipes = []
     for _ in range(n_pipes):
-        q = DetectionPipeline("centerpoint", dev, caps=caps, kernel=args.kernel)
+        q = DetectionPipeline("centerpoint", dev, caps=caps, kernel=args.kernel, regroup=args.regroup)
         q.load_frame(frames[0], boxes)
         q.capture()
         pipes.append(q)
@@ -470,6 +473,7 @@ def run_ours(args):
                        "l2": "no flush: a frame rewrites %.0f MB of rulebooks/tables/activations (> 126 MB L2) and "
                              "inputs rotate over %d frames" % (working_set / 1e6, N_ROTATE),
                        "kernel": {0: "auto", 1: "simt", 2: "tcgen05"}[args.kernel],
+                       "regrouped_tables": bool(args.regroup),
                        "rank_seconds": {"min": min(elapsed_all), "median": float(np.median(elapsed_all)),
                                         "max": max(elapsed_all)},
                        "outputs": "NMS scores and voxel counts return to the host; the BEV map stays on the device, "
@@ -538,14 +542,14 @@ def run_config5(args):
     probe = SegmentationPipeline(dev)
     caps = {k: (probe.n_pts if k == "in" else 3 * probe.n_pts) for k in probe.set_names}
     del probe
-    probe = SegmentationPipeline(dev, caps=caps)
+    probe = SegmentationPipeline(dev, caps=caps, regroup=args.regroup)
     caps = probe.calibrate(all_frames)  # every rank sizes its buffers for the whole batch: identical engines
     del probe
     torch.cuda.empty_cache()
     n_pipes = max(1, args.in_flight)
     pipes = []
     for _ in range(n_pipes):
-        q = SegmentationPipeline(dev, caps=caps)
+        q = SegmentationPipeline(dev, caps=caps, regroup=args.regroup)
         q.load_frame(frames[0])
         q.capture()
         pipes.append(q)
@@ -615,7 +619,7 @@ def run_config5(args):
                        "parallelism": "batch of %d frames sharded %d per GPU (no collective)" % (BATCH5, share),
                        "frames_in_flight_per_gpu": n_pipes,
                        "voxels": {k: int(v) for k, v in pipe.net.counts().items()},
-                       "conv_layers": len(layers),
+                       "conv_layers": len(layers), "regrouped_tables": bool(args.regroup),
                        "rank_seconds": {"min": min(elapsed_all), "median": float(np.median(elapsed_all)),
                                         "max": max(elapsed_all)}},
             "clocks": clocks,
@@ -731,6 +735,9 @@ def main():
     ap.add_argument("--in-flight", type=int, default=2,
                     help="pipelines (buffers + CUDA graph + stream each) that take the frames in turn")
     ap.add_argument("--layers", action="store_true", help="print the per-layer SPConvMM table to stderr")
+    ap.add_argument("--regroup", action="store_true",
+                    help="rebuild every neighbour table with its outputs grouped by offset mask (d3d_spconv_mm_regroup): "
+                         "fewer (tile, offset) blocks for the convolutions, three more kernels per rulebook")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-plugin-order", action="store_true", help="skip the single-stream plugin-order figure")
     ap.add_argument("--no-reference-gpu", action="store_true",

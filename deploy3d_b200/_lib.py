@@ -53,7 +53,7 @@ class SpconvMMParams(ctypes.Structure):
 
 
 class SpconvMMEpilogue(ctypes.Structure):
-    _fields_ = [("relu", ctypes.c_int32), ("residual", ctypes.c_void_p)]
+    _fields_ = [("relu", ctypes.c_int32), ("residual", ctypes.c_void_p), ("regrouped", ctypes.c_int32)]
 
 
 class BevDensifyParams(ctypes.Structure):
@@ -100,6 +100,8 @@ SIGNATURES = {
     "d3d_version": (ctypes.c_char_p, []),
     "d3d_status_string": (ctypes.c_char_p, [ctypes.c_int]),
     "d3d_debug_take_kernel_error": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int)]),
+    "d3d_spconv_mm_regroup_scratch_bytes": (ctypes.c_size_t, [ctypes.c_int, ctypes.c_int64]),
+    "d3d_spconv_mm_regroup": (ctypes.c_int, [ctypes.c_int, ctypes.c_int64, _vp, _vp, _vp, ctypes.c_size_t, _vp]),
     "d3d_debug_take_bounds_violation": (ctypes.c_int, [ctypes.POINTER(ctypes.c_int32)]),
     "d3d_debug_set_tc_plan": (ctypes.c_int, [ctypes.c_int, ctypes.c_int, ctypes.c_int]),
     "d3d_spconv_index_parse": (ctypes.c_int, [ctypes.c_int, _vp, _sz, ctypes.POINTER(SpconvIndexParams)]),

@@ -199,8 +199,11 @@ class SparseNet:
     """
 
     def __init__(self, layers, spatial, caps, dtype=torch.float16, device="cuda:0", seed=0, kernel=0,
-                 pad_input=True, overlap_rulebooks=False, plugin_order=False):
+                 pad_input=True, overlap_rulebooks=False, plugin_order=False, regroup=False):
         self.layers, self.device, self.dtype = layers, torch.device(device), dtype
+        # regroup: every neighbour table is rebuilt with its outputs grouped by offset mask (same results, fewer
+        # (tile, offset) blocks for the convolutions to walk); never in plugin order, where a table serves one layer
+        self.regroup = regroup and not plugin_order
         # plugin order: what a TensorRT engine built from the reference's ONNX graph executes -- one stream, every
         # SPConvMM node through the plugin-level enqueue (which rebuilds its neighbour table in its own workspace,
         # trt/spconv/mm_trt.cu:149-205 has no state shared between nodes), ReLU / residual add as separate
@@ -268,6 +271,13 @@ class SparseNet:
                         max(SPConvMMPlugin.table_bytes(rb.kvol, out["cap"]), 16), dtype=torch.uint8,
                         device=self.device)
                     rb.table_inv = None
+                    rb.raw_fwd = rb.raw_inv = rb.scratch_fwd = rb.scratch_inv = None
+                    rb.regroup = self.regroup and rb.kvol <= 32
+                    if rb.regroup:  # the builders write the plain table, the layers read the regrouped one
+                        rb.raw_fwd = torch.empty_like(rb.table_fwd)
+                        rb.scratch_fwd = torch.empty(
+                            max(SPConvMMPlugin.regroup_scratch_bytes(rb.kvol, out["cap"]), 16), dtype=torch.uint8,
+                            device=self.device)
                     # the net owns index, workspace and tables for its whole life: stale-padding-only refills, and
                     # the table of a mirror-symmetric SubM rulebook straight from the probe kernel
                     rb.calls = 0
@@ -280,6 +290,11 @@ class SparseNet:
                         rb.table_inv = torch.empty(
                             max(SPConvMMPlugin.table_bytes(rb.kvol, self.sets[out_set]["cap"]), 16),
                             dtype=torch.uint8, device=self.device)
+                        if rb.regroup:
+                            rb.raw_inv = torch.empty_like(rb.table_inv)
+                            rb.scratch_inv = torch.empty(
+                                max(SPConvMMPlugin.regroup_scratch_bytes(rb.kvol, self.sets[out_set]["cap"]), 16),
+                                dtype=torch.uint8, device=self.device)
                 else:
                     out_set, in_set = rb.out_set, rb.in_set
                 assert in_set == cur, "layer %d expects voxel set %s but the data is on %s" % (li, in_set, cur)
@@ -323,19 +338,25 @@ class SparseNet:
             return
         first = rb.calls == 0
         rb.calls += 1
+        plain_fwd = rb.raw_fwd if rb.regroup else rb.table_fwd
         if rb.kind == "subm":
             rb.plugin.enqueue_ex(src["coors"], src["num"], rb.shape_tensor, outputs=[rb.index, rb.num_index],
                                  persistent=True, first_call=first,
-                                 subm_table=rb.table_fwd if rb.fused_table else None)
+                                 subm_table=plain_fwd if rb.fused_table else None)
         else:
             rb.plugin.enqueue_ex(src["coors"], src["num"], rb.shape_tensor,
                                  outputs=[rb.index, rb.num_index, dst["coors"], dst["num"], rb.out_shape_tensor],
                                  persistent=True, first_call=first)
         if not rb.fused_table:
-            SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=rb.table_fwd,
+            SPConvMMPlugin.prepare(rb.kvol, False, dst["cap"], rb.index, rb.num_index, table=plain_fwd,
                                    mirror=rb.mirror)
+        if rb.regroup:
+            SPConvMMPlugin.regroup(rb.kvol, dst["cap"], plain_fwd, rb.table_fwd, rb.scratch_fwd)
         if rb.table_inv is not None:
-            SPConvMMPlugin.prepare(rb.kvol, True, src["cap"], rb.index, rb.num_index, table=rb.table_inv)
+            SPConvMMPlugin.prepare(rb.kvol, True, src["cap"], rb.index, rb.num_index,
+                                   table=rb.raw_inv if rb.regroup else rb.table_inv)
+            if rb.regroup:
+                SPConvMMPlugin.regroup(rb.kvol, src["cap"], rb.raw_inv, rb.table_inv, rb.scratch_inv)
 
     def forward(self, feats):
         """feats [cap_in, Cin] in the net dtype; coordinates / count as given to set_input.  Returns
@@ -401,7 +422,8 @@ class SparseNet:
                 x = out_buf
             else:
                 table = rb.table_inv if L.kind == "inverse" else rb.table_fwd
-                x = plug.run(x, self.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res)
+                x = plug.run(x, self.sets[out_set]["num"], table, out=out_buf, relu=L.relu_mode, residual=res,
+                             regrouped=rb.regroup)
             if L.save:
                 saved[L.save] = x
         if self.overlap_rulebooks:

@@ -191,20 +191,24 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
                    const int32_t* num_act_in, int64_t n_max, Geometry g, uint32_t cap_max,
                    int32_t* __restrict__ pair_out, int32_t* __restrict__ block_counts, int nblk,
                    int32_t* __restrict__ nbr, uint32_t* __restrict__ nbr_mask, uint32_t* __restrict__ nbr_rows,
-                   int64_t nbr_tiles) {
+                   int32_t* __restrict__ nbr_perm, int64_t nbr_tiles) {
   constexpr int kBatch = 4;  // probes in flight per thread
   constexpr int kTilesPerCta = kIdxThreads / 128;
   __shared__ int cnt[kMaxKernelVol];
   __shared__ unsigned tile_bits[kTilesPerCta];
   const int n = live_count(num_act_in, n_max);
   const int64_t tile0 = (int64_t)blockIdx.x * kTilesPerCta;
+  if (nbr && tile0 + (threadIdx.x >> 7) < nbr_tiles) {  // tile row p of the table stands for output p
+    const int64_t pos = (int64_t)blockIdx.x * kIdxThreads + threadIdx.x;
+    nbr_perm[pos] = pos < n_max ? (int32_t)pos : -1;
+  }
   if ((int64_t)blockIdx.x * kIdxThreads >= n) {
     // no live voxel here: the tiles of this CTA take part in no offset and hold no neighbour
     if (nbr) {
       if (threadIdx.x < kTilesPerCta && tile0 + threadIdx.x < nbr_tiles) nbr_mask[tile0 + threadIdx.x] = 0u;
       const int64_t tile = tile0 + (threadIdx.x >> 7);
       if (tile < nbr_tiles) {
-        for (int k = 0; k < g.kvol; ++k) nbr[(tile * g.kvol + k) * 128 + (threadIdx.x & 127)] = -1;
+        // (the ids of rows without an input are never read: only the row masks need a value)
         for (int w = threadIdx.x & 127; w < g.kvol * 4; w += 128) nbr_rows[tile * g.kvol * 4 + w] = 0u;
       }
     }
@@ -1036,16 +1040,19 @@ extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, con
       uint32_t* nbr_rows = nbr ? reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(nbr_mask) +
                                                              align_up((size_t)nbr_tiles * sizeof(uint32_t), 256))
                                : nullptr;
+      int32_t* nbr_perm = nbr ? reinterpret_cast<int32_t*>(reinterpret_cast<unsigned char*>(nbr_rows) +
+                                                           align_up((size_t)nbr_tiles * g.kvol * 16, 256))
+                              : nullptr;
       // one CTA per 256 rows up to the end of the table, so that rows beyond the live count get their -1 / masks
       const int nblk_t = nbr ? (int)ceil_div(nbr_tiles * 128, kIdxThreads) : nblk;
       if (g.ksize[1] == 3 && g.klast == 3)
         subm_probe3_kernel<true><<<nblk_t, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max,
                                                                  plan.pair_out, plan.block_counts, nblk, nbr, nbr_mask,
-                                                                 nbr_rows, nbr_tiles);
+                                                                 nbr_rows, nbr_perm, nbr_tiles);
       else
         subm_probe3_kernel<false><<<nblk_t, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,
                                                                   plan.cap_max, plan.pair_out, plan.block_counts, nblk,
-                                                                  nbr, nbr_mask, nbr_rows, nbr_tiles);
+                                                                  nbr, nbr_mask, nbr_rows, nbr_perm, nbr_tiles);
     } else {
       D3D_REQUIRE(!nbr, D3D_ERR_INVALID_ARGUMENT);
       subm_probe_kernel<<<dim3(nblk, g.rows), kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g,

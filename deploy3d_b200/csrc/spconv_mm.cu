@@ -11,6 +11,7 @@
 // channel counts the tensor-core kernel cannot take; spconv_mm_tc.cu holds the tcgen05/TMEM kernel.
 #include <string.h>
 
+#include <cub/device/device_radix_sort.cuh>
 #include <new>
 
 #include "common.cuh"
@@ -22,20 +23,15 @@ namespace {
 // ---------------------------------------------------------------------------------------------
 // Neighbour table
 // ---------------------------------------------------------------------------------------------
-// Fills the ids with -1 and clears the row masks (four 32-bit words per (tile, offset): bit r of word q says that
-// row 32 q + r of the tile has an input under that offset).  The scatter kernel sets the bits; the per-tile offset
-// masks are derived from them afterwards.
-__global__ void table_fill_kernel(int4* table, int64_t n16, uint32_t* row_masks, int64_t mask_words) {
+// Clears the row masks (four 32-bit words per (tile, offset): bit r of word q says that row 32 q + r of the tile has
+// an input under that offset) and writes the identity output map (tile row p holds output p; a table whose outputs
+// were regrouped holds a permutation instead).  The ids themselves need no initialisation: an id is only ever read
+// where its row-mask bit is set.  The scatter kernel sets ids and bits; the per-tile offset masks are derived from
+// the row masks afterwards.
+__global__ void table_fill_kernel(uint32_t* row_masks, int64_t mask_words, int32_t* perm, int64_t perm_words,
+                                  int64_t m_max) {
   const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nthreads = (int64_t)gridDim.x * blockDim.x;
-  const int4 fill = make_int4(-1, -1, -1, -1);
-  int64_t i = tid;
-  for (; i + 3 * nthreads < n16; i += 4 * nthreads) {  // four independent 16-byte stores in flight
-    table[i] = fill;
-    table[i + nthreads] = fill;
-    table[i + 2 * nthreads] = fill;
-    table[i + 3 * nthreads] = fill;
-  }
-  for (; i < n16; i += nthreads) table[i] = fill;
+  for (int64_t w = tid; w < perm_words; w += nthreads) perm[w] = w < m_max ? (int32_t)w : -1;
   for (int64_t w = tid; w < mask_words; w += nthreads) row_masks[w] = 0u;
 }
 
@@ -105,6 +101,84 @@ __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t 
 }
 
 // ---------------------------------------------------------------------------------------------
+// Regrouping: tiles of outputs with like offset masks
+// ---------------------------------------------------------------------------------------------
+// A (tile, offset) block costs the convolution kernel a stage slot, a weight block and its MMAs whether one row or
+// all 128 have an input, and with the outputs in voxel order nearly every offset feeds some row of every tile.  Sorted
+// by their own offset mask (which of the kVol offsets have an input), outputs with like masks share a tile and the
+// tile's mask shrinks to little more than theirs: LiDAR frames go from 27 to 4-19 blocks per tile.  The regrouped
+// table lists for every tile row the output it stands for (`perm`); the convolution writes each row where it belongs,
+// so nothing outside the table changes, and each output still accumulates its offsets in ascending order: the
+// results are bit-identical to those of the plain table.
+
+// One thread per output: its offset mask (bit k: offset k has an input) as sort key, its index as value.
+__global__ void regroup_keys_kernel(const uint32_t* __restrict__ row_masks, int kvol, int64_t m_max,
+                                    uint32_t* __restrict__ keys, int32_t* __restrict__ vals) {
+  const int64_t o = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= m_max) return;
+  const uint32_t* w = row_masks + (o >> 7) * kvol * 4 + ((o & 127) >> 5);
+  const int r = (int)(o & 31);
+  uint32_t key = 0;
+  for (int k = 0; k < kvol; ++k) key |= ((__ldg(w + k * 4) >> r) & 1u) << k;
+  keys[o] = key;
+  vals[o] = (int32_t)o;
+}
+
+// One CTA of 128 threads per tile of the regrouped table: thread r fetches the ids of its output from the plain table
+// (only where the output has an input), and the ballots of the four warps are the row masks.
+__global__ void __launch_bounds__(128)
+regroup_gather_kernel(const int32_t* __restrict__ ids_in, const uint32_t* __restrict__ keys, const int32_t* __restrict__ vals,
+                      int kvol, int64_t m_max, int32_t* __restrict__ ids_out, uint32_t* __restrict__ row_masks,
+                      uint32_t* __restrict__ tile_mask, int32_t* __restrict__ perm) {
+  __shared__ unsigned tile_bits;
+  const int64_t tile = blockIdx.x, p = tile * 128 + threadIdx.x;
+  if (threadIdx.x == 0) tile_bits = 0u;
+  __syncthreads();
+  const bool live = p < m_max;
+  const int32_t o = live ? __ldg(vals + p) : -1;
+  const uint32_t key = live ? __ldg(keys + p) : 0u;
+  perm[p] = o;
+  const int32_t* src = ids_in + ((int64_t)(o >> 7) * kvol) * 128 + (o & 127);
+  int32_t* dst = ids_out + (tile * kvol) * 128 + threadIdx.x;
+  uint32_t* rows = row_masks + (tile * kvol) * 4 + (threadIdx.x >> 5);
+  unsigned mine = 0u;
+#pragma unroll 3
+  for (int k = 0; k < kvol; ++k) {
+    const bool has = (key >> k) & 1u;
+    if (has) dst[k * 128] = __ldg(src + k * 128);
+    const unsigned ballot = __ballot_sync(0xffffffffu, has);
+    if ((threadIdx.x & 31) == 0) {
+      rows[k * 4] = ballot;
+      if (ballot) mine |= 1u << k;
+    }
+  }
+  if ((threadIdx.x & 31) == 0 && mine) atomicOr(&tile_bits, mine);
+  __syncthreads();
+  if (threadIdx.x == 0) tile_mask[tile] = tile_bits;
+}
+
+struct RegroupScratch {
+  uint32_t *keys, *keys_sorted;
+  int32_t *vals, *vals_sorted;
+  void* temp;
+  size_t temp_bytes, total;
+};
+RegroupScratch regroup_scratch(void* scratch, int kernel_vol, int64_t m_max) {
+  RegroupScratch r;
+  const size_t arr = align_up((size_t)(m_max > 0 ? m_max : 1) * 4, 256);
+  unsigned char* b = reinterpret_cast<unsigned char*>(scratch);
+  r.keys = reinterpret_cast<uint32_t*>(b), r.keys_sorted = reinterpret_cast<uint32_t*>(b + arr);
+  r.vals = reinterpret_cast<int32_t*>(b + 2 * arr), r.vals_sorted = reinterpret_cast<int32_t*>(b + 3 * arr);
+  r.temp = b + 4 * arr;
+  r.temp_bytes = 0;
+  // size query: host only, no launch
+  cub::DeviceRadixSort::SortPairs(nullptr, r.temp_bytes, (const uint32_t*)nullptr, (uint32_t*)nullptr,
+                                  (const int32_t*)nullptr, (int32_t*)nullptr, (int)m_max, 0, kernel_vol);
+  r.total = 4 * arr + align_up(r.temp_bytes, 256);
+  return r;
+}
+
+// ---------------------------------------------------------------------------------------------
 // SIMT kernel: tile of 32 outputs per CTA, 256 threads, thread = (row, 8-strided column group).
 // ---------------------------------------------------------------------------------------------
 constexpr int kTileM = 32;
@@ -123,21 +197,25 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 template <class T, int CPT>
 __global__ void __launch_bounds__(kSimtThreads)
 spconv_mm_simt_kernel(const T* __restrict__ in_feats, int64_t n_in_max, const T* __restrict__ weight,
-                      const float* __restrict__ bias, const int32_t* __restrict__ table, int64_t m_max,
-                      int64_t pitch, int kvol, int cin, int cout, T* __restrict__ out_feats, int relu, const T* __restrict__ residual) {
+                      const float* __restrict__ bias, const int32_t* __restrict__ table,
+                      const uint32_t* __restrict__ row_masks, const int32_t* __restrict__ perm, int64_t m_max,
+                      int kvol, int cin, int cout, T* __restrict__ out_feats, int relu, const T* __restrict__ residual) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* a_s = reinterpret_cast<float*>(smem_raw);                   // [kTileM][kChunkK + 1]
   float* w_s = a_s + kTileM * (kChunkK + 1);                         // [kChunkK][cout]
   int32_t* idx_s = reinterpret_cast<int32_t*>(w_s + kChunkK * cout); // [kvol][kTileM]
   int32_t* kvalid_s = idx_s + kvol * kTileM;                         // [kvol]
 
+  // the CTA's 32 tile rows are one quarter of a 128-row tile of the table: one row-mask word per offset
   const int64_t tile0 = (int64_t)blockIdx.x * kTileM;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int r = tid >> 3, cg = tid & 7;
+  const int64_t blk0 = (tile0 >> 7) * kvol;
+  const int quarter = (int)((tile0 & 127) >> 5);
 
   for (int k = warp; k < kvol; k += kSimtThreads / 32) {
-    int64_t o = tile0 + lane;
-    int v = o < m_max ? __ldg(table + ((o >> 7) * kvol + k) * 128 + (o & 127)) : -1;
+    const unsigned rows = __ldg(row_masks + (blk0 + k) * 4 + quarter);
+    int v = ((rows >> lane) & 1u) ? __ldg(table + (blk0 + k) * 128 + quarter * 32 + lane) : -1;
     if (!D3D_BOUNDS_OK(v, -1, n_in_max, kSiteMmSimtId) || v >= n_in_max) v = -1;
     idx_s[k * kTileM + lane] = v;
     unsigned any = __ballot_sync(0xffffffffu, v >= 0);
@@ -175,8 +253,8 @@ spconv_mm_simt_kernel(const T* __restrict__ in_feats, int64_t n_in_max, const T*
     }
   }
 
-  int64_t o = tile0 + r;
-  if (o < m_max) {
+  const int64_t o = __ldg(perm + tile0 + r);  // the output this tile row stands for, -1 = none
+  if (o >= 0 && o < m_max) {
 #pragma unroll
     for (int j = 0; j < CPT; ++j) {
       int col = cg + 8 * j;
@@ -200,6 +278,7 @@ template <class T> int launch_simt_typed(const MmLaunch& a) {
                 sizeof(int32_t) * ((size_t)kvol * kTileM + kvol);
   D3D_REQUIRE(smem <= 200 * 1024, D3D_ERR_TOO_LARGE);
   dim3 grid((unsigned)ceil_div(m_max, kTileM));
+  const TableParts tp = table_parts(const_cast<int32_t*>(a.table), kvol, m_max);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(a.stream);
   int cpt = (cout + 7) / 8;
 #define D3D_SIMT_CASE(N)                                                                                           \
@@ -207,9 +286,9 @@ template <class T> int launch_simt_typed(const MmLaunch& a) {
     auto kern = spconv_mm_simt_kernel<T, N>;                                                                       \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
     kern<<<grid, kSimtThreads, smem, st>>>(reinterpret_cast<const T*>(a.in_feats), a.max_num_act_in,               \
-                                           reinterpret_cast<const T*>(h->w_dev), h->b_dev, a.table, m_max,          \
-                                           (m_max + 127) / 128 * 128, kvol, cin, cout, reinterpret_cast<T*>(a.out_feats), a.relu,                    \
-                                           reinterpret_cast<const T*>(a.residual));                                \
+                                           reinterpret_cast<const T*>(h->w_dev), h->b_dev, tp.ids, tp.row_masks,    \
+                                           tp.perm, m_max, kvol, cin, cout, reinterpret_cast<T*>(a.out_feats),      \
+                                           a.relu, reinterpret_cast<const T*>(a.residual));                        \
   }
   if (cpt <= 2) D3D_SIMT_CASE(2)
   else if (cpt <= 4) D3D_SIMT_CASE(4)
@@ -401,9 +480,10 @@ extern "C" int d3d_spconv_mm_set_kernel(d3d_spconv_mm_t h, int which) {
 
 extern "C" size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out) {
   // rows are padded to a multiple of 128 entries so every 128-output tile can be read as a whole
-  // followed by one 32-bit offset mask per tile and four 32-bit row masks per (tile, offset)
+  // followed by one 32-bit offset mask per tile, four 32-bit row masks per (tile, offset) and the output row of
+  // every tile row
   return table_ids_bytes(kernel_vol, max_num_act_out) + table_mask_bytes(max_num_act_out) +
-         table_rows_bytes(kernel_vol, max_num_act_out);
+         table_rows_bytes(kernel_vol, max_num_act_out) + table_perm_bytes(max_num_act_out);
 }
 
 extern "C" int d3d_spconv_mm_workspace(d3d_spconv_mm_t h, const d3d_tensor_desc* in, int n_in, size_t* bytes) {
@@ -423,21 +503,46 @@ extern "C" int d3d_spconv_mm_prepare(int kernel_vol, int mode, int64_t max_num_a
   const int inverse = mode & 1;
   const int mirror = (mode & 2) && !inverse;  // a symmetric rulebook is its own inverse
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  int64_t pitch = (max_num_act_out + 127) / 128 * 128;
-  int64_t n16 = (int64_t)kernel_vol * pitch / 4;
-  uint32_t* tile_mask = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(table) +
-                                                    table_ids_bytes(kernel_vol, max_num_act_out));
-  const int64_t tiles = pitch / 128;
-  uint32_t* row_masks = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(tile_mask) +
-                                                    table_mask_bytes(max_num_act_out));
-  table_fill_kernel<<<stream_grid(n16, 256), 256, 0, st>>>(reinterpret_cast<int4*>(table), n16, row_masks,
-                                                           tiles * kernel_vol * 4);
+  const int64_t pitch = (max_num_act_out + 127) / 128 * 128;
+  const TableParts t = table_parts(table, kernel_vol, max_num_act_out);
+  table_fill_kernel<<<stream_grid(t.tiles * kernel_vol * 4, 256), 256, 0, st>>>(t.row_masks, t.tiles * kernel_vol * 4,
+                                                                               t.perm, t.tiles * 128, max_num_act_out);
   if (index_row_len > 0)
     table_scatter_kernel<<<stream_grid(index_row_len, 256), 256, 0, st>>>(
-        index, index_row_len, num_index, inverse, mirror, kernel_vol, pitch, reinterpret_cast<int32_t*>(table),
-        row_masks);
-  pack_mask_kernel<<<(unsigned)ceil_div(tiles * 32, 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(row_masks),
-                                                                        tiles, kernel_vol, tile_mask);
+        index, index_row_len, num_index, inverse, mirror, kernel_vol, pitch, t.ids, t.row_masks);
+  pack_mask_kernel<<<(unsigned)ceil_div(t.tiles * 32, 256), 256, 0, st>>>(reinterpret_cast<const uint4*>(t.row_masks),
+                                                                          t.tiles, kernel_vol, t.tile_mask);
+  D3D_CHECK_LAUNCH();
+  return D3D_OK;
+}
+
+// No plugin counterpart: see the header.
+extern "C" size_t d3d_spconv_mm_regroup_scratch_bytes(int kernel_vol, int64_t max_num_act_out) {
+  if (kernel_vol < 1 || kernel_vol > 32 || max_num_act_out < 0 || max_num_act_out >= (1ll << 31)) return 0;
+  return regroup_scratch(nullptr, kernel_vol, max_num_act_out).total;
+}
+
+extern "C" int d3d_spconv_mm_regroup(int kernel_vol, int64_t max_num_act_out, const void* table_in, void* table_out,
+                                     void* scratch, size_t scratch_bytes, void* stream) {
+  D3D_NVTX_RANGE("d3d_spconv_mm_regroup");
+  D3D_REQUIRE(kernel_vol >= 1 && kernel_vol <= 32 && max_num_act_out >= 0 && max_num_act_out < (1ll << 31),
+              D3D_ERR_INVALID_ARGUMENT);
+  if (max_num_act_out == 0) return D3D_OK;
+  D3D_REQUIRE(table_in && table_out && scratch && table_in != table_out, D3D_ERR_INVALID_ARGUMENT);
+  RegroupScratch r = regroup_scratch(scratch, kernel_vol, max_num_act_out);
+  D3D_REQUIRE(scratch_bytes >= r.total, D3D_ERR_WORKSPACE_TOO_SMALL);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const TableParts in = table_parts(const_cast<void*>(table_in), kernel_vol, max_num_act_out);
+  const TableParts out = table_parts(table_out, kernel_vol, max_num_act_out);
+  regroup_keys_kernel<<<(unsigned)ceil_div(max_num_act_out, 256), 256, 0, st>>>(in.row_masks, kernel_vol,
+                                                                                max_num_act_out, r.keys, r.vals);
+  // stable, so outputs with equal masks keep their order: the table is the same every time
+  if (cub::DeviceRadixSort::SortPairs(r.temp, r.temp_bytes, r.keys, r.keys_sorted, r.vals, r.vals_sorted,
+                                      (int)max_num_act_out, 0, kernel_vol, st) != cudaSuccess)
+    return D3D_ERR_CUDA;
+  regroup_gather_kernel<<<(unsigned)out.tiles, 128, 0, st>>>(in.ids, r.keys_sorted, r.vals_sorted, kernel_vol,
+                                                              max_num_act_out, out.ids, out.row_masks, out.tile_mask,
+                                                              out.perm);
   D3D_CHECK_LAUNCH();
   return D3D_OK;
 }
@@ -456,6 +561,7 @@ extern "C" int d3d_spconv_mm_run(d3d_spconv_mm_t h, int dtype, const void* in_fe
   a.table = reinterpret_cast<const int32_t*>(table), a.out_feats = out_feats;
   a.relu = epilogue ? epilogue->relu : 0;
   a.residual = epilogue ? epilogue->residual : nullptr;
+  a.regrouped = epilogue ? epilogue->regrouped : 0;
   a.stream = stream;
   bool tc_ok = spconv_mm_tc_eligible(h, dtype);
   if (h->kernel_choice == 2 || h->kernel_choice == 3) {

@@ -28,12 +28,14 @@ struct MmLaunch {
   const void* in_feats;
   int64_t max_num_act_in;
   const int32_t* num_act_out;
-  // [tiles][kVol][128] input row per (output tile, offset, row in tile), -1 = none; tiles = ceil(max_num_act_out /
-  // 128); then one offset mask per tile; then the row masks [tiles][kVol][4] (bit r of word q: row 32 q + r has an input)
+  // [tiles][kVol][128] input row per (output tile, offset, row in tile); tiles = ceil(max_num_act_out / 128); then
+  // one offset mask per tile; then the row masks [tiles][kVol][4] (bit r of word q: row 32 q + r has an input; an id
+  // whose bit is clear is unspecified); then the output row of every tile row, int32 [tiles][128] (-1 = none)
   const int32_t* table;
   void* out_feats;
   int relu;
   const void* residual;
+  int regrouped;  // hint: the table's outputs were regrouped (few offsets per tile)
   void* stream;
 };
 
@@ -51,6 +53,32 @@ inline size_t table_mask_bytes(int64_t max_num_act_out) {
 inline size_t table_rows_bytes(int kernel_vol, int64_t max_num_act_out) {
   const size_t tiles = (size_t)((max_num_act_out + 127) / 128);
   return (tiles * (size_t)kernel_vol * 4 * sizeof(uint32_t) + 255) / 256 * 256;
+}
+
+// The parts of a neighbour table.
+struct TableParts {
+  int32_t* ids;
+  uint32_t* tile_mask;
+  uint32_t* row_masks;
+  int32_t* perm;
+  int64_t tiles;
+};
+inline TableParts table_parts(void* table, int kernel_vol, int64_t max_num_act_out) {
+  TableParts t;
+  unsigned char* b = reinterpret_cast<unsigned char*>(table);
+  t.tiles = (max_num_act_out + 127) / 128;
+  t.ids = reinterpret_cast<int32_t*>(b);
+  b += table_ids_bytes(kernel_vol, max_num_act_out);
+  t.tile_mask = reinterpret_cast<uint32_t*>(b);
+  b += table_mask_bytes(max_num_act_out);
+  t.row_masks = reinterpret_cast<uint32_t*>(b);
+  b += table_rows_bytes(kernel_vol, max_num_act_out);
+  t.perm = reinterpret_cast<int32_t*>(b);
+  return t;
+}
+inline size_t table_perm_bytes(int64_t max_num_act_out) {
+  const size_t tiles = (size_t)((max_num_act_out + 127) / 128);
+  return (tiles * 128 * sizeof(int32_t) + 255) / 256 * 256;
 }
 
 int launch_spconv_mm_simt(const MmLaunch& a);

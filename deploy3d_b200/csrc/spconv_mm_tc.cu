@@ -99,6 +99,7 @@ struct TcParams {
   const int32_t* table;        // [tiles][kvol][128]
   const uint32_t* tile_mask;   // [tiles] bit k set: offset k feeds the tile
   const uint32_t* row_masks;   // [tiles][kvol][4] bit r of word q set: row 32 q + r has an input under the offset
+  const int32_t* perm;         // [tiles][128] output row of every tile row, -1 = none
   const void* in_feats;        // [n_in_rows][cin]
   int64_t m_max;
   int32_t n_in_rows;  // rows of the gathered tensor (an id outside [0, n_in_rows) = zero row)
@@ -304,49 +305,96 @@ template <int kGroup> __device__ __forceinline__ Smem carve_smem(unsigned char* 
   return s;
 }
 
-// The stage sequence of a tile is derived identically by every role from the tile's offset mask: the kernel
-// offsets are cut into windows of kGroup consecutive offsets; a window with at least one offset present is one
-// stage per K part, and offset `base + e` of the window owns block slot e of the stage whether or not its
-// neighbours in the window are present.  All addresses are then plain increments.
+// The stage sequence of a tile is derived identically by every role from the tile's offset mask, in ascending order of
+// the offsets, one stage per K part (see stage_bits for the two ways a stage picks its offsets).
 struct StageIter {
   int tile;
-  uint32_t mask;       // offset mask of `tile`
+  int round;           // how many tiles of this CTA came before `tile`
+  uint32_t rest;       // offsets of `tile` not yet handed out, including those of the current stage
   uint32_t mask_next;  // of the CTA's next tile, loaded while this one is walked (a load per tile is a round trip to L2)
-  int base;
+  uint32_t bits;       // the offsets of the current stage: packed stages, absolute; windows, relative to `base`
+  int base;            // windows only: first offset of the stage's window
   int part;
-  uint32_t take;  // offsets of the window [base, base + kGroup) that are present
 };
 __device__ __forceinline__ uint32_t load_mask(const TcParams& p, int tile) {
   return tile < p.num_tiles ? __ldg(p.tile_mask + tile) : 0u;
 }
-template <int kGroup> __device__ __forceinline__ void first_tile(const TcParams& p, StageIter& it) {
-  it.tile = blockIdx.x;
-  it.mask = load_mask(p, it.tile);
-  it.mask_next = load_mask(p, it.tile + gridDim.x);
+// The CTA's tile of round r, or num_tiles when it has none.  A regrouped table holds its tiles in ascending order of
+// their offset masks, the costly ones last: there the CTAs take the tiles round by round from the last tile down, in
+// alternating direction, so that every CTA starts with a costly tile and the rounds pair a CTA's costlier tiles with
+// cheaper ones.
+template <bool kPacked> __device__ __forceinline__ int tile_at(const TcParams& p, int round) {
+  const int g = (int)gridDim.x, c = (int)blockIdx.x;
+  if (!kPacked) {  // plain tables: every tile costs about the same, the CTAs sweep them front to back
+    const int idx = round * g + c;
+    return idx < p.num_tiles ? idx : p.num_tiles;
+  }
+  const int idx = round * g + ((round & 1) ? g - 1 - c : c);
+  return idx < p.num_tiles ? p.num_tiles - 1 - idx : p.num_tiles;
+}
+// Two ways a stage picks its offsets.  kPacked: the kGroup lowest offsets still present (tables whose outputs were
+// regrouped have few offsets per tile, anywhere among the kVol).  Otherwise: the present offsets of the next window
+// of kGroup consecutive offsets that has any -- a plain table has nearly all offsets in every tile, and with fixed
+// windows the offset of slot e is window + e, so every address is the window's plus a constant.
+template <int kGroup> __device__ __forceinline__ uint32_t lowest_bits(uint32_t m) {
+  uint32_t r = m;
+#pragma unroll
+  for (int e = 0; e < kGroup; ++e) r &= r - 1u;
+  return m & ~r;
+}
+// Offset of every slot of a stage (always a valid index) and, as bit e of the result, whether slot e is in use.
+template <int kGroup, bool kPacked>
+__device__ __forceinline__ uint32_t slot_offsets(uint32_t bits, int base, int (&k)[kGroup]) {
+  if (kPacked) {
+    const uint32_t used = (1u << __popc(bits)) - 1u;
+#pragma unroll
+    for (int e = 0; e < kGroup; ++e) {
+      k[e] = bits ? __ffs(bits) - 1 : 0;
+      bits &= bits - 1u;
+    }
+    return used;
+  }
+#pragma unroll
+  for (int e = 0; e < kGroup; ++e) k[e] = base + e;
+  return bits;
+}
+template <int kGroup, bool kPacked> __device__ __forceinline__ void first_tile(const TcParams& p, StageIter& it) {
+  it.round = 0;
+  it.tile = tile_at<kPacked>(p, 0);
+  it.rest = load_mask(p, it.tile);
+  it.mask_next = load_mask(p, tile_at<kPacked>(p, 1));
+  it.bits = 0;
   it.base = -kGroup;
   it.part = p.kparts - 1;
-  it.take = 0;
 }
 // Moves to the next stage of this CTA's tiles; false when there is none.
-template <int kGroup> __device__ __forceinline__ bool next_stage(const TcParams& p, StageIter& it) {
+template <int kGroup, bool kPacked> __device__ __forceinline__ bool next_stage(const TcParams& p, StageIter& it) {
   constexpr uint32_t gmask = (1u << kGroup) - 1u;
   if (++it.part < p.kparts) return true;
   it.part = 0;
-  it.base += kGroup;
+  if (kPacked) it.rest &= ~it.bits;
+  else it.base += kGroup;
   for (;;) {
     if (it.tile >= p.num_tiles) return false;
-    while (it.base < p.kvol) {
-      const uint32_t take = (it.mask >> it.base) & gmask;
-      if (take) {
-        it.take = take;
+    if (kPacked) {
+      if (it.rest) {
+        it.bits = lowest_bits<kGroup>(it.rest);
         return true;
       }
-      it.base += kGroup;
+    } else {
+      while (it.base < p.kvol) {
+        const uint32_t take = (it.rest >> it.base) & gmask;
+        if (take) {
+          it.bits = take;
+          return true;
+        }
+        it.base += kGroup;
+      }
+      it.base = 0;
     }
-    it.tile += gridDim.x;
-    it.base = 0;
-    it.mask = it.mask_next;
-    it.mask_next = load_mask(p, it.tile + gridDim.x);
+    it.tile = tile_at<kPacked>(p, ++it.round);
+    it.rest = it.mask_next;
+    it.mask_next = load_mask(p, tile_at<kPacked>(p, it.round + 1));
   }
 }
 
@@ -445,7 +493,7 @@ __device__ __forceinline__ void cta_teardown(const TcParams& p, uint32_t tmem_ba
 // the same for the whole warp -- predicates the copies, and the MMA warp keeps the other accumulator lanes out of the
 // product, so whatever an unused row of the ring holds is never seen.  Ids and row masks come straight from global
 // memory; the loads of the team's next stage are issued before the copies of this one.
-template <int kPieces, int kChunks, int kGroup, int kProdWarps>
+template <int kPieces, int kChunks, int kGroup, int kProdWarps, bool kPacked>
 __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, int warp, int lane) {
   constexpr int kTeams = kProdWarps / 4;
   constexpr int kRows = 32;                   // rows of a block per warp
@@ -473,15 +521,28 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
     uint32_t rows[kGroup];  // row mask word of this warp's quarter, 0 for an offset the stage does not take
   };
   auto load_ids = [&](const StageIter& it, Ids& v) {
-    const int64_t blk = (int64_t)it.tile * p.kvol + it.base;
-    const int32_t* base = p.table + blk * kTileRows + row0;
-    const uint32_t* rows = p.row_masks + blk * 4 + quarter;
+    const int64_t blk0 = (int64_t)it.tile * p.kvol;
+    if (kPacked) {
+      int k[kGroup];
+      const uint32_t used = slot_offsets<kGroup, true>(it.bits, 0, k);
 #pragma unroll
-    for (int e = 0; e < kGroup; ++e) {
-      const bool take = (it.take >> e) & 1u;
-      v.rows[e] = take ? __ldg(rows + e * 4) : 0u;
+      for (int e = 0; e < kGroup; ++e) {
+        const bool take = (used >> e) & 1u;
+        const int32_t* base = p.table + (blk0 + k[e]) * kTileRows + row0;
+        v.rows[e] = take ? __ldg(p.row_masks + (blk0 + k[e]) * 4 + quarter) : 0u;
 #pragma unroll
-      for (int i = 0; i < kPasses; ++i) v.id[e][i] = take ? __ldg(base + e * kTileRows + i * kRowsPerPass) : -1;
+        for (int i = 0; i < kPasses; ++i) v.id[e][i] = take ? __ldg(base + i * kRowsPerPass) : -1;
+      }
+    } else {  // the window's blocks follow each other in the table: constant offsets from its first block
+      const int32_t* base = p.table + (blk0 + it.base) * kTileRows + row0;
+      const uint32_t* rows = p.row_masks + (blk0 + it.base) * 4 + quarter;
+#pragma unroll
+      for (int e = 0; e < kGroup; ++e) {
+        const bool take = (it.bits >> e) & 1u;
+        v.rows[e] = take ? __ldg(rows + e * 4) : 0u;
+#pragma unroll
+        for (int i = 0; i < kPasses; ++i) v.id[e][i] = take ? __ldg(base + e * kTileRows + i * kRowsPerPass) : -1;
+      }
     }
   };
   // the neighbour ids of a tile are kvol * 512 contiguous bytes: one 128-byte line per lane of a team
@@ -496,11 +557,11 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   auto next_own = [&](StageIter& it) -> bool {
 #pragma unroll
     for (int t = 0; t < kTeams; ++t)
-      if (!next_stage<kGroup>(p, it)) return false;
+      if (!next_stage<kGroup, kPacked>(p, it)) return false;
     return true;
   };
   pdl_wait();  // masks, ids and features may come from the preceding kernels
-  prefetch_ids((int)blockIdx.x + (int)gridDim.x);
+  prefetch_ids(tile_at<kPacked>(p, 1));
   int stage = team;  // slot of the team's current stage (at least two stages exist)
   uint32_t phase = 0;
   PROF_DECL
@@ -513,7 +574,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
     if (have_next) load_ids(nxt, ids_next);
     // on entering a tile, pull the ids of the CTA's next tile towards the SM: they may come from DRAM, which takes
     // longer than the one stage the loads above run ahead
-    if (have_next && nxt.tile != cur.tile) prefetch_ids(nxt.tile + (int)gridDim.x);
+    if (have_next && nxt.tile != cur.tile) prefetch_ids(tile_at<kPacked>(p, nxt.round + 1));
     PROF(1);
     if (!mbar_wait_warp(&sh->empty[stage], phase ^ 1, abort_flag, 12)) return false;
     PROF(2);
@@ -530,7 +591,10 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
 #pragma unroll
       for (int i = 0; i < kPasses; ++i)
       {
-        (void)D3D_BOUNDS_OK(ids.id[e][i], -1, (long long)last_in_row + 1, kSiteMmTcId);  // checked build: recorded
+#ifdef DEPLOY3D_BOUNDS_CHECK  // ids of rows that have an input (the others are unspecified) are recorded when off
+        if ((ids.rows[e] >> (rsub + i * kRowsPerPass)) & 1u)
+          (void)D3D_BOUNDS_OK(ids.id[e][i], 0, (long long)last_in_row + 1, kSiteMmTcId);
+#endif
         src[e][i] = src_part + (uint64_t)min((uint32_t)ids.id[e][i], last_in_row) * row_src_bytes;
       }
 #pragma unroll
@@ -555,9 +619,9 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
   // two id buffers used in turn: the loaded ids are first touched a whole stage after their loads were issued
   StageIter it_a, it_b;
   Ids ids_a, ids_b;
-  first_tile<kGroup>(p, it_a);
+  first_tile<kGroup, kPacked>(p, it_a);
   bool have = true;
-  for (int t = 0; t <= team && have; ++t) have = next_stage<kGroup>(p, it_a);
+  for (int t = 0; t <= team && have; ++t) have = next_stage<kGroup, kPacked>(p, it_a);
   if (have) {
     load_ids(it_a, ids_a);
     while (step(it_a, ids_a, it_b, ids_b) && step(it_b, ids_b, it_a, ids_a)) {
@@ -569,7 +633,7 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
 // ---- control warp (one lane) ---------------------------------------------------------------------------------------
 // Brings in the weights: all of them once when they are resident, else the blocks of every stage as soon as the
 // stage is free.
-template <int kGroup>
+template <int kGroup, bool kPacked>
 __device__ __forceinline__ void control_role(const TcParams& p, const Smem& s, const CUtensorMap* map_b) {
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
@@ -586,19 +650,21 @@ __device__ __forceinline__ void control_role(const TcParams& p, const Smem& s, c
   }
   pdl_wait();  // the offset masks come from the preceding kernels
   StageIter it;
-  first_tile<kGroup>(p, it);
+  first_tile<kGroup, kPacked>(p, it);
   int stage = 0;
   uint32_t phase = 0;
-  while (next_stage<kGroup>(p, it)) {
+  while (next_stage<kGroup, kPacked>(p, it)) {
     if (!mbar_wait(&sh->empty[stage], phase ^ 1, abort_flag, 11)) return;
-    mbar_arrive_expect_tx(&sh->full[stage], (uint32_t)__popc(it.take) * b_tx);
+    mbar_arrive_expect_tx(&sh->full[stage], (uint32_t)__popc(it.bits) * b_tx);
     unsigned char* b_dst = s.tiles + (size_t)stage * s.stage_bytes + (size_t)kGroup * p.a_bytes;
+    int k[kGroup];
+    const uint32_t used = slot_offsets<kGroup, kPacked>(it.bits, it.base, k);
 #pragma unroll
     for (int e = 0; e < kGroup; ++e, b_dst += p.b_bytes) {
-      if (!((it.take >> e) & 1u)) continue;
+      if (!((used >> e) & 1u)) continue;
       for (int c = 0; c < p.chunks; ++c)
         tma_load_2d(map_b, &sh->full[stage], b_dst + (size_t)c * p.cout * p.row_bytes,
-                    it.part * p.kchunk + c * 64, (it.base + e) * p.cout);
+                    it.part * p.kchunk + c * 64, k[e] * p.cout);
     }
     if (++stage == p.stages) stage = 0, phase ^= 1;
   }
@@ -615,13 +681,12 @@ __device__ __forceinline__ uint32_t desc_lo(uint32_t smem_addr) { return ((smem_
 // and the commit.  Every MMA accumulates (the epilogue hands the accumulators over zeroed) and updates only the
 // accumulator lanes of rows that have an input under its offset: the row masks of a tile are loaded a tile ahead
 // (one coalesced load per 32 words), parked inverted in shared memory, and the issuing lane reads four words per offset.
-template <int kPieces, int kChunks, int kGroup>
+template <int kPieces, int kChunks, int kGroup, bool kPacked>
 __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint32_t tmem_base) {
   constexpr int kSteps = kPieces * kChunks / 2;  // tcgen05.mma instructions (K = 16 each) per block
   constexpr uint32_t kRowBytes = kPieces * 16;
   constexpr uint32_t a_step = (kTileRows * kRowBytes * kChunks) >> 4;  // = p.a_bytes / 16
   constexpr uint32_t cs_a = (kTileRows * kRowBytes) >> 4;              // between the 64-column blocks of A
-  constexpr uint32_t gmask = (1u << kGroup) - 1u;
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
   const int lane = threadIdx.x & 31;
@@ -635,8 +700,8 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
   if (resident && !__all_sync(0xffffffffu, mbar_wait(&sh->b_ready, 0, abort_flag, 23))) return;
   int stage = 0, acc = 0, buf = 0;
   uint32_t phase = 0, acc_phase = 0;
-  const int num_stages = p.stages, kvol = p.kvol, kparts = p.kparts;
-  const int row_words = kvol * 4;  // at most 128
+  const int num_stages = p.stages, kparts = p.kparts;
+  const int row_words = p.kvol * 4;  // at most 128
   bool landed = false;  // the stage about to be waited for was already seen full by the probe below
   pdl_wait();
   PROF_DECL
@@ -647,9 +712,9 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
     for (int i = 0; i < 4; ++i)
       rows_ahead[i] = (tile < p.num_tiles && lane + 32 * i < row_words) ? __ldg(w + 32 * i) : 0u;
   };
-  uint32_t mask_ahead = load_mask(p, blockIdx.x);
-  load_rows(blockIdx.x);
-  for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+  uint32_t mask_ahead = load_mask(p, tile_at<kPacked>(p, 0));
+  load_rows(tile_at<kPacked>(p, 0));
+  for (int round = 0, tile; (tile = tile_at<kPacked>(p, round)) < p.num_tiles; ++round) {
     const uint32_t mask = __shfl_sync(0xffffffffu, mask_ahead, 0);
     uint32_t* lanes_off = sh->lanes_off[buf];
     if (mask != 0) {
@@ -657,8 +722,8 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
       for (int i = 0; i < 4; ++i) lanes_off[lane + 32 * i] = ~rows_ahead[i];
     }
     // round trips to L2: in flight while this tile is issued
-    mask_ahead = load_mask(p, tile + gridDim.x);
-    load_rows(tile + gridDim.x);
+    mask_ahead = load_mask(p, tile_at<kPacked>(p, round + 1));
+    load_rows(tile_at<kPacked>(p, round + 1));
     if (mask == 0) continue;  // a tile no offset feeds uses no accumulator: the epilogue writes its bias rows alone
     __syncwarp();
     PROF(0);
@@ -666,9 +731,23 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
     tc_fence_after();
     PROF(4);
     const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.cout);
-    for (int base = 0; base < kvol; base += kGroup) {
-      const uint32_t take = (mask >> base) & gmask;
-      if (take == 0) continue;
+    int base = 0;
+    for (uint32_t rest = mask; rest != 0u;) {
+      uint32_t bits;  // the offsets of the tile's next stage
+      if (kPacked) {
+        bits = lowest_bits<kGroup>(rest);
+        rest &= ~bits;
+      } else {
+        bits = (rest >> base) & ((1u << kGroup) - 1u);
+        rest &= ~(bits << base);
+        if (bits == 0u) {
+          base += kGroup;
+          continue;
+        }
+      }
+      int k[kGroup];
+      const uint32_t used = slot_offsets<kGroup, kPacked>(bits, base, k);
+      if (!kPacked) base += kGroup;
       for (int part = 0; part < kparts; ++part) {
         // the full barrier guards shared memory only: no tcgen05 fence is needed, but the rows written by
         // cp.async (generic proxy) must be made visible to the tensor core's reads (async proxy)
@@ -684,29 +763,32 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
         const uint32_t phase_next = phase ^ (wrap ? 1u : 0u);
         const bool landed_next = mbar_test(&sh->full[stage_next], phase_next);
         const uint32_t a_lo = tiles_lo + (uint32_t)stage * stage_step;
-        const uint32_t b_lo = resident ? bres_lo + (uint32_t)base * b_step : a_lo + (uint32_t)kGroup * a_step;
+        const uint32_t b_stage = a_lo + (uint32_t)kGroup * a_step;
         // descriptors of all MMAs of the stage first (independent, warp-uniform arithmetic), then the straight
         // line of MMAs: the issuing lane runs no dependent chain between two of them
         uint64_t desc_a[kGroup][kSteps], desc_b[kGroup][kSteps];
 #pragma unroll
         for (int e = 0; e < kGroup; ++e) {
+          // resident weights are indexed by the offset, streamed ones by the slot
+          const uint32_t b_lo = resident ? bres_lo + (uint32_t)k[e] * b_step
+                                         : b_stage + (uint32_t)e * b_step;
 #pragma unroll
           for (int ks = 0; ks < kSteps; ++ks) {
             // 32 bytes per K step inside the swizzle span, the next 64-column block every 4 steps
             const uint32_t adv_a = (uint32_t)e * a_step + (uint32_t)(ks >> 2) * cs_a + (uint32_t)(ks & 3) * 2u;
-            const uint32_t adv_b = (uint32_t)e * b_step + (uint32_t)(ks >> 2) * cs_b + (uint32_t)(ks & 3) * 2u;
+            const uint32_t adv_b = (uint32_t)(ks >> 2) * cs_b + (uint32_t)(ks & 3) * 2u;
             desc_a[e][ks] = desc_hi | (a_lo + adv_a);
             desc_b[e][ks] = desc_hi | (b_lo + adv_b);
           }
         }
         if (elect_one()) {
-          const uint4* off = reinterpret_cast<const uint4*>(lanes_off) + base;
+          const uint4* off = reinterpret_cast<const uint4*>(lanes_off);
 #pragma unroll
           for (int e = 0; e < kGroup; ++e) {
-            const uint4 o = off[e];  // beyond kvol: inside the buffer, never used (the offset is not taken)
+            const uint4 o = off[k[e]];
 #pragma unroll
             for (int ks = 0; ks < kSteps; ++ks)
-              umma_f16_rows_if((take >> e) & 1u, d_addr, desc_a[e][ks], desc_b[e][ks], idesc, o);
+              umma_f16_rows_if((used >> e) & 1u, d_addr, desc_a[e][ks], desc_b[e][ks], idesc, o);
           }
           umma_commit(&sh->empty[stage]);  // the stage may be refilled once these MMAs have read it
         }
@@ -726,6 +808,7 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
 // ---- epilogue ----------------------------------------------------------------------------------------------------
 // Epilogue warp `quad` (= warp index mod 4: it may touch TMEM lanes [32*quad, 32*quad + 32)).  The accumulators are
 // handed to the MMA warp zeroed: once at the start, then every time one has been read.
+template <bool kPacked>
 __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, uint32_t tmem_base, int quad) {
   Shared* sh = s.sh;
   volatile int* abort_flag = &sh->abort_flag;
@@ -741,11 +824,22 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
     if (lane == 0) mbar_arrive(&sh->acc_empty[a]);
   }
   pdl_wait();  // residual rows come from an earlier layer; output rows may still be read by the preceding kernel
-  uint32_t mask = (int)blockIdx.x < p.num_tiles ? __ldg(p.tile_mask + blockIdx.x) : 0u;
+  uint32_t mask = load_mask(p, tile_at<kPacked>(p, 0));
+  // the output a tile row stands for (the row itself, unless the table's outputs were regrouped): loaded a tile ahead
+  auto load_row = [&](int tile) -> int {
+#ifdef D3D_TC_NO_PERM
+    return tile < p.num_tiles ? tile * kTileRows + quad * 32 + lane : -1;
+#else
+    return tile < p.num_tiles ? __ldg(p.perm + (int64_t)tile * kTileRows + quad * 32 + lane) : -1;
+#endif
+  };
+  int row_ahead = load_row(tile_at<kPacked>(p, 0));
   PROF_DECL
-  for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-    const int next = tile + gridDim.x;
+  for (int round = 0, tile; (tile = tile_at<kPacked>(p, round)) < p.num_tiles; ++round) {
+    const int next = tile_at<kPacked>(p, round + 1);
     const uint32_t next_mask = next < p.num_tiles ? __ldg(p.tile_mask + next) : 0u;
+    const int64_t row = row_ahead;
+    row_ahead = load_row(next);
     const bool empty_tile = mask == 0;  // bias (+ residual) only, no accumulator involved
     PROF(0);
     if (!empty_tile) {
@@ -753,8 +847,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
       tc_fence_after();
     }
     PROF(1);
-    const int64_t row = (int64_t)tile * kTileRows + quad * 32 + lane;
-    const bool row_ok = row < p.m_max;
+    const bool row_ok = row >= 0 && row < p.m_max;
     unsigned short* out_row = reinterpret_cast<unsigned short*>(p.out) + row * p.cout;
     const unsigned short* res_row =
         (p.residual && row_ok) ? reinterpret_cast<const unsigned short*>(p.residual) + row * p.cout : nullptr;
@@ -789,7 +882,7 @@ __device__ __forceinline__ void epilogue_role(const TcParams& p, const Smem& s, 
 
 // kPieces x kChunks = 16-byte pieces per A row (2, 4, 8, 16), kGroup = offsets per stage, kProdWarps = 4 or 8,
 // kCtas = CTAs per SM the launch is planned for (1 or 2).
-template <int kPieces, int kChunks, int kGroup, int kProdWarps, int kCtas>
+template <int kPieces, int kChunks, int kGroup, int kProdWarps, int kCtas, bool kPacked>
 __global__ void __launch_bounds__(threads_of(kProdWarps), kCtas)
 spconv_mm_tc_kernel(const __grid_constant__ CUtensorMap map_b, const TcParams p) {
   extern __shared__ __align__(1024) unsigned char smem_raw[];
@@ -798,15 +891,15 @@ spconv_mm_tc_kernel(const __grid_constant__ CUtensorMap map_b, const TcParams p)
   const uint32_t tmem_base = cta_setup<kProdWarps>(p, s);
   pdl_release();
   if (warp < kProdWarps) {
-    producer_role<kPieces, kChunks, kGroup, kProdWarps>(p, s, warp, lane);
+    producer_role<kPieces, kChunks, kGroup, kProdWarps, kPacked>(p, s, warp, lane);
   } else if (warp == kProdWarps) {
-    mma_role<kPieces, kChunks, kGroup>(p, s, tmem_base);
+    mma_role<kPieces, kChunks, kGroup, kPacked>(p, s, tmem_base);
     __syncwarp();
   } else if (warp == kProdWarps + 1) {
-    if (lane == 0) control_role<kGroup>(p, s, &map_b);
+    if (lane == 0) control_role<kGroup, kPacked>(p, s, &map_b);
     __syncwarp();
   } else {
-    epilogue_role(p, s, tmem_base, warp & 3);
+    epilogue_role<kPacked>(p, s, tmem_base, warp & 3);
   }
   cta_teardown<kProdWarps>(p, tmem_base);
 }
@@ -856,9 +949,10 @@ int g_plan_group = 0, g_plan_stages = 0, g_plan_prod_warps = 0;
 typedef void (*KernelFn)(const CUtensorMap, const TcParams);
 struct KernelEntry {
   int pieces, chunks, group, prod_warps, ctas;
-  KernelFn fn;
+  KernelFn fn[2];  // fixed windows of offsets per stage / the offsets present packed into the stages
 };
-#define D3D_TC_K(P, C, G, W, N) {P, C, G, W, N, spconv_mm_tc_kernel<P, C, G, W, N>}
+#define D3D_TC_K(P, C, G, W, N) \
+  {P, C, G, W, N, {spconv_mm_tc_kernel<P, C, G, W, N, false>, spconv_mm_tc_kernel<P, C, G, W, N, true>}}
 // One kernel instance per (row width of a block, offsets per stage, CTAs per SM).
 const KernelEntry kKernels[] = {
     D3D_TC_K(2, 1, 8, 8, 2), D3D_TC_K(2, 1, 4, 8, 2), D3D_TC_K(2, 1, 2, 8, 2), D3D_TC_K(2, 1, 1, 8, 2),
@@ -927,6 +1021,8 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
                                                   table_ids_bytes(kvol, m_max));
   p.row_masks = reinterpret_cast<const uint32_t*>(reinterpret_cast<const unsigned char*>(p.tile_mask) +
                                                   table_mask_bytes(m_max));
+  p.perm = reinterpret_cast<const int32_t*>(reinterpret_cast<const unsigned char*>(p.row_masks) +
+                                            table_rows_bytes(kvol, m_max));
   p.in_feats = a.in_feats;
   p.m_max = m_max;
   p.n_in_rows = (int32_t)a.max_num_act_in;
@@ -1027,19 +1123,20 @@ int launch_spconv_mm_tc(const MmLaunch& a) {
   p.a_bytes = (uint32_t)((size_t)kTileRows * pl.kchunk * 2);
   p.b_bytes = (uint32_t)align_up((size_t)cout * pl.kchunk * 2, swizzle_repeat);
   p.b_resident = pl.resident, p.stages = pl.stages;
-  const KernelFn kernel = pl.kernel->fn;
+  const int packed = a.regrouped ? 1 : 0;
+  const KernelFn kernel = pl.kernel->fn[packed];
   {
     // raising the dynamic shared memory limit is per function and per device; once each, under a lock
     static std::mutex attr_lock;
-    static bool attr_set[64][kNumKernels] = {};
+    static bool attr_set[64][kNumKernels][2] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return D3D_ERR_CUDA;
     const int ki = (int)(pl.kernel - kKernels);
     std::lock_guard<std::mutex> guard(attr_lock);
-    if (!attr_set[dev][ki]) {
+    if (!attr_set[dev][ki][packed]) {
       if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess)
         return D3D_ERR_CUDA;
-      attr_set[dev][ki] = true;
+      attr_set[dev][ki][packed] = true;
     }
   }
   const int ctas = kNumSMs * (two_per_sm ? 2 : 1);

@@ -20,7 +20,8 @@ class DetectionPipeline:
     """CenterPoint-shaped (``kind='centerpoint'``) or SECOND-shaped (``kind='second'``) frame pipeline."""
 
     def __init__(self, kind="centerpoint", device="cuda:0", caps=None, kernel=0, n_class=10, topk=1000,
-                 iou_threshold=0.2, dtype=torch.float16, n_pts=None, overlap_rulebooks=True, plugin_order=False):
+                 iou_threshold=0.2, dtype=torch.float16, n_pts=None, overlap_rulebooks=True, plugin_order=False,
+                 regroup=False):
         self.kind, self.device, self.dtype = kind, torch.device(device), dtype
         # plugin order: one stream, nodes in ONNX order through the plugin-level entry points only (see SparseNet)
         self.plugin_order = plugin_order
@@ -51,7 +52,8 @@ class DetectionPipeline:
             self.vox_num = torch.zeros(1, dtype=torch.int32, device=dev)
             spatial_b = [self.spatial[0]] + list(self.spatial[2:])
             self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel,
-                                          overlap_rulebooks=overlap_rulebooks, plugin_order=plugin_order)
+                                          overlap_rulebooks=overlap_rulebooks, plugin_order=plugin_order,
+                                          regroup=regroup)
             # low-precision copy of the voxel features, zero-padded to the channel count the first layer runs with
             self.vox_feats_lp = torch.zeros((cap_in, self.net.in_channels), dtype=dtype, device=dev)
             self.net.set_input(self.vox_coors, self.vox_num)
@@ -177,7 +179,7 @@ class SegmentationPipeline:
     1x3x3 SubM blocks, channels 32 / 64 / 128 / 256, 20 classes); ``net='unet'`` a small 3x3x3 encoder-decoder."""
 
     def __init__(self, device="cuda:0", n_pts=120000, caps=None, n_class=None, dtype=torch.float16, kernel=0,
-                 net="cylinder3d", overlap_rulebooks=True):
+                 net="cylinder3d", overlap_rulebooks=True, regroup=False):
         from .ops import data_s_gather_back, data_s_scatter_to
         frame = synth.config5_points()
         self.device, self.dtype, self.n_pts = torch.device(device), dtype, int(n_pts)
@@ -210,7 +212,7 @@ class SegmentationPipeline:
             self.vox_feats = torch.zeros((cap, self.c_pts + 5), dtype=torch.float32, device=dev)
             spatial_b = [self.spatial[0]] + list(self.spatial[2:])
             self.net = backbone.SparseNet(self.layers, spatial_b, self.caps, dtype=dtype, device=dev, kernel=kernel,
-                                          overlap_rulebooks=overlap_rulebooks)
+                                          overlap_rulebooks=overlap_rulebooks, regroup=regroup)
             self.vox_feats_lp = torch.zeros((cap, self.net.in_channels), dtype=dtype, device=dev)
             self.net.set_input(self.vox_coors, self.vox_num)
             self.gather = deserialize_plugin("GatherBack", data_s_gather_back(0.0))

@@ -228,11 +228,37 @@ class SPConvMMPlugin(_Plugin):
                                               ctypes.c_void_p(table.data_ptr()), _stream_ptr(stream)))
         return table
 
-    def run(self, in_feats, num_act_out, table, out=None, relu=False, residual=None, stream=None):
+    @staticmethod
+    def regroup_scratch_bytes(kernel_vol, max_num_act_out):
+        return int(lib().d3d_spconv_mm_regroup_scratch_bytes(int(kernel_vol), int(max_num_act_out)))
+
+    @staticmethod
+    def regroup(kernel_vol, max_num_act_out, table_in, table_out=None, scratch=None, stream=None):
+        """The table with its outputs grouped by offset mask (d3d_spconv_mm_regroup): same results from `run`, fewer
+        (tile, offset) blocks for it to walk.  Returns table_out."""
+        nbytes = SPConvMMPlugin.table_bytes(kernel_vol, max_num_act_out)
+        sbytes = SPConvMMPlugin.regroup_scratch_bytes(kernel_vol, max_num_act_out)
+        if table_out is None:
+            table_out = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=table_in.device)
+        if scratch is None:
+            scratch = torch.empty(max(sbytes, 16), dtype=torch.uint8, device=table_in.device)
+        assert table_in.numel() >= nbytes and table_out.numel() >= nbytes and scratch.numel() >= sbytes
+        with torch.cuda.device(table_in.device):
+            check("d3d_spconv_mm_regroup",
+                  lib().d3d_spconv_mm_regroup(int(kernel_vol), int(max_num_act_out),
+                                              ctypes.c_void_p(table_in.data_ptr()),
+                                              ctypes.c_void_p(table_out.data_ptr()),
+                                              ctypes.c_void_p(scratch.data_ptr()), int(scratch.numel()),
+                                              _stream_ptr(stream)))
+        return table_out
+
+    def run(self, in_feats, num_act_out, table, out=None, relu=False, residual=None, stream=None, regrouped=False):
+        """`regrouped`: hint that `table` came from `regroup` (same results either way)."""
         if out is None:
             out = torch.empty((self.p.max_num_act_out, self.p.out_channels), dtype=in_feats.dtype,
                               device=in_feats.device)
-        epi = _lib.SpconvMMEpilogue(int(relu), residual.data_ptr() if residual is not None else None)  # relu: 0 / 1 / 2
+        epi = _lib.SpconvMMEpilogue(int(relu), residual.data_ptr() if residual is not None else None,  # relu: 0 / 1 / 2
+                                    int(bool(regrouped)))
         with torch.cuda.device(in_feats.device):
             check("d3d_spconv_mm_run",
                   lib().d3d_spconv_mm_run(self.handle, _TORCH2D3D[in_feats.dtype],

@@ -182,10 +182,13 @@ typedef struct {
 /* Epilogue fused after bias; all zero == the reference plugin (activation is a separate graph op there,
  * tests/cylinder/test_cylinder3d.py:91-92).  `residual` (same dtype/shape as outFeats) is added to the result.
  * relu: 0 none; 1 ReLU after the residual add (residual block); 2 ReLU before it (sum of two activated branches,
- * tests/cylinder/test_cylinder3d.py:113-124). */
+ * tests/cylinder/test_cylinder3d.py:113-124).
+ * regrouped: a hint, nonzero when `table` went through d3d_spconv_mm_regroup: the kernel then packs the few offsets a
+ * tile has left into its pipeline stages instead of walking fixed windows of offsets.  Results do not depend on it. */
 typedef struct {
   int32_t relu;
   const void* residual;
+  int32_t regrouped;
 } d3d_spconv_mm_epilogue;
 
 int d3d_spconv_mm_create(const void* data_s, size_t len, d3d_spconv_mm_t* handle);
@@ -217,6 +220,19 @@ int d3d_spconv_mm_enqueue(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int
  * unique and inside the grid (with duplicates the rulebook is not symmetric and the mirrored build writes a wrong
  * table).  The plugin-level d3d_spconv_mm_enqueue never sets bit 1. */
 size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out);
+/* Optional step between prepare and run (no reference counterpart): rebuilds a neighbour table with its outputs
+ * grouped by offset mask.  The convolution kernel works on tiles of 128 outputs and spends a pipeline slot, a weight
+ * block and its MMAs on every kernel offset that feeds at least one output of the tile; in voxel order that is nearly
+ * every offset for every tile.  Sorted by which offsets feed them, outputs with like masks share tiles and most
+ * (tile, offset) blocks disappear (LiDAR frames: 27 -> 4..19 per tile).  `table_in` is a table as d3d_spconv_mm_prepare
+ * or the SubM probe kernel wrote it, `table_out` a second buffer of d3d_spconv_mm_table_bytes bytes, `scratch`
+ * d3d_spconv_mm_regroup_scratch_bytes bytes.  The regrouped table records the output row of every tile row, run writes
+ * every row where it belongs and accumulates every output's offsets in the same order: results are bit-identical to
+ * those of the plain table.  Worth its three kernels (keys, a radix sort, a gather) when several layers share the
+ * rulebook or the rulebook is very sparse.  kernel_vol <= 32. */
+size_t d3d_spconv_mm_regroup_scratch_bytes(int kernel_vol, int64_t max_num_act_out);
+int d3d_spconv_mm_regroup(int kernel_vol, int64_t max_num_act_out, const void* table_in, void* table_out,
+                          void* scratch, size_t scratch_bytes, void* stream);
 int d3d_spconv_mm_prepare(int kernel_vol, int mode, int64_t max_num_act_out, const int32_t* index,
                           int64_t index_row_len, const int32_t* num_index, void* table, void* stream);
 int d3d_spconv_mm_run(d3d_spconv_mm_t handle, int dtype, const void* in_feats, int64_t max_num_act_in,

@@ -32,6 +32,8 @@ def main():
     ap.add_argument("--index-reps", type=int, default=0, help="also time the rulebook + table build this many times")
     ap.add_argument("--plan", type=int, nargs=3, default=None, metavar=("GROUP", "STAGES", "PRODUCER_WARPS"),
                     help="override the tensor-core kernel's pipeline plan (0 = automatic)")
+    ap.add_argument("--regroup", action="store_true",
+                    help="run on the neighbour table with its outputs grouped by offset mask (d3d_spconv_mm_regroup)")
     ap.add_argument("--lib", default=None, metavar="NAME",
                     help="load the tuning build libs/libdeploy3d_b200_NAME.so (python -m deploy3d_b200.build --tuning NAME ...)")
     ap.add_argument("--role-cycles", action="store_true",
@@ -60,6 +62,15 @@ def main():
     num_out = num_in if subm else outs[3]
     m = int(num_out.item())
     table = SPConvMMPlugin.prepare(27, False, max_out, outs[0], outs[1], mirror=subm)
+    blocks_plain = None
+    if args.regroup:
+        tiles = (max_out + 127) // 128
+        mask_off = (27 * tiles * 128 * 4 + 255) // 256 * 256
+        count = lambda t: int(sum(bin(int(v) & 0xFFFFFFFF).count("1")
+                                  for v in t[mask_off:mask_off + 4 * tiles].view(torch.int32).cpu().numpy()))
+        blocks_plain = count(table)
+        table = SPConvMMPlugin.regroup(27, max_out, table)
+        blocks_grouped = count(table)
     pairs = int((outs[0][2, :int(outs[1].item())] >= 0).sum().item())
     tdt = torch.float16 if args.dtype == "fp16" else torch.bfloat16
     w = synth.kaiming_weight(rng, 27, args.cin, args.cout)
@@ -83,6 +94,8 @@ def main():
            "us_per_launch": sec * 1e6, "tflops_dense": 2.0 * m * 27 * args.cin * args.cout / sec / 1e12,
            "tflops_pair": 2.0 * pairs * args.cin * args.cout / sec / 1e12,
            "neighbours_per_output": pairs / max(m, 1)}
+    if blocks_plain is not None:
+        res["tile_offset_blocks"] = {"plain": blocks_plain, "regrouped": blocks_grouped}
     if args.role_cycles:
         import ctypes
         from deploy3d_b200 import _lib

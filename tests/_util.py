@@ -53,30 +53,63 @@ def pairs_equal(a, b, kvol):
 
 
 def table_parts(table, kvol, max_num_act_out):
-    """The three parts of SPConvMM's neighbour table (a uint8 tensor): ids int32 [tiles, kvol, 128], offset masks
-    int32 [tiles], row masks int32 [tiles, kvol, 4]; every part starts on a multiple of 256 bytes."""
+    """The four parts of SPConvMM's neighbour table (a uint8 tensor): ids int32 [tiles, kvol, 128], offset masks
+    int32 [tiles], row masks int32 [tiles, kvol, 4], output row of every tile row int32 [tiles, 128]; every part
+    starts on a multiple of 256 bytes."""
     import torch
     tiles = (max_num_act_out + 127) // 128
     up = lambda v: (v + 255) // 256 * 256
-    ids_bytes, mask_bytes = kvol * tiles * 128 * 4, tiles * 4
+    ids_bytes, mask_bytes, rows_bytes = kvol * tiles * 128 * 4, tiles * 4, tiles * kvol * 16
     mask_off = up(ids_bytes)
     rows_off = mask_off + up(mask_bytes)
+    perm_off = rows_off + up(rows_bytes)
     ids = table[:ids_bytes].view(torch.int32).view(tiles, kvol, 128)
     mask = table[mask_off:mask_off + mask_bytes].view(torch.int32)
-    rows = table[rows_off:rows_off + tiles * kvol * 16].view(torch.int32).view(tiles, kvol, 4)
-    return ids, mask, rows
+    rows = table[rows_off:rows_off + rows_bytes].view(torch.int32).view(tiles, kvol, 4)
+    perm = table[perm_off:perm_off + tiles * 128 * 4].view(torch.int32).view(tiles, 128)
+    return ids, mask, rows, perm
 
 
-def assert_table_consistent(ids, mask, rows):
-    """Row masks and offset masks say exactly what the ids say: bit r of word q <=> ids[.., 32 q + r] >= 0."""
+def table_row_bits(rows):
+    """Row masks [tiles, kvol, 4] -> bool [tiles, kvol, 128]."""
+    import torch
+    tiles, kvol, _ = rows.shape
+    bit = (rows.long().view(tiles, kvol, 4, 1) >> torch.arange(32, device=rows.device).view(1, 1, 1, 32)) & 1
+    return bit.view(tiles, kvol, 128).bool()
+
+
+def assert_tables_equal(a, b, what=""):
+    """Same offset masks, row masks and output map; same ids wherever a row-mask bit is set (the others are
+    unspecified)."""
+    import torch
+    (ids_a, mask_a, rows_a, perm_a), (ids_b, mask_b, rows_b, perm_b) = a, b
+    assert torch.equal(mask_a, mask_b), what + ": offset masks differ"
+    assert torch.equal(rows_a, rows_b), what + ": row masks differ"
+    assert torch.equal(perm_a, perm_b), what + ": output maps differ"
+    bits = table_row_bits(rows_a)
+    assert torch.equal(ids_a[bits], ids_b[bits]), what + ": ids differ"
+
+
+def assert_table_consistent(ids, mask, rows, perm=None):
+    """Offset masks say what the row masks say, ids under a set bit are row indices, and a plain table maps tile row
+    p to output p."""
     import torch
     tiles, kvol, _ = ids.shape
-    have = (ids >= 0).view(tiles, kvol, 4, 32).long()
-    weights = (1 << torch.arange(32, device=ids.device, dtype=torch.int64))
-    want_rows = (have * weights).sum(-1)
-    got_rows = rows.long() & 0xFFFFFFFF
-    assert torch.equal(got_rows, want_rows), "row masks disagree with the ids"
+    bits = table_row_bits(rows)
+    assert (ids[bits] >= 0).all(), "an id under a set row-mask bit is negative"
     if kvol <= 32:
-        any_k = (want_rows != 0).any(-1).long()
+        any_k = bits.any(-1).long()
         want_mask = (any_k * (1 << torch.arange(kvol, device=ids.device, dtype=torch.int64))).sum(-1)
-        assert torch.equal(mask.long() & 0xFFFFFFFF, want_mask), "offset masks disagree with the ids"
+        assert torch.equal(mask.long() & 0xFFFFFFFF, want_mask), "offset masks disagree with the row masks"
+
+
+def table_pairs(parts):
+    """The set of (output row, offset, input row) a table encodes, as a sorted int64 [n, 3] tensor."""
+    import torch
+    ids, mask, rows, perm = parts
+    bits = table_row_bits(rows)
+    t, k, r = bits.nonzero(as_tuple=True)
+    out = perm[t, r].long()
+    trip = torch.stack([out, k, ids[t, k, r].long()], 1)
+    key = (trip[:, 0] * 64 + trip[:, 1]) * (1 << 32) + trip[:, 2]
+    return trip[torch.argsort(key)]

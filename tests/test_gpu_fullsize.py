@@ -137,7 +137,8 @@ def test_every_layer_matches_reference_gpu(d3d, ref, pipe):
         # the reference's add / ReLU are half-precision graph ops: their result is rounded to fp16 like the product's
         want = finish(ref.spconv_mm(x, w_t, b_t, rb.index, rb.num_index, inverse, cap))[:m].half().float()
         exact = finish(_exact_layer(x, w_t, b_t, rb.index, rb.num_index, inverse, cap))[:m]
-        got = plug.run(x, net.sets[out_set]["num"], table, out=out_buf, relu=lay.relu, residual=res)
+        got = plug.run(x, net.sets[out_set]["num"], table, out=out_buf, relu=lay.relu, residual=res,
+                       regrouped=rb.regroup)
         torch.cuda.synchronize()
         g = got[:m].float()
         rms = float(torch.sqrt((exact ** 2).mean())) + 1e-30

@@ -104,3 +104,59 @@ def test_segmentation_frame_matches_cpu_pipeline(d3d, net):
     torch.cuda.synchronize()
     assert np.array_equal(pipe.logits.cpu().numpy(), got), "graph replay differs from the eager frame"
     assert np.array_equal(pipe.labels.cpu().numpy(), got.argmax(1))
+
+
+def test_regrouped_tables_leave_the_frames_unchanged(d3d):
+    """Both pipelines with every neighbour table regrouped by offset mask (d3d_spconv_mm_regroup between the table
+    build and the layers, the packed stage walk in the kernel): the detection frame's sparse features, BEV map and
+    NMS scores and the segmentation frame's logits are the bytes the plain tables give, eagerly and from the graph,
+    and the regrouped tables have fewer (tile, offset) blocks."""
+    from deploy3d_b200 import synth
+    from deploy3d_b200.pipeline import DetectionPipeline, SegmentationPipeline
+    from tests._util import table_parts
+    frame = synth.config4_points()
+    pts = _sector(frame, 12)
+    cfg = frame["voxel_config"]
+    pts = pts[synth.drop_edge_points(pts[:, :3], cfg[:3], cfg[3:])]
+    n = len(pts)
+    boxes = synth.config4_boxes(3, 300)
+    sub = dict(points=pts, batch=np.zeros(n, np.int32))
+    caps = {"in": n, "down2": 8 * n, "down3": 8 * n, "down4": 8 * n, "out": 8 * n}
+    outs = {}
+    for regroup in (False, True):
+        pipe = DetectionPipeline("centerpoint", "cuda:0", n_class=3, topk=300, n_pts=n, caps=caps, regroup=regroup)
+        pipe.load_frame(sub, boxes)
+        feats, coors, num = pipe.enqueue()
+        torch.cuda.synchronize()
+        eager = [t.clone() for t in (feats, coors, num, pipe.bev, pipe.nms_scores)]
+        pipe.capture()
+        pipe.bev.zero_()
+        pipe.replay()
+        torch.cuda.synchronize()
+        for a, b in zip(eager, (feats, coors, num, pipe.bev, pipe.nms_scores)):
+            assert torch.equal(a, b), "graph replay differs from the eager frame (regroup=%s)" % regroup
+        blocks = 0
+        for rb in pipe.net.rulebooks.values():
+            cap = pipe.net.sets[rb.out_set]["cap"]
+            mask = table_parts(rb.table_fwd, rb.kvol, cap)[1]
+            blocks += int(sum(bin(int(v) & 0xFFFFFFFF).count("1") for v in mask.cpu().numpy()))
+        outs[regroup] = (eager, blocks)
+        del pipe
+    for a, b in zip(outs[False][0], outs[True][0]):
+        assert torch.equal(a, b), "regrouped tables change the detection frame"
+    assert outs[True][1] < outs[False][1], (outs[True][1], outs[False][1])
+
+    frame5 = synth.config5_points()
+    pts5 = _sector(frame5, 16)[:20000]
+    batch5 = np.zeros(len(pts5), np.int32)
+    logits = {}
+    for regroup in (False, True):
+        probe = SegmentationPipeline("cuda:0", n_pts=len(pts5))
+        caps5 = {k: (len(pts5) if k == "in" else 4 * len(pts5)) for k in probe.set_names}
+        del probe
+        pipe = SegmentationPipeline("cuda:0", n_pts=len(pts5), caps=caps5, regroup=regroup)
+        pipe.load_frame(dict(points=pts5, batch=batch5))
+        logits[regroup] = pipe.enqueue().clone()
+        torch.cuda.synchronize()
+        del pipe
+    assert torch.equal(logits[False], logits[True]), "regrouped tables change the segmentation logits"

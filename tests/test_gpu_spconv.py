@@ -8,8 +8,8 @@ import numpy as np
 import pytest
 import torch
 
-from tests._util import (assert_feats_close, assert_table_consistent, pairs_equal, rng, round_to, table_parts,
-                         unique_coors)
+from tests._util import (assert_feats_close, assert_table_consistent, assert_tables_equal, pairs_equal, rng,
+                         round_to, table_parts, unique_coors)
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -302,8 +302,7 @@ def test_extended_enqueue_same_index_and_table(d3d, ks, dil):
         assert torch.equal(index, want[0]), "call %d: index differs from the plain entry point's" % call
         ref_table = SPConvMMPlugin.prepare(kvol, False, cap, want[0], want[1])
         got_parts, want_parts = table_parts(table, kvol, cap), table_parts(ref_table, kvol, cap)
-        for part, a, b in zip(("ids", "offset masks", "row masks"), got_parts, want_parts):
-            assert torch.equal(a, b), "call %d: %s differ from the prepared table's" % (call, part)
+        assert_tables_equal(got_parts, want_parts, "call %d, probe kernel's table vs the prepared one" % call)
         assert_table_consistent(*got_parts)
 
 

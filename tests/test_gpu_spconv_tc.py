@@ -7,7 +7,8 @@ import numpy as np
 import pytest
 import torch
 
-from tests._util import assert_feats_close, assert_table_consistent, rng, round_to, table_parts, unique_coors
+from tests._util import (assert_feats_close, assert_table_consistent, assert_tables_equal, rng, round_to, table_pairs,
+                         table_parts, table_row_bits, unique_coors)
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
@@ -131,12 +132,62 @@ def test_mirror_table_build_gives_the_same_table(d3d, ks, dil):
     kvol = int(np.prod(ks))
     plain = SPConvMMPlugin.prepare(kvol, False, 3000, outs[0], outs[1])
     mirrored = SPConvMMPlugin.prepare(kvol, False, 3000, outs[0], outs[1], mirror=True)
-    (ids_a, mask_a, rows_a), (ids_b, mask_b, rows_b) = table_parts(plain, kvol, 3000), table_parts(mirrored, kvol, 3000)
-    assert (ids_a == ids_b).all()
-    assert (ids_a >= 0).sum() == (outs[0][2, :int(outs[1].item())] >= 0).sum()
-    assert (mask_a == mask_b).all() and (mask_a != 0).any()
-    assert (rows_a == rows_b).all()
-    assert_table_consistent(ids_a, mask_a, rows_a)
+    a, b = table_parts(plain, kvol, 3000), table_parts(mirrored, kvol, 3000)
+    assert_tables_equal(a, b, "mirrored build vs generic scatter")
+    assert_table_consistent(*a)
+    assert int(table_row_bits(a[2]).sum()) == int((outs[0][2, :int(outs[1].item())] >= 0).sum())
+    assert (a[1] != 0).any()
+
+
+@pytest.mark.parametrize("case", ["subm", "strided", "inverse", "subm_313"])
+def test_regrouped_table_same_pairs_same_bytes(d3d, orc, case):
+    """d3d_spconv_mm_regroup: the regrouped table encodes exactly the (output, offset, input) triples of the plain
+    one, its output map is a permutation, it has fewer (tile, offset) blocks on a LiDAR-like scene, and the
+    convolution through it gives the same bytes as through the plain table (tensor-core and SIMT kernels, with
+    residual and ReLU)."""
+    from deploy3d_b200 import synth
+    from deploy3d_b200.plugins import SPConvMMPlugin, deserialize_plugin
+    r = rng(77)
+    shape = [1, 21, 200, 200]
+    vox = synth.lidar_like_voxels(r, 30000, tuple(shape[1:]))
+    coors = np.concatenate([np.zeros((len(vox), 1), np.int32), vox], 1)
+    n = len(coors)
+    ks = (3, 1, 3) if case == "subm_313" else (3, 3, 3)
+    subm = case.startswith("subm")
+    st = (1, 1, 1) if subm else (2, 2, 2)
+    pad = tuple(k // 2 for k in ks) if subm else (1, 1, 1)
+    cap = n if subm else 4 * n
+    outs, num_in = _rulebook(d3d, coors, shape, ks, st, pad, subm, cap)
+    kvol = int(np.prod(ks))
+    inverse = case == "inverse"
+    m_max = n if (subm or inverse) else cap
+    num_out = num_in if (subm or inverse) else outs[3]
+    n_in_rows = cap if inverse else n
+    plain = SPConvMMPlugin.prepare(kvol, inverse, m_max, outs[0], outs[1])
+    grouped = SPConvMMPlugin.regroup(kvol, m_max, plain)
+    pp, gp = table_parts(plain, kvol, m_max), table_parts(grouped, kvol, m_max)
+    assert_table_consistent(*gp)
+    assert torch.equal(table_pairs(pp), table_pairs(gp)), "the regrouped table encodes other pairs"
+    perm = gp[3].flatten()
+    live = perm[perm >= 0]
+    assert live.numel() == m_max and torch.equal(torch.sort(live)[0], torch.arange(m_max, device=DEV, dtype=torch.int32))
+    blocks = lambda parts: int(sum(bin(int(v) & 0xFFFFFFFF).count("1") for v in parts[1].cpu().numpy()))
+    assert blocks(gp) < blocks(pp), (blocks(gp), blocks(pp))
+    again = SPConvMMPlugin.regroup(kvol, m_max, plain)
+    assert torch.equal(again, grouped) or all(torch.equal(x, y) for x, y in zip(table_parts(again, kvol, m_max)[1:], gp[1:]))
+    cin, cout = 32, 64
+    w = (r.standard_normal((kvol, cin, cout)) * np.sqrt(2.0 / (kvol * cin))).astype(np.float32)
+    b = r.standard_normal(cout).astype(np.float32)
+    x = torch.randn((n_in_rows, cin), device=DEV).half()
+    res = torch.randn((m_max, cout), device=DEV).half()
+    for which in (2, 3, 1):
+        plug = deserialize_plugin("SPConvMM", d3d.data_s_spconv_mm(ks, cin, cout, m_max, subm, inverse, w, b))
+        plug.configure(torch.float16)
+        plug.set_kernel(which)
+        y_plain = plug.run(x, num_out, plain, relu=True, residual=res).clone()
+        y_grouped = plug.run(x, num_out, grouped, relu=True, residual=res)
+        assert _kernel_error() == 0
+        assert torch.equal(y_plain, y_grouped), "kernel choice %d: regrouped table changes the result" % which
 
 
 def test_dependent_launch_is_bit_identical(d3d):
