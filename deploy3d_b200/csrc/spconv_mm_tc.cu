@@ -45,6 +45,11 @@
 //   1 MMA warp         waits for a stage, one elected lane issues its tcgen05.mma and commits; owns the TMEM allocation
 //   1 control warp     one lane loads B by TMA (all offsets once when they fit, else per stage)
 //   4 epilogue warps   TMEM -> registers -> global, then zeros -> TMEM
+// A tile row need not stand for output tile * 128 + row: the table carries the output row of every tile row, and a
+// table rebuilt by d3d_spconv_mm_regroup lists its outputs sorted by offset mask, so that a tile keeps only the few
+// offsets its like outputs share.  For such tables the kernel is instantiated with a second stage walk (kPacked: a
+// stage takes the next offsets that are present instead of a fixed window of offsets) and a tile order that hands
+// every CTA a like share of the costly tiles.
 // Every role derives the stage sequence of a tile from the tile's offset mask (built with the neighbour table), so
 // no per-stage metadata is exchanged.  Stages and accumulators are handed over through mbarriers; every wait is
 // bounded (about one second) and on expiry raises an error word, lets the CTA drain and return instead of spinning.
@@ -731,23 +736,20 @@ __device__ __forceinline__ void mma_role(const TcParams& p, const Smem& s, uint3
     tc_fence_after();
     PROF(4);
     const uint32_t d_addr = tmem_base + (uint32_t)(acc * p.cout);
-    int base = 0;
-    for (uint32_t rest = mask; rest != 0u;) {
+    // windows: for (base = 0; base < kvol; base += kGroup) over the windows that have an offset; packed stages:
+    // while offsets are left, the kGroup lowest of them
+    uint32_t rest = mask;
+    for (int base = 0; kPacked ? rest != 0u : base < p.kvol; base += kPacked ? 0 : kGroup) {
       uint32_t bits;  // the offsets of the tile's next stage
       if (kPacked) {
         bits = lowest_bits<kGroup>(rest);
         rest &= ~bits;
       } else {
-        bits = (rest >> base) & ((1u << kGroup) - 1u);
-        rest &= ~(bits << base);
-        if (bits == 0u) {
-          base += kGroup;
-          continue;
-        }
+        bits = (mask >> base) & ((1u << kGroup) - 1u);
+        if (bits == 0u) continue;
       }
       int k[kGroup];
       const uint32_t used = slot_offsets<kGroup, kPacked>(bits, base, k);
-      if (!kPacked) base += kGroup;
       for (int part = 0; part < kparts; ++part) {
         // the full barrier guards shared memory only: no tcgen05 fence is needed, but the rows written by
         // cp.async (generic proxy) must be made visible to the tensor core's reads (async proxy)

@@ -69,8 +69,18 @@ def main():
         count = lambda t: int(sum(bin(int(v) & 0xFFFFFFFF).count("1")
                                   for v in t[mask_off:mask_off + 4 * tiles].view(torch.int32).cpu().numpy()))
         blocks_plain = count(table)
-        table = SPConvMMPlugin.regroup(27, max_out, table)
+        plain = table
+        table = SPConvMMPlugin.regroup(27, max_out, plain)
         blocks_grouped = count(table)
+        scratch = torch.empty(max(SPConvMMPlugin.regroup_scratch_bytes(27, max_out), 16), dtype=torch.uint8, device=dev)
+        torch.cuda.synchronize()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(10):
+            SPConvMMPlugin.regroup(27, max_out, plain, table, scratch)
+        t1.record()
+        torch.cuda.synchronize()
+        regroup_us = t0.elapsed_time(t1) * 100.0
     pairs = int((outs[0][2, :int(outs[1].item())] >= 0).sum().item())
     tdt = torch.float16 if args.dtype == "fp16" else torch.bfloat16
     w = synth.kaiming_weight(rng, 27, args.cin, args.cout)
@@ -96,6 +106,7 @@ def main():
            "neighbours_per_output": pairs / max(m, 1)}
     if blocks_plain is not None:
         res["tile_offset_blocks"] = {"plain": blocks_plain, "regrouped": blocks_grouped}
+        res["regroup_us"] = regroup_us
     if args.role_cycles:
         import ctypes
         from deploy3d_b200 import _lib
