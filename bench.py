@@ -699,7 +699,7 @@ def aggregate_frames_per_second(world, steps, frames_per_step, elapsed_max):
 
 def count_launches(pipe, kind="detection"):
     """Kernels of this library launched per frame, counted from the pipeline's plan (every enqueue is a fixed launch
-    list; `profiles/bench_config4_launch_list.md` shows the same 105 launches per config-4 frame)."""
+    list: 105 launches per config-4 frame, as a profiler's launch list of this script shows)."""
     net = pipe.net
     n = 0
     for rb in net.rulebooks.values():

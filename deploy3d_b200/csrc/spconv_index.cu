@@ -614,19 +614,29 @@ __global__ void segment_scan_kernel(int32_t* __restrict__ block_counts, int nblk
   int n = live_count(num_act_in, n_max);
   int live_blk = (n + kIdxThreads - 1) / kIdxThreads;
   int warp = threadIdx.x >> 5, lane = lane_id();
+  constexpr int kBatch = 8;  // 32-count groups loaded together: the loop is bound by the latency of its loads
   for (int k = warp; k < kvol; k += blockDim.x >> 5) {
     int carry = 0;
-    for (int base = 0; base < live_blk; base += 32) {
-      int j = base + lane;
-      int v = j < live_blk ? block_counts[(int64_t)k * nblk + j] : 0;
-      int inc = v;
+    int32_t* row = block_counts + (int64_t)k * nblk;
+    for (int base = 0; base < live_blk; base += 32 * kBatch) {
+      int v[kBatch];
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        int t = __shfl_up_sync(0xffffffffu, inc, d);
-        if (lane >= d) inc += t;
+      for (int u = 0; u < kBatch; ++u) {
+        const int j = base + u * 32 + lane;
+        v[u] = j < live_blk ? row[j] : 0;
       }
-      if (j < live_blk) block_counts[(int64_t)k * nblk + j] = carry + inc - v;
-      carry += __shfl_sync(0xffffffffu, inc, 31);
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int j = base + u * 32 + lane;
+        int inc = v[u];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          int t = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += t;
+        }
+        if (j < live_blk) row[j] = carry + inc - v[u];
+        carry += __shfl_sync(0xffffffffu, inc, 31);
+      }
     }
     if (lane == 0) counts[k] = carry;
   }

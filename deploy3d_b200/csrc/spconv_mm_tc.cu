@@ -15,9 +15,10 @@
 //
 // The A rows are gathered with 16-byte cp.async written straight into the swizzled layout.  A TMA tile::gather4
 // producer was measured on B200 at 11.4 ns per gathered row whatever the row width (a request-rate limit), three
-// times slower than cp.async for these row sizes (profiles/gather_rows_cp_async_vs_tma_gather4.md), and is not used.
+// times slower than cp.async for these row sizes (microbench/gather_rows.cu measures both), and is not used.
 //
-// What bounds this kernel, measured on B200 (profiles/spconv_mm_tc_role_cycles.md):
+// What bounds this kernel, measured on B200 (tuning builds with D3D_TC_PROFILE / D3D_TC_NO_MMA / D3D_TC_NO_COPY below,
+// microbench/mma_issue.cu):
 //   * the instruction streams of its roles.  With every MMA and every gather copy predicated off the layers still
 //     take 56-88 % of their time.  One warp that waits for a stage, fences and issues eight M128 K16 MMAs needs about
 //     750 cycles for what the tensor core executes in 320 to 512; two such warps on one SM keep it busy.  A lone
