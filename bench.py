@@ -423,7 +423,7 @@ def run_ours(args):
     f1.record()
     barrier()
     e2e_elapsed = f0.elapsed_time(f1) * 1e-3
-    # the results that came back are real: both slots ran the same candidate boxes (same NMS verdicts, some boxes
+    # the results that came back are real: both slots ran the same candidate boxes (same NMS decisions, some boxes
     # suppressed, some kept) and every voxel set of the last two frames is populated
     a, b = out_scores[0].numpy(), out_scores[1].numpy()
     if not ((a == b).all() and (a < 0).any() and (a > 0).any() and (out_counts[0][:len(count_tensors[0])] > 0).all()
