@@ -285,7 +285,7 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
         if (live) pair_out[(int64_t)(k + b) * n_max + i] = v[b];
         const unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
         if (lane_id() == 0 && hits) atomicAdd(&cnt[k + b], __popc(hits));
-        if (nbr_col) nbr_col[(g.kvol - 1 - (k + b)) * 128] = v[b];
+        if (nbr_col && v[b] >= 0) nbr_col[(g.kvol - 1 - (k + b)) * 128] = v[b];  // ids without a row-mask bit are never read
         if (rows_word && lane_id() == 0) rows_word[(g.kvol - 1 - (k + b)) * 4] = hits;
         if (nbr && lane_id() == 0 && hits) atomicOr(&tile_bits[my_tile], 1u << (g.kvol - 1 - (k + b)));
       }
@@ -316,7 +316,7 @@ subm_probe3_kernel(const unsigned long long* __restrict__ table, const int32_t* 
             if (live) pair_out[(int64_t)(k + b) * n_max + i] = v[b];
             const unsigned hits = __ballot_sync(0xffffffffu, v[b] >= 0);
             if (lane_id() == 0 && hits) atomicAdd(&cnt[k + b], __popc(hits));
-            if (nbr_col) nbr_col[(g.kvol - 1 - (k + b)) * 128] = v[b];
+            if (nbr_col && v[b] >= 0) nbr_col[(g.kvol - 1 - (k + b)) * 128] = v[b];  // ids without a row-mask bit are never read
             if (rows_word && lane_id() == 0) rows_word[(g.kvol - 1 - (k + b)) * 4] = hits;
             if (nbr && lane_id() == 0 && hits) atomicOr(&tile_bits[my_tile], 1u << (g.kvol - 1 - (k + b)));
           }
