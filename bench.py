@@ -281,6 +281,8 @@ def run_ours(args):
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the library has no CPU path")
     _lib.lib()  # fails loudly when the CUDA library is missing
+    if args.tc_plan:
+        _lib.check("d3d_debug_set_tc_plan", _lib.lib().d3d_debug_set_tc_plan(*args.tc_plan))
     torch.cuda.set_device(local)
     dev = "cuda:%d" % local
     dist = None
@@ -735,6 +737,8 @@ def main():
     ap.add_argument("--in-flight", type=int, default=2,
                     help="pipelines (buffers + CUDA graph + stream each) that take the frames in turn")
     ap.add_argument("--layers", action="store_true", help="print the per-layer SPConvMM table to stderr")
+    ap.add_argument("--tc-plan", type=int, nargs=3, default=None, metavar=("GROUP", "STAGES", "PRODUCER_WARPS"),
+                    help="override the tensor-core kernel's pipeline plan for every layer (0 = automatic)")
     ap.add_argument("--regroup", action="store_true",
                     help="rebuild every neighbour table with its outputs grouped by offset mask (d3d_spconv_mm_regroup): "
                          "fewer (tile, offset) blocks for the convolutions, three more kernels per rulebook")

@@ -961,7 +961,7 @@ const KernelEntry kKernels[] = {
     D3D_TC_K(2, 1, 8, 8, 2), D3D_TC_K(2, 1, 4, 8, 2), D3D_TC_K(2, 1, 2, 8, 2), D3D_TC_K(2, 1, 1, 8, 2),
     D3D_TC_K(4, 1, 4, 8, 2), D3D_TC_K(4, 1, 3, 8, 2), D3D_TC_K(4, 1, 2, 8, 2), D3D_TC_K(4, 1, 1, 8, 2),
     D3D_TC_K(8, 1, 2, 8, 2), D3D_TC_K(8, 1, 1, 8, 2),
-    D3D_TC_K(2, 1, 8, 4, 2), D3D_TC_K(4, 1, 3, 4, 2), D3D_TC_K(8, 1, 1, 4, 2),
+    D3D_TC_K(2, 1, 8, 4, 2), D3D_TC_K(4, 1, 3, 4, 2), D3D_TC_K(8, 1, 1, 4, 2), D3D_TC_K(8, 1, 2, 4, 2),
     D3D_TC_K(2, 1, 8, 8, 1), D3D_TC_K(2, 1, 4, 8, 1), D3D_TC_K(2, 1, 2, 8, 1), D3D_TC_K(2, 1, 1, 8, 1),
     D3D_TC_K(4, 1, 4, 8, 1), D3D_TC_K(4, 1, 3, 8, 1), D3D_TC_K(4, 1, 2, 8, 1), D3D_TC_K(4, 1, 1, 8, 1),
     D3D_TC_K(8, 1, 2, 8, 1), D3D_TC_K(8, 1, 1, 8, 1), D3D_TC_K(8, 2, 1, 8, 1),
