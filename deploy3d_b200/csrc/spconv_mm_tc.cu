@@ -20,7 +20,7 @@
 // What bounds this kernel, measured on B200 (tuning builds with D3D_TC_PROFILE / D3D_TC_NO_MMA / D3D_TC_NO_COPY below,
 // microbench/mma_issue.cu):
 //   * the instruction streams of its roles.  With every MMA and every gather copy predicated off the layers still
-//     take 56-88 % of their time.  One warp that waits for a stage, fences and issues eight M128 K16 MMAs needs about
+//     take 52-80 % of their time.  One warp that waits for a stage, fences and issues eight M128 K16 MMAs needs about
 //     750 cycles for what the tensor core executes in 320 to 512; two such warps on one SM keep it busy.  A lone
 //     warp issues a dependent instruction every four cycles or so, so what a role executes per stage besides its
 //     copies / MMAs (walking the stage sequence, waits, address arithmetic) costs as much as the work itself.
