@@ -398,9 +398,15 @@ template <int kGroup, bool kPacked> __device__ __forceinline__ bool next_stage(c
       }
       it.base = 0;
     }
-    it.tile = tile_at<kPacked>(p, ++it.round);
-    it.rest = it.mask_next;
-    it.mask_next = load_mask(p, tile_at<kPacked>(p, it.round + 1));
+    if (kPacked) {
+      it.tile = tile_at<true>(p, ++it.round);
+      it.rest = it.mask_next;
+      it.mask_next = load_mask(p, tile_at<true>(p, it.round + 1));
+    } else {  // front to back: the next tile is gridDim.x further
+      it.tile += gridDim.x;
+      it.rest = it.mask_next;
+      it.mask_next = load_mask(p, it.tile + (int)gridDim.x);
+    }
   }
 }
 
@@ -580,7 +586,8 @@ __device__ __forceinline__ void producer_role(const TcParams& p, const Smem& s, 
     if (have_next) load_ids(nxt, ids_next);
     // on entering a tile, pull the ids of the CTA's next tile towards the SM: they may come from DRAM, which takes
     // longer than the one stage the loads above run ahead
-    if (have_next && nxt.tile != cur.tile) prefetch_ids(tile_at<kPacked>(p, nxt.round + 1));
+    if (have_next && nxt.tile != cur.tile)
+      prefetch_ids(kPacked ? tile_at<true>(p, nxt.round + 1) : nxt.tile + (int)gridDim.x);
     PROF(1);
     if (!mbar_wait_warp(&sh->empty[stage], phase ^ 1, abort_flag, 12)) return false;
     PROF(2);
