@@ -70,6 +70,21 @@ __global__ void gather_rows_kernel(const V* __restrict__ in, const int32_t* __re
   out[t] = __ldg(in + (int64_t)v * groups + g);
 }
 
+// The same for half-precision features (the output of a convolution) gathered into half or float rows.
+template <class TIn, class TOut>
+__global__ void gather_rows_convert_kernel(const TIn* __restrict__ in, const int32_t* __restrict__ scatter_to, int64_t n,
+                                           int64_t c, int64_t m, int fill, float fill_val, TOut* __restrict__ out) {
+  int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n * c) return;
+  int64_t p = t / c, g = t % c;
+  int v = __ldg(scatter_to + p);
+  if (v < 0 || !D3D_BOUNDS_OK(v, 0, m, kSiteGatherBack) || v >= m) {
+    if (fill) out[t] = static_cast<TOut>(fill_val);
+    return;
+  }
+  out[t] = static_cast<TOut>(static_cast<float>(in[(int64_t)v * c + g]));
+}
+
 }  // namespace
 }  // namespace d3d
 
@@ -131,13 +146,31 @@ extern "C" int d3d_gather_back_enqueue(const d3d_gather_back_params* p, const d3
   D3D_NVTX_RANGE("d3d_gather_back_enqueue");
   (void)workspace, (void)workspace_bytes;
   D3D_REQUIRE(p && in && out && inputs && outputs && n_in >= 2 && n_out >= 1, D3D_ERR_INVALID_ARGUMENT);
-  D3D_REQUIRE(in[0].dtype == D3D_FLOAT, D3D_ERR_UNSUPPORTED_DTYPE);
+  // the reference takes float features (gather_back.cu:146-150); half / bf16 features -- what a half-precision
+  // network hands over -- are accepted as well and gathered into rows of the same type or widened to float
+  const int tin = in[0].dtype, tout = out[0].dtype;
+  D3D_REQUIRE(tin == D3D_FLOAT || tin == D3D_HALF || tin == D3D_BF16, D3D_ERR_UNSUPPORTED_DTYPE);
+  D3D_REQUIRE(tout == tin || (tout == D3D_FLOAT && tin != D3D_FLOAT), D3D_ERR_UNSUPPORTED_DTYPE);
   D3D_REQUIRE(in[0].nb_dims >= 1 && in[1].nb_dims == 1, D3D_ERR_INVALID_ARGUMENT);
   const int64_t m = in[0].dims[0], n = in[1].dims[0];
   int64_t c = 1;
   for (int d = 1; d < in[0].nb_dims; ++d) c *= in[0].dims[d];  // gather_back.cu:36: row width = stride(0)
   if (n == 0 || c == 0) return D3D_OK;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (tin != D3D_FLOAT) {
+    const unsigned grid = (unsigned)ceil_div(n * c, 256);
+    const int32_t* ids = reinterpret_cast<const int32_t*>(inputs[1]);
+#define D3D_GATHER_CASE(TI, TO)                                                                             \
+  gather_rows_convert_kernel<TI, TO><<<grid, 256, 0, st>>>(reinterpret_cast<const TI*>(inputs[0]), ids, n, c, m, \
+                                                         p->fill, p->fill_val, reinterpret_cast<TO*>(outputs[0]))
+    if (tin == D3D_HALF && tout == D3D_HALF) D3D_GATHER_CASE(__half, __half);
+    else if (tin == D3D_HALF) D3D_GATHER_CASE(__half, float);
+    else if (tout == D3D_BF16) D3D_GATHER_CASE(__nv_bfloat16, __nv_bfloat16);
+    else D3D_GATHER_CASE(__nv_bfloat16, float);
+#undef D3D_GATHER_CASE
+    D3D_CHECK_LAUNCH();
+    return D3D_OK;
+  }
   const float* feats = reinterpret_cast<const float*>(inputs[0]);
   const int32_t* idx = reinterpret_cast<const int32_t*>(inputs[1]);
   float* o = reinterpret_cast<float*>(outputs[0]);

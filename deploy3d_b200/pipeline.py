@@ -216,8 +216,7 @@ class SegmentationPipeline:
             self.vox_feats_lp = torch.zeros((cap, self.net.in_channels), dtype=dtype, device=dev)
             self.net.set_input(self.vox_coors, self.vox_num)
             self.gather = deserialize_plugin("GatherBack", data_s_gather_back(0.0))
-            # GatherBack is an fp32 operator (as in the reference): the network output is widened first
-            self.net_out_f32 = torch.zeros((cap, n_class), dtype=torch.float32, device=dev)
+            # GatherBack reads the half-precision network output and writes float logits
             self.logits = torch.zeros((self.n_pts, n_class), dtype=torch.float32, device=dev)
             self.labels = torch.zeros(self.n_pts, dtype=torch.int32, device=dev)
         self.graph = None
@@ -250,8 +249,7 @@ class SegmentationPipeline:
         self.scatter.enqueue(self.pts_feats, self.scatter_index, self.scatter_count, outputs=[self.vox_feats])
         self.vox_feats_lp[:, :self.c_pts + 5].copy_(self.vox_feats)
         feats, _, _ = self.net.forward(self.vox_feats_lp)
-        self.net_out_f32.copy_(feats)
-        self.gather.enqueue(self.net_out_f32, self.scatter_index, outputs=[self.logits])
+        self.gather.enqueue(feats, self.scatter_index, outputs=[self.logits])
         self.labels.copy_(torch.argmax(self.logits, dim=1))  # the label pass of the reference (test_cylinder3d.py:322)
         return self.logits
 

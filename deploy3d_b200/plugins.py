@@ -88,6 +88,9 @@ class _Plugin:
         if outputs is None:
             outputs = [torch.empty(tuple(d.dims[:d.nb_dims]), dtype=_D3D2TORCH[d.dtype], device=device)
                        for d in out_descs]
+        else:  # the caller's buffers say which of the accepted output types it wants (GatherBack can widen)
+            for d, t in zip(out_descs, outputs):
+                d.dtype = _TORCH2D3D[t.dtype]
         ws_bytes = self.workspace_size(in_descs)
         ws = self._get_workspace(ws_bytes, device)
         fn = getattr(lib(), self._prefix + "_enqueue")
@@ -337,7 +340,8 @@ class ScatterToPlugin(_PodPlugin):
 
 
 class GatherBackPlugin(_PodPlugin):
-    """``GatherBack`` (trt/point_voxel_mapping/gather_back.cu:77-184)."""
+    """``GatherBack`` (trt/point_voxel_mapping/gather_back.cu:77-184).  Besides the reference's float features it
+    takes half / bfloat16 ones and writes them as they are or, into a float `outputs` tensor, widened."""
     name = "GatherBack"
     _prefix = "d3d_gather_back"
     _params_t = _lib.GatherBackParams

@@ -333,6 +333,9 @@ int d3d_cylinder_encoder_enqueue(const d3d_voxel_encoder_params* p, const d3d_te
  * GatherBack data_s: bool fill; float fillVal.
  *   Inputs : 0 reducedFeats float [M, ...], 1 scatterTo int32 [N]
  *   Output : 0 batchPointFeats float [N, ...]
+ *   Beyond the reference (float only, gather_back.cu:146-150): reducedFeats may be half / bf16, as a
+ *   half-precision network writes them; the output is then of the same type (what output_desc reports) or,
+ *   when the caller's output descriptor says float, widened while gathering.
  * ------------------------------------------------------------------------------------------- */
 typedef struct {
   int32_t reduce_type;

@@ -158,6 +158,29 @@ def test_gather_back(d3d, orc, feat_shape, fill_val):
     assert (out == want).all()
 
 
+@pytest.mark.parametrize("in_dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("widen", [True, False])
+@pytest.mark.parametrize("fill_val", [None, 6.5])
+def test_gather_back_half_precision_features(d3d, orc, in_dtype, widen, fill_val):
+    """Half-precision features (an extension: the reference's GatherBack is float only, gather_back.cu:146-150) are
+    gathered exactly, into rows of the same type or widened into a float output; the float oracle on the rounded
+    features is the expected result either way.  A float output for float input stays the only other combination."""
+    r = rng(61)
+    n, m, c = 70001, 20000, 20
+    idx = r.integers(-1, m, n).astype(np.int32)
+    x = torch.from_numpy(r.standard_normal((m, c)).astype(np.float32)).to(in_dtype)
+    out_dtype = torch.float32 if widen else in_dtype
+    init = torch.full((n, c), 3.25, dtype=out_dtype, device=DEV)
+    from deploy3d_b200.ops import data_s_gather_back
+    from deploy3d_b200.plugins import deserialize_plugin
+    plug = deserialize_plugin("GatherBack", data_s_gather_back(fill_val))
+    out, = plug.enqueue(x.to(DEV), _t(idx), outputs=[init])
+    want = orc.gather_back(x.float().numpy(), idx, fill_val, out_init=np.full((n, c), 3.25, np.float32))
+    assert out.dtype == out_dtype and (out.float().cpu().numpy() == want).all()
+    with pytest.raises(RuntimeError):  # float features never narrow
+        plug.enqueue(x.float().to(DEV), _t(idx), outputs=[torch.zeros((n, c), dtype=torch.float16, device=DEV)])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("num_act", [10000, 100, 0])
 def test_bev_densify(d3d, orc, dtype, num_act):
