@@ -219,6 +219,8 @@ enum BoundsSite {
   kSiteBevCoord = 4,    // BEVDensify: voxel coordinate outside the dense grid
   kSiteScatterTo = 5,   // ScatterTo: voxel id >= number of voxels
   kSiteGatherBack = 6,  // GatherBack: voxel id >= number of voxels
+  kSiteMirror = 7,      // neighbour table build with the mirror hint: a centre-offset entry that does not map a row to
+                        // itself (duplicate input coordinates: the rulebook is not mirror-symmetric)
 };
 #ifdef DEPLOY3D_BOUNDS_CHECK
 extern __device__ int g_d3d_bounds[4];  // violations seen; site, value and limit of the first

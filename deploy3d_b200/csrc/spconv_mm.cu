@@ -76,6 +76,8 @@ __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t 
       // kvol - 1 - k.  Reading every entry as its mirror image makes the table writes follow the ascending gather
       // index of the segment: neighbouring lanes then hit the same few table rows instead of scattered ones.
       if (mirror && k[u] >= 0 && k[u] < kvol) {
+        // checked build: the hint holds only if every row is its own centre neighbour
+        if (k[u] * 2 + 1 == kvol) (void)D3D_BOUNDS_OK(g[u], s[u], (long long)s[u] + 1, kSiteMirror);
         const int t = g[u];
         g[u] = s[u], s[u] = t, k[u] = kvol - 1 - k[u];
       }

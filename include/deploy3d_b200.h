@@ -77,8 +77,10 @@ int d3d_debug_take_kernel_error(int* code);
  * row id, table entry and coordinate its kernels index with, skips an access that is out of range and records it:
  * this call synchronises the device, copies {violations seen, site, value, limit of the first} to record[0..3] and
  * clears them.  Sites: 1 / 2 neighbour id in SPConvMM (tensor-core / SIMT kernel), 3 rulebook entry while the
- * neighbour table is built, 4 BEVDensify coordinate, 5 ScatterTo id, 6 GatherBack id.  The regular build checks
- * nothing of the kind and returns D3D_ERR_INVALID_ARGUMENT. */
+ * neighbour table is built, 4 BEVDensify coordinate, 5 ScatterTo id, 6 GatherBack id, 7 a centre-offset rulebook
+ * entry that does not map a row to itself although d3d_spconv_mm_prepare was given the mirror hint (value = gather
+ * index, limit = scatter index + 1).  The regular build checks nothing of the kind and returns
+ * D3D_ERR_INVALID_ARGUMENT. */
 int d3d_debug_take_bounds_violation(int32_t* record);
 /* Tuning aid (no reference counterpart): overrides the pipeline plan of the tensor-core SPConvMM kernel for every
  * later launch of the process: kernel offsets per pipeline stage, maximum number of stages, producer warps (4 or 8);
@@ -218,7 +220,8 @@ int d3d_spconv_mm_enqueue(d3d_spconv_mm_t handle, const d3d_tensor_desc* in, int
  * reference's test checks, tests/spconv/test_spconv.py:101-108); the table is then written in gather order, which
  * is faster.  The result is the same table.  Precondition the library does not verify: the input coordinates are
  * unique and inside the grid (with duplicates the rulebook is not symmetric and the mirrored build writes a wrong
- * table).  The plugin-level d3d_spconv_mm_enqueue never sets bit 1. */
+ * table; the checked build records it, site 7 of d3d_debug_take_bounds_violation).  The plugin-level
+ * d3d_spconv_mm_enqueue never sets bit 1. */
 size_t d3d_spconv_mm_table_bytes(int kernel_vol, int64_t max_num_act_out);
 /* Optional step between prepare and run (no reference counterpart): rebuilds a neighbour table with its outputs
  * grouped by offset mask.  The convolution kernel works on tiles of 128 outputs and spends a pipeline slot, a weight

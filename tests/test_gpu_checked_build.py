@@ -88,6 +88,16 @@ CHILD = textwrap.dedent("""
     bad[3, 2] = shape[1] + 5
     ops.bev_densify(results[(True, 2)], bad, num, shp, 32 * shape[0])
     out["bev"] = take()
+    # the mirror hint on a rulebook of duplicated coordinates (not mirror-symmetric): recorded at the centre offset
+    dup = torch.cat([coors, coors[:40]])
+    nd = torch.tensor([n + 40], dtype=torch.int32, device=dev)
+    ip = deserialize_plugin("SPConvIdx3d", data_s_spconv_index((3, 3, 3), (1, 1, 1), (1, 1, 1), (1, 1, 1), (0, 0, 0),
+                                                                n + 40, True, False))
+    outs = ip.enqueue(dup, nd, shp)
+    SPConvMMPlugin.prepare(27, False, n + 40, outs[0], outs[1], mirror=False)
+    out["no_hint"] = take()
+    SPConvMMPlugin.prepare(27, False, n + 40, outs[0], outs[1], mirror=True)
+    out["mirror"] = take()
     print("RESULT " + json.dumps(out))
 """) % ROOT
 
@@ -102,10 +112,12 @@ def test_checked_build_records_and_skips(tmp_path):
     assert run.returncode == 0, run.stderr[-3000:]
     got = json.loads([ln for ln in run.stdout.splitlines() if ln.startswith("RESULT ")][-1][7:])
     assert got["clean"] == [0, 0, 0, 0], "valid inputs must leave no record: %s" % got["clean"]
-    # {violations, site, value, limit}: sites 1 / 2 = SPConvMM tensor-core / SIMT kernel, 5 ScatterTo, 6 GatherBack, 4 BEV
+    # {violations, site, value, limit}: sites 1 / 2 = SPConvMM tensor-core / SIMT kernel, 5 ScatterTo, 6 GatherBack, 4 BEV, 7 mirror hint
     for key, site in (("tc", 1), ("simt", 2)):
         count, where, value, limit = got[key]
         assert count > 0 and where == site and value >= limit > 0, (key, got[key])
     assert got["scatter_to"][1:] == [5, 60, 50] and got["scatter_to"][0] >= 1  # one thread per (point, channel group)
     assert got["gather_back"][1:] == [6, 60, 50] and got["gather_back"][0] >= 1
     assert got["bev"][0] == 1 and got["bev"][1] == 4
+    assert got["no_hint"] == [0, 0, 0, 0]
+    assert got["mirror"][0] == 40 and got["mirror"][1] == 7  # site 7: a row that is not its own centre neighbour
