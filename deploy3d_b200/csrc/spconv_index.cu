@@ -102,7 +102,8 @@ __device__ __forceinline__ int live_count(const int32_t* num_act_in, int64_t n_m
 
 // ---------------------------------------------------------------------------------------------
 __global__ void reset_table_kernel(unsigned long long* table, const int32_t* num_act_in, int64_t n_max, int fan,
-                                   uint32_t cap_max) {
+                                   uint32_t cap_max, int32_t* __restrict__ state) {
+  if (blockIdx.x == 0 && threadIdx.x == 0) state[2] = 0;  // the ticket of this call's segment_scan_kernel
   uint32_t cap = hash_capacity((long long)live_count(num_act_in, n_max) * fan, cap_max);
   ulonglong2* t2 = reinterpret_cast<ulonglong2*>(table);
   for (uint32_t s = blockIdx.x * blockDim.x + threadIdx.x; s < cap / 2; s += gridDim.x * blockDim.x)
@@ -600,61 +601,83 @@ conv_translate_packed_kernel(int32_t* __restrict__ pair_out, const int32_t* __re
   for (int t = threadIdx.x; t < kvol; t += kIdxThreads) block_counts[(int64_t)t * nblk + blockIdx.x] = cnt[t];
 }
 
-// Single CTA of 1024 threads.  Warp w scans the counts of offsets w, w+32, ..; then the segment starts
-// (each rounded up to 128, trt/spconv/index.cu:148-156) and numIndex (index.cu:139-144) are produced.
+// One CTA of 1024 threads per kernel offset: an exclusive scan of the offset's per-CTA counts, in place; the CTA that
+// finishes last (a ticket in `state[2]`, which reset_table_kernel zeroes at the start of every call) then produces
+// the segment starts (each rounded up to 128, trt/spconv/index.cu:148-156) and numIndex (index.cu:139-144).
 // seg[0..kvol] = start of each segment (seg[kvol] = numIndex), seg[kvol+1 .. 2*kvol] = pair count of each offset.
-// `state` (two words kept in the workspace between calls): [0] where the padding fill of this call ends, [1] the
+// `state` (words kept in the workspace between calls): [0] where the padding fill of this call ends, [1] the
 // num_index of this call.  A caller that owns the index buffer across calls (`persistent`) and did not pass
 // `first` gets only [num_index, previous num_index) refilled: everything beyond is still -1 from earlier calls.
-__global__ void segment_scan_kernel(int32_t* __restrict__ block_counts, int nblk, int kvol,
-                                    const int32_t* num_act_in, int64_t n_max, int32_t* __restrict__ seg,
-                                    int32_t* num_index, int32_t* __restrict__ state, int persistent, int first,
-                                    int64_t row_len) {
-  __shared__ int counts[kMaxKernelVol];
-  int n = live_count(num_act_in, n_max);
-  int live_blk = (n + kIdxThreads - 1) / kIdxThreads;
-  int warp = threadIdx.x >> 5, lane = lane_id();
-  constexpr int kBatch = 8;  // 32-count groups loaded together: the loop is bound by the latency of its loads
-  for (int k = warp; k < kvol; k += blockDim.x >> 5) {
-    int carry = 0;
-    int32_t* row = block_counts + (int64_t)k * nblk;
-    for (int base = 0; base < live_blk; base += 32 * kBatch) {
-      int v[kBatch];
+__global__ void __launch_bounds__(1024) segment_scan_kernel(int32_t* __restrict__ block_counts, int nblk, int kvol,
+                                                            const int32_t* num_act_in, int64_t n_max,
+                                                            int32_t* __restrict__ seg, int32_t* num_index,
+                                                            int32_t* __restrict__ state, int persistent, int first,
+                                                            int64_t row_len) {
+  __shared__ int warp_sum[32];
+  __shared__ int carry_s, chunk_total;
+  __shared__ bool last;
+  const int n = live_count(num_act_in, n_max);
+  const int live_blk = (n + kIdxThreads - 1) / kIdxThreads;
+  const int warp = threadIdx.x >> 5, lane = lane_id();
+  const int k = blockIdx.x;
+  int32_t* row = block_counts + (int64_t)k * nblk;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (int base = 0; base < live_blk; base += 1024) {  // 1024 counts at a time
+    const int j = base + (int)threadIdx.x;
+    const int v = j < live_blk ? row[j] : 0;
+    int inc = v;
 #pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const int j = base + u * 32 + lane;
-        v[u] = j < live_blk ? row[j] : 0;
-      }
-#pragma unroll
-      for (int u = 0; u < kBatch; ++u) {
-        const int j = base + u * 32 + lane;
-        int inc = v[u];
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) {
-          int t = __shfl_up_sync(0xffffffffu, inc, d);
-          if (lane >= d) inc += t;
-        }
-        if (j < live_blk) row[j] = carry + inc - v[u];
-        carry += __shfl_sync(0xffffffffu, inc, 31);
-      }
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += t;
     }
-    if (lane == 0) counts[k] = carry;
+    if (lane == 31) warp_sum[warp] = inc;
+    __syncthreads();
+    if (warp == 0) {
+      const int w = warp_sum[lane];
+      int winc = w;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xffffffffu, winc, d);
+        if (lane >= d) winc += t;
+      }
+      warp_sum[lane] = winc - w;  // exclusive over the warps
+      if (lane == 31) chunk_total = winc;
+    }
+    __syncthreads();
+    const int carry = carry_s;
+    if (j < live_blk) row[j] = carry + warp_sum[warp] + inc - v;
+    __syncthreads();  // everyone has read the carry and the warp offsets
+    if (threadIdx.x == 0) carry_s = carry + chunk_total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    seg[kvol + 1 + k] = carry_s;
+    __threadfence();
+    last = atomicAdd(&state[2], 1) == kvol - 1;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    int pos = 0;
-    for (int k = 0; k < kvol; ++k) {
-      seg[k] = pos;
-      seg[kvol + 1 + k] = counts[k];
-      pos += (counts[k] + kSegment - 1) / kSegment * kSegment;
-    }
-    seg[kvol] = pos;
-    *num_index = pos;
-    const int64_t prev = state[1];
-    const bool partial = persistent && !first && prev >= 0 && prev <= row_len;
-    state[0] = (int32_t)(partial ? (prev > pos ? prev : pos) : row_len);
-    state[1] = pos;
+  if (!last) return;
+  __threadfence();
+  // the other CTAs' totals: loaded side by side (one after the other they would cost a round trip to L2 each)
+  __shared__ int counts[kMaxKernelVol];
+  const volatile int32_t* totals = seg + kvol + 1;
+  for (int q = threadIdx.x; q < kvol; q += blockDim.x) counts[q] = totals[q];
+  __syncthreads();
+  if (threadIdx.x != 0) return;
+  int pos = 0;
+  for (int q = 0; q < kvol; ++q) {
+    seg[q] = pos;
+    pos += (counts[q] + kSegment - 1) / kSegment * kSegment;
   }
+  seg[kvol] = pos;
+  *num_index = pos;
+  const int64_t prev = state[1];
+  const bool partial = persistent && !first && prev >= 0 && prev <= row_len;
+  state[0] = (int32_t)(partial ? (prev > pos ? prev : pos) : row_len);
+  state[1] = pos;
+  state[2] = 0;
 }
 
 // Write the compacted (gatherIn, scatterOut, kernelOffset) triples (trt/spconv/index.cu:123-146).
@@ -851,7 +874,7 @@ struct Plan {
   int32_t* slot_out;
   int32_t* winners;
   uint32_t* win_bits;  // per input: which of its offsets won an output voxel (kvol <= 32)
-  int32_t* state;      // two words that survive between calls (see segment_scan_kernel)
+  int32_t* state;      // words that survive between calls, and the ticket of segment_scan_kernel
   bool packed;         // strided rulebook kept as kPackedSlots entries per input instead of kvol
   size_t bytes;
 };
@@ -917,7 +940,7 @@ int make_plan(const d3d_spconv_index_params* p, const d3d_tensor_desc* in, int n
   plan->packed = !p->subm && !g.transpose && ndim == 3 && g.ksize[0] <= 3 && g.ksize[1] <= 3 && g.ksize[2] <= 3 &&
                  fan <= kPackedSlots && g.kvol > kPackedSlots /* the pair table has kvol rows */ && plan->cap_max <= (1u << kPackedShift) &&
                  p->max_num_act_out <= (1 << kPackedShift);
-  plan->state = w.take<int32_t>(2);
+  plan->state = w.take<int32_t>(4);
   plan->bytes = w.off;
   return D3D_OK;
 }
@@ -1037,7 +1060,7 @@ extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, con
   D3D_REQUIRE(coors && num_act_in && index && num_index, D3D_ERR_INVALID_ARGUMENT);
   const int nblk = plan.nblk;
   reset_table_kernel<<<stream_grid(plan.cap_max / 2, 256), 256, 0, st>>>(plan.table, num_act_in, n_max, plan.fan,
-                                                                         plan.cap_max);
+                                                                         plan.cap_max, plan.state);
   if (p->subm) {
     subm_insert_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.table, coors, num_act_in, n_max, g, plan.cap_max, status);
     if (g.ndim == 3 && !g.transpose && g.stride[0] == 1 && g.stride[1] == 1 && g.stride[2] == 1) {
@@ -1096,7 +1119,7 @@ extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, con
       conv_translate_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.slot_out, num_act_in, n_max, g.kvol,
                                                               plan.block_counts, nblk);
   }
-  segment_scan_kernel<<<1, 1024, 0, st>>>(plan.block_counts, nblk, g.kvol, num_act_in, n_max, plan.seg, num_index,
+  segment_scan_kernel<<<g.kvol, 1024, 0, st>>>(plan.block_counts, nblk, g.kvol, num_act_in, n_max, plan.seg, num_index,
                                           plan.state, persistent, first, plan.row_len);
   if (!p->subm && plan.packed)
     compact_packed_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in, n_max,
