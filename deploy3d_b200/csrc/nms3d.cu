@@ -137,12 +137,13 @@ __device__ float clipped_area(const Box& A, const Box& B) {
   return (float)((double)area / 2.0);
 }
 
-// nms3d.cu:42-56: BEV IoU, z ignored.
-__device__ __forceinline__ bool overlaps(const Box& a, const Box& b, float thr) {
-  if (thr > 0.f) {
-    float dx = a.cx - b.cx, dy = a.cy - b.cy, r = a.rad + b.rad;
-    if (dx * dx + dy * dy > r * r * 1.0001f + 1e-6f) return false;  // disjoint: clipped area is exactly 0
-  }
+// nms3d.cu:42-56: BEV IoU, z ignored.  Two boxes whose bounding circles are disjoint cannot overlap (their clipped
+// area is exactly 0, and 0 >= thr fails for thr > 0): such pairs never reach the polygon clipping.
+__device__ __forceinline__ bool circles_touch(const Box& a, const Box& b) {
+  float dx = a.cx - b.cx, dy = a.cy - b.cy, r = a.rad + b.rad;
+  return !(dx * dx + dy * dy > r * r * 1.0001f + 1e-6f);
+}
+__device__ __forceinline__ bool iou_reaches(const Box& a, const Box& b, float thr) {
   float ov = clipped_area(a, b);
   return ov / fmaxf(a.area + b.area - ov, 1e-8f) >= thr;
 }
@@ -150,31 +151,62 @@ __device__ __forceinline__ bool overlaps(const Box& a, const Box& b, float thr) 
 constexpr int kNmsBlock = 64;
 
 // grid (col block, row block, batch); upper triangle only.  mask[b][row][col block] bit j = row suppresses col*64+j.
+// Two passes over the 64 x 64 pairs of a CTA: the bounding-circle test for every pair (cheap, uniform), then the
+// polygon clipping for the pairs that passed, dealt out evenly over the 256 threads -- taken pair by pair inside the
+// first loop, the few survivors would each hold up their whole warp.
 __global__ void __launch_bounds__(256)
 overlap_mask_kernel(const float* __restrict__ boxes, int k, int box_dim, float thr, int nw,
                     unsigned long long* __restrict__ mask) {
   const int cb = blockIdx.x, rb = blockIdx.y, b = blockIdx.z;
   if (rb > cb) return;
-  __shared__ Box cols[kNmsBlock];
-  __shared__ unsigned int part[kNmsBlock][8];
+  __shared__ Box cols[kNmsBlock], rows[kNmsBlock];
+  __shared__ unsigned int part[kNmsBlock][4];       // 16 columns per word
+  __shared__ unsigned short cand[kNmsBlock * kNmsBlock];  // row << 8 | column of a pair to clip
+  __shared__ int warp_base[9];
   const float* bx = boxes + (int64_t)b * k * box_dim;
   const int tid = threadIdx.x, r = tid & 63, quarter = tid >> 6;
   if (tid < kNmsBlock) {
     int c = cb * kNmsBlock + tid;
     if (c < k) cols[tid] = make_box(bx + (int64_t)c * box_dim);
+  } else if (tid < 2 * kNmsBlock) {
+    int rr = rb * kNmsBlock + tid - kNmsBlock;
+    if (rr < k) rows[tid - kNmsBlock] = make_box(bx + (int64_t)rr * box_dim);
   }
+  part[r][quarter] = 0u;
   __syncthreads();
   const int row = rb * kNmsBlock + r;
   const int ncol = min(k - cb * kNmsBlock, kNmsBlock);
-  unsigned int bits = 0;
+  unsigned int near = 0;  // bit j - 16 * quarter: column j passed the circle test
   if (row < k) {
-    Box me = make_box(bx + (int64_t)row * box_dim);
     int j0 = quarter * 16, j1 = min(j0 + 16, ncol);
     if (rb == cb) j0 = max(j0, r + 1);
     for (int j = j0; j < j1; ++j)
-      if (overlaps(me, cols[j], thr)) bits |= 1u << (j - quarter * 16);
+      if (thr <= 0.f || circles_touch(rows[r], cols[j])) near |= 1u << (j - quarter * 16);
   }
-  part[r][quarter] = bits;
+  // positions of this thread's pairs in the CTA's list: warp scan, then the eight warp totals
+  const int lane = tid & 31, warp = tid >> 5;
+  const int mine = __popc(near);
+  int inc = mine;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, d);
+    if (lane >= d) inc += t;
+  }
+  if (lane == 31) warp_base[warp + 1] = inc;
+  __syncthreads();
+  if (tid == 0) {
+    warp_base[0] = 0;
+    for (int w = 1; w <= 8; ++w) warp_base[w] += warp_base[w - 1];
+  }
+  __syncthreads();
+  int pos = warp_base[warp] + inc - mine;
+  for (unsigned int m = near; m; m &= m - 1) cand[pos++] = (unsigned short)((r << 8) | (quarter * 16 + __ffs(m) - 1));
+  __syncthreads();
+  const int total = warp_base[8];
+  for (int i = tid; i < total; i += 256) {
+    const int pr = cand[i] >> 8, pj = cand[i] & 255;
+    if (iou_reaches(rows[pr], cols[pj], thr)) atomicOr(&part[pr][pj >> 4], 1u << (pj & 15));
+  }
   __syncthreads();
   if (tid < kNmsBlock && row < k) {
     unsigned long long w = (unsigned long long)part[r][0] | ((unsigned long long)part[r][1] << 16) |
