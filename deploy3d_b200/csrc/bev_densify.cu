@@ -60,6 +60,43 @@ __global__ void densify_kernel(const int32_t* __restrict__ map, const T* __restr
     out[((((int64_t)b * c + ch) * z + zz) * y + yy) * x + xx] = tile[lane * pitch + ch];
 }
 
+// 16-bit features, c a multiple of 8, even x: a CTA takes 64 cells of a row; the feature rows come in as 16-byte
+// loads, and every warp store covers 64 consecutive cells of one channel plane (128 bytes).
+constexpr int kWideStrip = 64;
+__global__ void __launch_bounds__(256)
+densify_wide_kernel(const int32_t* __restrict__ map, const unsigned short* __restrict__ feats, int c, int z, int y,
+                    int x, unsigned short* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  uint32_t* tile = reinterpret_cast<uint32_t*>(smem_raw);  // [kWideStrip][c / 2 + 1] words: odd pitch
+  __shared__ int32_t vid[kWideStrip];
+  const int pitch = c / 2 + 1;
+  const int x0 = blockIdx.x * kWideStrip, yy = blockIdx.y, bz = blockIdx.z;
+  const int b = bz / z, zz = bz % z;
+  if (threadIdx.x < kWideStrip) {
+    int xx = x0 + threadIdx.x;
+    vid[threadIdx.x] = xx < x ? map[((int64_t)bz * y + yy) * x + xx] : -1;
+  }
+  __syncthreads();
+  const int vec_per_row = c / 8;
+  for (int e = threadIdx.x; e < kWideStrip * vec_per_row; e += blockDim.x) {
+    const int r = e / vec_per_row, q = e - r * vec_per_row;
+    const int v = vid[r];
+    uint4 w = make_uint4(0u, 0u, 0u, 0u);
+    if (v >= 0) w = __ldg(reinterpret_cast<const uint4*>(feats + (int64_t)v * c) + q);
+    uint32_t* d = tile + r * pitch + q * 4;
+    d[0] = w.x, d[1] = w.y, d[2] = w.z, d[3] = w.w;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+  const int xx = x0 + 2 * lane;
+  if (xx >= x) return;  // x is even: a pair of cells is inside or outside together
+  const unsigned short* t16 = reinterpret_cast<const unsigned short*>(tile);
+  for (int ch = warp; ch < c; ch += nwarp) {
+    const uint32_t lo = t16[(2 * lane) * pitch * 2 + ch], hi = t16[(2 * lane + 1) * pitch * 2 + ch];
+    *reinterpret_cast<uint32_t*>(out + ((((int64_t)b * c + ch) * z + zz) * y + yy) * x + xx) = lo | (hi << 16);
+  }
+}
+
 }  // namespace
 }  // namespace d3d
 
@@ -121,6 +158,15 @@ extern "C" int d3d_bev_densify_enqueue(const d3d_bev_densify_params* p, const d3
                                                    reinterpret_cast<float*>(outputs[0]));
   } else {
     // half and bf16 are both moved as 16-bit words
+    const size_t wide_smem = (size_t)kWideStrip * (c / 2 + 1) * 4;
+    if (c % 8 == 0 && x % 2 == 0 && wide_smem <= 48 * 1024 && reinterpret_cast<uintptr_t>(inputs[0]) % 16 == 0 &&
+        reinterpret_cast<uintptr_t>(outputs[0]) % 4 == 0) {
+      dim3 wide((unsigned)ceil_div(x, kWideStrip), (unsigned)y, (unsigned)(b * z));
+      densify_wide_kernel<<<wide, 256, wide_smem, st>>>(map, reinterpret_cast<const unsigned short*>(inputs[0]), c, z,
+                                                        y, x, reinterpret_cast<unsigned short*>(outputs[0]));
+      D3D_CHECK_LAUNCH();
+      return D3D_OK;
+    }
     size_t smem = (size_t)kStrip * (c + 2) * 2;
     D3D_REQUIRE(smem <= 48 * 1024, D3D_ERR_TOO_LARGE);
     densify_kernel<unsigned short><<<grid, 256, smem, st>>>(map, reinterpret_cast<const unsigned short*>(inputs[0]),

@@ -166,19 +166,28 @@ __global__ void mean_accumulate_kernel(const int32_t* __restrict__ slot_of, cons
 // trt/voxel_encoder/simple_mean_trt.cu:93-102
 // With `lp` != null the mean is also written in half / bfloat16 into rows of `lp_c` >= c channels (the extra
 // channels zero): the tensor the first sparse convolution reads, without a separate cast-and-pad kernel.
+// One thread per voxel: its c sums become means in place; the low-precision row is put together in registers and
+// leaves as 16-byte stores where the row width allows.
 template <class LP>
 __global__ void mean_divide_kernel(float* __restrict__ out_feats, const int32_t* __restrict__ count,
                                    const int32_t* num_act_out, int c, LP* __restrict__ lp, int lp_c) {
-  int64_t n = (int64_t)*num_act_out * c;
-  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < n; e += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t v = e / c;
-    const float mean = __fdiv_rn(out_feats[e], (float)count[v]);
-    out_feats[e] = mean;
-    if (lp) {
-      const int ch = (int)(e - v * c);
-      lp[v * lp_c + ch] = LP(mean);
-      if (ch == c - 1)
-        for (int z = c; z < lp_c; ++z) lp[v * lp_c + z] = LP(0.f);
+  const int n = *num_act_out;
+  const bool wide = lp && lp_c % 8 == 0 && (reinterpret_cast<uintptr_t>(lp) & 15) == 0;
+  for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < n; v += gridDim.x * blockDim.x) {
+    const float cnt = (float)count[v];
+    float* row = out_feats + (int64_t)v * c;
+    for (int ch = 0; ch < c; ++ch) row[ch] = __fdiv_rn(row[ch], cnt);
+    if (!lp) continue;
+    LP* lrow = lp + (int64_t)v * lp_c;
+    if (wide) {
+      for (int z0 = 0; z0 < lp_c; z0 += 8) {
+        __align__(16) LP h[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) h[q] = LP(z0 + q < c ? row[z0 + q] : 0.f);
+        *reinterpret_cast<uint4*>(lrow + z0) = *reinterpret_cast<const uint4*>(h);
+      }
+    } else {
+      for (int z = 0; z < lp_c; ++z) lrow[z] = LP(z < c ? row[z] : 0.f);
     }
   }
 }
@@ -322,10 +331,10 @@ extern "C" int d3d_simple_mean_encoder_enqueue_ex(const d3d_voxel_encoder_params
     mean_accumulate_kernel<<<pl.nblk, kEncThreads, 0, st>>>(pl.slot_of, pl.slot_vid, pts, pl.n, pl.c, out_feats,
                                                             pl.count);
     if (lp && extras->lp_dtype == D3D_BF16)
-      mean_divide_kernel<__nv_bfloat16><<<stream_grid(m_max * pl.c, 256), 256, 0, st>>>(
+      mean_divide_kernel<__nv_bfloat16><<<stream_grid(m_max, 256), 256, 0, st>>>(
           out_feats, pl.count, num_act_out, pl.c, reinterpret_cast<__nv_bfloat16*>(lp), extras->lp_channels);
     else
-      mean_divide_kernel<__half><<<stream_grid(m_max * pl.c, 256), 256, 0, st>>>(
+      mean_divide_kernel<__half><<<stream_grid(m_max, 256), 256, 0, st>>>(
           out_feats, pl.count, num_act_out, pl.c, reinterpret_cast<__half*>(lp), lp ? extras->lp_channels : 0);
   }
   D3D_CHECK_LAUNCH();

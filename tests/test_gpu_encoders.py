@@ -214,6 +214,21 @@ def test_bev_densify_config3_shape(d3d, orc):
         assert (out.float().cpu().numpy() == want).all()
 
 
+@pytest.mark.parametrize("c,y,x", [(128, 180, 180), (40, 50, 62), (8, 3, 2), (136, 7, 130), (12, 20, 64)])
+def test_bev_densify_strips(d3d, orc, c, y, x):
+    """Row lengths that end inside a 64-cell strip, channel counts that are and are not a multiple of eight (the
+    16-byte row loads of the half-precision kernel need one), the 180 x 180 map of benchmark config 4."""
+    from tests._util import unique_coors
+    r = rng(78 + c + x)
+    n = min(9000, y * x)
+    coors = unique_coors(r, n, [1, 2, y, x])
+    feats = r.standard_normal((n, c)).astype(np.float16)
+    out = d3d.bev_densify(_t(feats), _t(coors), torch.tensor([n], dtype=torch.int32, device=DEV),
+                          _shape([1, 0, 2, y, x]), 2 * c)
+    want = orc.bev_densify(feats.astype(np.float32), coors, n, [1, 0, 2, y, x])
+    assert (out.float().cpu().numpy() == want).all()
+
+
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 def test_mean_encoder_low_precision_output(d3d, dtype):
     """The optional extra output of SimpleMeanEncoder: the voxel means in half / bfloat16, zero-padded to 16
