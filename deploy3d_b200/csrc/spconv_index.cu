@@ -520,12 +520,35 @@ __global__ void conv_assign_kernel(const unsigned long long* __restrict__ table,
   int total;
   int id = winners_base[blockIdx.x] + block_exclusive_scan(cnt, scratch, &total);
   if (i >= n || cnt == 0) return;
-  // packed: the bits and the loop run over the entries of the input (ascending by offset, so the numbering is the same)
-  const int steps = packed ? kPackedSlots : g.kvol;
+  if (packed) {
+    // the bits run over the entries of the input (ascending by offset, so the numbering is the same): all entries,
+    // then all keys of the winning ones (independent gathers), then the writes
+    int slot[kPackedSlots];
+    unsigned long long kv[kPackedSlots];
+#pragma unroll
+    for (int j = 0; j < kPackedSlots; ++j)
+      slot[j] = ((bits >> j) & 1u) ? entry_value(__ldg(pair_out + (int64_t)j * n_max + i)) : -1;
+#pragma unroll
+    for (int j = 0; j < kPackedSlots; ++j) kv[j] = slot[j] >= 0 ? __ldg(table + slot[j]) : 0ull;
+#pragma unroll
+    for (int j = 0; j < kPackedSlots; ++j) {
+      if (slot[j] < 0) continue;
+      if (id < max_out) {
+        slot_out[slot[j]] = id;
+        int32_t oc[D3D_MAX_NDIM + 1];
+        decode_key(g, (uint32_t)(kv[j] >> 32), oc);
+        for (int d = 0; d <= g.ndim; ++d) out_coors[(int64_t)id * (g.ndim + 1) + d] = oc[d];
+      } else {
+        slot_out[slot[j]] = -1;  // beyond maxNumActOut: the pair is dropped (index.cu:158-172)
+      }
+      ++id;
+    }
+    return;
+  }
+  const int steps = g.kvol;
   for (int k = 0; k < steps; ++k) {
     if (small && !((bits >> k) & 1u)) continue;
-    int slot = pair_out[(int64_t)k * n_max + i];
-    if (packed) slot = entry_value(slot);
+    const int slot = pair_out[(int64_t)k * n_max + i];
     if (!small && !is_winner(table, slot, (uint32_t)(i * g.kvol + k))) continue;
     if (id < max_out) {
       slot_out[slot] = id;
@@ -711,6 +734,8 @@ __global__ void compact_kernel(const int32_t* __restrict__ pair_out, const int32
 // Same result for small kernels (kvol <= kCompactAllMaxVol): one CTA per input block walks all offsets, with a
 // single barrier between counting and writing instead of two per (block, offset).
 constexpr int kCompactAllMaxVol = 64;
+constexpr int kCompactHeld = 27;  // kernel volumes up to 3 x 3 x 3 keep an input's entries in registers
+template <bool kHold>
 __global__ void __launch_bounds__(kIdxThreads)
 compact_all_kernel(const int32_t* __restrict__ pair_out, const int32_t* __restrict__ block_prefix,
                    const int32_t* __restrict__ seg, const int32_t* num_act_in, int64_t n_max, int nblk, int kvol,
@@ -722,14 +747,27 @@ compact_all_kernel(const int32_t* __restrict__ pair_out, const int32_t* __restri
   constexpr int kBatch = 9;  // loads in flight per thread
   const int i = blockIdx.x * kIdxThreads + threadIdx.x;
   const int warp = threadIdx.x >> 5;
-  for (int k0 = 0; k0 < kvol; k0 += kBatch) {
-    int v[kBatch];
+  int held[kHold ? kCompactHeld : 1];
+  if (kHold) {  // one read of the pair table: all loads first, then the ballots
 #pragma unroll
-    for (int j = 0; j < kBatch; ++j) v[j] = (i < n && k0 + j < kvol) ? __ldg(pair_out + (int64_t)(k0 + j) * n_max + i) : -1;
+    for (int k = 0; k < kCompactHeld; ++k)
+      held[k] = (i < n && k < kvol) ? __ldg(pair_out + (int64_t)k * n_max + i) : -1;
 #pragma unroll
-    for (int j = 0; j < kBatch; ++j) {
-      const unsigned hits = __ballot_sync(0xffffffffu, v[j] >= 0);
-      if (lane_id() == 0 && k0 + j < kvol) warp_cnt[k0 + j][warp] = __popc(hits);
+    for (int k = 0; k < kCompactHeld; ++k) {
+      const unsigned hits = __ballot_sync(0xffffffffu, held[k] >= 0);
+      if (lane_id() == 0 && k < kvol) warp_cnt[k][warp] = __popc(hits);
+    }
+  } else {
+    for (int k0 = 0; k0 < kvol; k0 += kBatch) {
+      int v[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j)
+        v[j] = (i < n && k0 + j < kvol) ? __ldg(pair_out + (int64_t)(k0 + j) * n_max + i) : -1;
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j) {
+        const unsigned hits = __ballot_sync(0xffffffffu, v[j] >= 0);
+        if (lane_id() == 0 && k0 + j < kvol) warp_cnt[k0 + j][warp] = __popc(hits);
+      }
     }
   }
   __syncthreads();
@@ -745,22 +783,30 @@ compact_all_kernel(const int32_t* __restrict__ pair_out, const int32_t* __restri
     }
   }
   __syncthreads();
-  for (int k0 = 0; k0 < kvol; k0 += kBatch) {
-    int v[kBatch];
-#pragma unroll
-    for (int j = 0; j < kBatch; ++j)
-      v[j] = (i < n && k0 + j < kvol) ? __ldg(pair_out + (int64_t)(k0 + j) * n_max + i) : -1;
-#pragma unroll
-    for (int j = 0; j < kBatch; ++j) {
-      const unsigned hits = __ballot_sync(0xffffffffu, v[j] >= 0);
-      if (v[j] >= 0) {
-        const int64_t pos = (int64_t)warp_cnt[k0 + j][warp] + __popc(hits & lanemask_lt());
-        if (pos < row_len) {
-          index[pos] = i;
-          index[row_len + pos] = v[j];
-          index[2 * row_len + pos] = k0 + j;
-        }
+  auto put = [&](int k, int v) {
+    const unsigned hits = __ballot_sync(0xffffffffu, v >= 0);
+    if (v >= 0) {
+      const int64_t pos = (int64_t)warp_cnt[k][warp] + __popc(hits & lanemask_lt());
+      if (pos < row_len) {
+        index[pos] = i;
+        index[row_len + pos] = v;
+        index[2 * row_len + pos] = k;
       }
+    }
+  };
+  if (kHold) {
+#pragma unroll
+    for (int k = 0; k < kCompactHeld; ++k)
+      if (k < kvol) put(k, held[k]);  // warp-uniform condition
+  } else {
+    for (int k0 = 0; k0 < kvol; k0 += kBatch) {
+      int v[kBatch];
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j)
+        v[j] = (i < n && k0 + j < kvol) ? __ldg(pair_out + (int64_t)(k0 + j) * n_max + i) : -1;
+#pragma unroll
+      for (int j = 0; j < kBatch; ++j)
+        if (k0 + j < kvol) put(k0 + j, v[j]);
     }
   }
 }
@@ -1125,8 +1171,8 @@ extern "C" int d3d_spconv_index_enqueue_ex(const d3d_spconv_index_params* p, con
     compact_packed_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in, n_max,
                                                         nblk, g.kvol, index, plan.row_len);
   else if (g.kvol <= kCompactAllMaxVol)
-    compact_all_kernel<<<nblk, kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg, num_act_in, n_max,
-                                                     nblk, g.kvol, index, plan.row_len);
+    (g.kvol <= kCompactHeld ? compact_all_kernel<true> : compact_all_kernel<false>)<<<nblk, kIdxThreads, 0, st>>>(
+        plan.pair_out, plan.block_counts, plan.seg, num_act_in, n_max, nblk, g.kvol, index, plan.row_len);
   else
     compact_kernel<<<dim3(nblk, g.kvol), kIdxThreads, 0, st>>>(plan.pair_out, plan.block_counts, plan.seg,
                                                                num_act_in, n_max, nblk, index, plan.row_len);
