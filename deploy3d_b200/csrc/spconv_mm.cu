@@ -56,8 +56,7 @@ __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t 
                                      int64_t m_max, int32_t* __restrict__ table, uint32_t* __restrict__ row_masks) {
   int64_t n = *num_index;
   n = n > row_len ? row_len : n;
-  // grid-stride over the live part of the rulebook only (the rows are sized for the worst case, mostly unused);
-  // whole warps iterate together so that the warp-wide match below is always fully populated
+  // grid-stride over the live part of the rulebook only (the rows are sized for the worst case, mostly unused)
   const int64_t n_warp = (n + 31) & ~(int64_t)31;
   constexpr int kUnroll = 4;  // entries in flight per thread
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
@@ -92,12 +91,11 @@ __global__ void table_scatter_kernel(const int32_t* __restrict__ index, int64_t 
                        D3D_BOUNDS_OK(s[u], 0, m_max, kSiteTableEntry));  // checked build: recorded
       // tile-major layout [tile of 128 outputs][k][128]: all offsets of a tile are one contiguous block
       if (valid) table[((int64_t)(s[u] >> 7) * kvol + k[u]) * 128 + (s[u] & 127)] = g[u];
-      // one atomic per distinct mask word in the warp: neighbouring entries mostly share (tile, offset, row quarter)
-      const unsigned long long word =
-          valid ? ((unsigned long long)(s[u] >> 7) * kvol + k[u]) * 4ull + (unsigned)((s[u] & 127) >> 5) : ~0ull;
-      const unsigned peers = __match_any_sync(0xffffffffu, word);
-      const unsigned bits = __reduce_or_sync(peers, valid ? 1u << (s[u] & 31) : 0u);
-      if (valid && (threadIdx.x & 31) == __ffs(peers) - 1) atomicOr(row_masks + word, bits);
+      // one result-less atomic per entry (collecting the bits of a warp per mask word first -- match.any + redux.or
+      // -- measured slower in the frame: 479 against 486 frames/s)
+      if (valid)
+        atomicOr(row_masks + ((unsigned long long)(s[u] >> 7) * kvol + k[u]) * 4ull + (unsigned)((s[u] & 127) >> 5),
+                 1u << (s[u] & 31));
     }
   }
 }
