@@ -170,6 +170,24 @@ __device__ __forceinline__ uint32_t hash_insert_min(unsigned long long* table, u
   return 0xFFFFFFFFu;
 }
 
+// The same insertion for key sets with few repeats (one voxel per key, or nearly): the slot is claimed without looking
+// first, so the common case -- an empty home slot -- costs one round trip to the table instead of two.
+__device__ __forceinline__ uint32_t hash_insert_min_claim_first(unsigned long long* table, uint32_t cap_mask,
+                                                                uint32_t key, uint32_t value) {
+  const unsigned long long mine = ((unsigned long long)key << 32) | value;
+  uint32_t slot = home_slot(key, cap_mask);
+  for (uint32_t probes = 0; probes <= (cap_mask >> 2); ++probes) {
+    const unsigned long long cur = atomicCAS(&table[slot], kEmptySlot, mine);
+    if (cur == kEmptySlot) return slot;
+    if ((uint32_t)(cur >> 32) == key) {
+      if ((uint32_t)cur > value) atomicMin(&table[slot], mine);
+      return slot;
+    }
+    slot = (slot + 4u) & cap_mask;
+  }
+  return 0xFFFFFFFFu;
+}
+
 // Lookup; returns the value or -1.
 __device__ __forceinline__ int32_t hash_lookup(const unsigned long long* __restrict__ table, uint32_t cap_mask,
                                                uint32_t key) {

@@ -124,7 +124,8 @@ __global__ void subm_insert_kernel(unsigned long long* table, const int32_t* __r
     if (c[d] < 0 || c[d] >= g.shape[d]) return;
     key = key * (uint32_t)g.shape[d] + (uint32_t)c[d];
   }
-  if (hash_insert_min(table, mask, key, (uint32_t)i) == 0xFFFFFFFFu) report_status(status, D3D_STATUS_HASH_FULL);
+  if (hash_insert_min_claim_first(table, mask, key, (uint32_t)i) == 0xFFFFFFFFu)
+    report_status(status, D3D_STATUS_HASH_FULL);
 }
 
 // SubM probe: pair_out[k][i] = id of the active voxel at (coor_i + pad - k*dil), or -1 (trt/spconv/index.cu:48-84).

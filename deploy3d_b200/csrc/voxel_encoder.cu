@@ -44,7 +44,7 @@ __global__ void voxelize_kernel(unsigned long long* table, uint32_t cap_mask, co
     int cz = (int)__fdiv_rn(__fsub_rn(p[2], cfg[2]), cfg[5]);
     if (cx >= 0 && cx < sx && cy >= 0 && cy < sy && cz >= 0 && cz < sz) {
       uint32_t key = (((uint32_t)b * sz + cz) * sy + cy) * sx + cx;
-      uint32_t s = hash_insert_min(table, cap_mask, key, (uint32_t)i);
+      uint32_t s = hash_insert_min_claim_first(table, cap_mask, key, (uint32_t)i);
       slot = s == 0xFFFFFFFFu ? -1 : (int)s;
       if (s == 0xFFFFFFFFu) report_status(status, D3D_STATUS_HASH_FULL);
     }
@@ -80,7 +80,7 @@ __global__ void cylinderize_kernel(unsigned long long* table, uint32_t cap_mask,
         zc = zc < 0 ? 0 : zc;  // z is clamped, not dropped (cylinder_trt.cu:64-66)
         zc = zc >= sz ? sz - 1 : zc;
         uint32_t key = (((uint32_t)b * sr + rc) * sp + pc) * sz + zc;
-        uint32_t s = hash_insert_min(table, cap_mask, key, (uint32_t)i);
+        uint32_t s = hash_insert_min_claim_first(table, cap_mask, key, (uint32_t)i);
         slot = s == 0xFFFFFFFFu ? -1 : (int)s;
         a[0] = z;
         a[1] = phi;
