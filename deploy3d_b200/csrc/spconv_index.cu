@@ -412,7 +412,7 @@ conv_insert3_kernel(unsigned long long* table, const int32_t* __restrict__ coors
           int v = -1;
           if (batch_ok && o0[k0] >= 0 && o1[k1] >= 0 && o2[k2] >= 0) {
             const uint32_t key = (((uint32_t)c.x * s1 + (uint32_t)o0[k0]) * s2 + (uint32_t)o1[k1]) * s3 + (uint32_t)o2[k2];
-            const uint32_t slot = hash_insert_min(table, mask, key, pair_base + (uint32_t)k);
+            const uint32_t slot = hash_insert_min_claim_first(table, mask, key, pair_base + (uint32_t)k);
             v = slot == 0xFFFFFFFFu ? -1 : (int)slot;
             if (slot == 0xFFFFFFFFu) report_status(status, D3D_STATUS_HASH_FULL);
           }
